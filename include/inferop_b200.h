@@ -1,0 +1,108 @@
+/*
+ * inferop_b200: C ABI of the B200 (sm_100a) blockwise-FP8 W8A8 path.
+ *
+ * This is the boundary a foreign-function binding attaches to: plain C,
+ * pointers and sizes only.  Every tensor pointer is caller-owned device memory
+ * on the current CUDA device unless a comment says "host".  `stream` is a
+ * cudaStream_t passed as void* (NULL = the default stream).  Calls enqueue
+ * work and return; they never synchronise unless stated.
+ *
+ * Return value: INFEROP_OK (0) when the work was enqueued, otherwise one of
+ * the INFEROP_ERR_* codes and nothing was launched.  There is no CPU or
+ * generic-GPU fallback: without an sm_100 device every operator returns
+ * INFEROP_ERR_NO_DEVICE / INFEROP_ERR_ARCH.
+ *
+ * dtype codes (reference include/inferop/common.h:13):
+ *   0 = fp32, 1 = fp16, 2 = bf16, 3 = fp8_e4m3.
+ */
+#ifndef INFEROP_B200_H_
+#define INFEROP_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define INFEROP_API __attribute__((visibility("default")))
+#else
+#define INFEROP_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  INFEROP_OK = 0,
+  INFEROP_ERR_SHAPE = 1,      /* sizes the reference treats as a no-op / contract violation */
+  INFEROP_ERR_DTYPE = 2,      /* dtype code not supported by this operator */
+  INFEROP_ERR_POINTER = 3,    /* NULL tensor pointer */
+  INFEROP_ERR_NO_DEVICE = 4,  /* no CUDA device visible */
+  INFEROP_ERR_ARCH = 5,       /* current device is not sm_100 */
+  INFEROP_ERR_CUDA = 6,       /* a CUDA runtime/driver call failed; see inferop_last_cuda_error */
+  INFEROP_ERR_LIMIT = 7,      /* size beyond a documented limit of the entry point */
+  INFEROP_ERR_DEVICE_WAIT = 8 /* a bounded wait inside a kernel ran out (inferop_device_status) */
+};
+
+/* Human-readable name of a status code. */
+INFEROP_API const char* inferop_status_string(int status);
+/* cudaError_t of the most recent failed CUDA call on this thread (0 if none). */
+INFEROP_API int inferop_last_cuda_error(void);
+
+/* ---- device queries (reference include/inferop/ops.h:19-25, kernels/api.cu:12-50) ---- */
+INFEROP_API int inferop_has_cuda(void);                 /* 1 when at least one device is visible */
+INFEROP_API int inferop_device_count(void);
+INFEROP_API const char* inferop_device_name(int ordinal);   /* "-" when out of range */
+INFEROP_API int inferop_device_sm_version(int ordinal);     /* major*10+minor, -1 when out of range */
+
+/* ---- per-token-group quantisation
+ * Replaces inferop::quant_fp8_per_token_group (reference include/inferop/ops.h:64-65,
+ * kernels/api.cu:73-76, kernels/quant.cu:50-75).
+ *   x [rows, cols] in dt (0/1/2) -> q [rows, cols] uint8, scales [rows, cols/group_size] fp32.
+ * Bit-exact against reference/reference.cpp:65-80.  Any group_size dividing cols is
+ * accepted; 128 takes the vectorised kernel. */
+INFEROP_API int inferop_quant_fp8_per_token_group(void* q, void* scales, const void* x, int32_t dt,
+                                      int64_t rows, int64_t cols, int32_t group_size,
+                                      void* stream);
+
+/* Replaces inferop::dequant_fp8_per_token_group (reference include/inferop/ops.h:68-70,
+ * kernels/quant.cu:77-103):  x = decode(q) * scale, stored as dt. */
+INFEROP_API int inferop_dequant_fp8_per_token_group(void* x, int32_t dt, const void* q, const void* scales,
+                                        int64_t rows, int64_t cols, int32_t group_size,
+                                        void* stream);
+
+/* ---- blockwise-FP8 GEMM
+ * Replaces inferop::w8a8_block_fp8_gemm (reference include/inferop/ops.h:81-84,
+ * kernels/api.cu:83-88, kernels/gemm/w8a8_block_fp8.cu:163-188).
+ *   a_q [M,K] E4M3, a_scales [M,K/128] fp32, b_q [N,K] E4M3,
+ *   b_scales [ceil(N/128), K/128] fp32, c [M,N] in out_dt (0/1/2).
+ * Contract as in the reference: group_size == 128, block_n == 128, K % 128 == 0,
+ * M > 0, N > 0 (else INFEROP_ERR_SHAPE).  a_q and b_q must be 16-byte aligned
+ * (INFEROP_ERR_POINTER otherwise); c may have any alignment and N any value. */
+INFEROP_API int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, const void* b_q,
+                                const void* b_scales, int64_t m, int64_t n, int64_t k,
+                                int32_t group_size, int32_t block_n, int32_t out_dt,
+                                void* stream);
+
+/* ---- diagnostics
+ * Synchronises the current device and copies out the device-side status record
+ * {code, block, aux0, aux1}.  code == 0 means no bounded wait has run out since
+ * the last reset.  Returns INFEROP_OK, INFEROP_ERR_DEVICE_WAIT (record non-zero)
+ * or INFEROP_ERR_CUDA.  `out4` (host, 4 x uint32) may be NULL. */
+INFEROP_API int inferop_device_status(uint32_t* out4, int reset);
+
+/* Self-test of the hardware fp32 -> E4M3 converter used by the quantiser against the
+ * software encoder of include/inferop/fp8.h (reference include/inferop/fp8.h:62-96) on every
+ * fp32 bit pattern in [lo, hi), hi <= 2^32.  Synchronous.  out2 (host): [0] mismatches on
+ * non-NaN inputs (must be 0), [1] mismatches on NaN inputs (sign handling, fixed up in the
+ * quantiser). */
+INFEROP_API int inferop_selftest_e4m3_cvt(uint64_t lo, uint64_t hi, uint64_t* out2);
+
+/* Tuning knobs for experiments and tests (process-wide, not thread-safe).
+ * key: "gemm_block_n" (0 = auto, 128, 256), "gemm_tma_store" (-1 auto, 0, 1),
+ *      "gemm_ctas" (0 = one per SM).  Returns INFEROP_ERR_SHAPE for an unknown key/value. */
+INFEROP_API int inferop_set_option(const char* key, int64_t value);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* INFEROP_B200_H_ */

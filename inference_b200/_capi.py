@@ -1,0 +1,63 @@
+"""ctypes binding of libinferop_b200.so (the C ABI declared in include/inferop_b200.h).
+
+The library is the only implementation: if it has not been built, importing
+this module raises, and nothing falls back to torch or to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from .build import LIB_PATH
+
+OK = 0
+ERR_SHAPE, ERR_DTYPE, ERR_POINTER, ERR_NO_DEVICE, ERR_ARCH, ERR_CUDA, ERR_LIMIT, ERR_DEVICE_WAIT = range(1, 9)
+
+# every symbol include/inferop_b200.h declares: name -> (restype, argtypes)
+_vp, _i32, _i64, _u64 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64
+SIGNATURES = {
+    "inferop_status_string": (C.c_char_p, [C.c_int]),
+    "inferop_last_cuda_error": (C.c_int, []),
+    "inferop_has_cuda": (C.c_int, []),
+    "inferop_device_count": (C.c_int, []),
+    "inferop_device_name": (C.c_char_p, [C.c_int]),
+    "inferop_device_sm_version": (C.c_int, [C.c_int]),
+    "inferop_quant_fp8_per_token_group": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _i64, _i32, _vp]),
+    "inferop_dequant_fp8_per_token_group": (C.c_int, [_vp, _i32, _vp, _vp, _i64, _i64, _i32, _vp]),
+    "inferop_w8a8_block_fp8_gemm": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32,
+                                              _i32, _vp]),
+    "inferop_device_status": (C.c_int, [C.POINTER(C.c_uint32), C.c_int]),
+    "inferop_selftest_e4m3_cvt": (C.c_int, [_u64, _u64, C.POINTER(_u64)]),
+    "inferop_set_option": (C.c_int, [C.c_char_p, _i64]),
+}
+
+
+class InferopError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        self.status = status
+        super().__init__(f"{what}: {status_string(status)} (status {status})")
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m inference_b200.build` "
+            "(nvcc, sm_100a). There is no fallback implementation.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+def status_string(status: int) -> str:
+    return lib.inferop_status_string(status).decode()
+
+
+def check(status: int, what: str) -> None:
+    if status != OK:
+        raise InferopError(status, what)

@@ -1,0 +1,466 @@
+// Blockwise-FP8 W8A8 GEMM for sm_100a: TMA -> swizzled shared memory ->
+// tcgen05.mma (E4M3 x E4M3 -> fp32 in tensor memory) -> per-K-block scale
+// promotion into fp32 registers -> bf16/fp16/fp32 output.
+//
+// Replaces the reference's kernels/gemm/w8a8_block_fp8.cu (CUDA-core kernel
+// :27-126, run-time tile dispatch :128-159) with one persistent, warp-
+// specialised kernel.  The arithmetic contract is the reference's
+// (w8a8_block_fp8.cu:100-114, reference/reference.cpp:93-110):
+//     C[m,n] = sum_kb ( sa[m,kb] * sb[n/128,kb] ) * sum_{k in kb} A_q[m,k] * B_q[n,k]
+// The inner sum over one 128-wide K block is exact-product fp32 accumulation
+// on the tensor core; the outer sum is an fp32 FMA per output element per K
+// block on the CUDA cores ("promotion"), so no scale is ever folded into a
+// reduced-precision accumulator.  Output is rounded once (RNE).
+//
+// CTA layout (384 threads, one CTA per SM, persistent over output tiles):
+//   warp 0      TMA producer: A tile [128 x 128 B] and B tile [BN x 128 B] per
+//               K block into a kStages-deep ring (128-byte swizzle, K-major)
+//   warp 1      MMA issuer: 4 x tcgen05.mma (M=128, N=BN, K=32) per K block into
+//               TMEM accumulator buffer (kb & 1); commits free the smem stage
+//               and publish the TMEM buffer
+//   warp 2      allocates / frees tensor memory (2 x BN columns)
+//   warps 4-11  promotion + epilogue.  Warp w reads TMEM lane quarter w % 4
+//               (its 32 rows) and column half (w - 4) / 4 of the tile; each
+//               thread owns one output row segment of BN/2 columns in registers.
+//
+// Shared memory (dynamic, 1024-byte aligned):
+//   [kStages x (A 16 KiB | B BN*128 B)] [2 x 16 KiB output staging] [barriers]
+//
+// HBM traffic per call (algorithmic): M*K + N*K operand bytes, 4*M*K/128 +
+// 4*ceil(N/128)*K/128 scale bytes, M*N*sizeof(out) output bytes; operand
+// re-reads by other tiles are served by L2 (tiles are rasterised in bands of
+// 16 M-tiles so that concurrently running CTAs share A and B panels).
+//
+// Every wait is bounded (ptx.cuh: mbar_wait).  A wait that runs out sets the
+// CTA's abort flag and the device status record; all roles then fall through
+// to the common exit, tensor memory is freed, and the kernel returns.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "internal.h"
+
+namespace ib200 {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 128;
+constexpr int kPromoWarps = 8;
+constexpr int kThreads = 128 + 32 * kPromoWarps;
+constexpr int kGroupM = 16;  // M-tiles per rasterisation band
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kBytesA = BM * BK;
+  static constexpr int kBytesB = BN * BK;
+  static constexpr int kStageBytes = kBytesA + kBytesB;
+  static constexpr int kCols = BN / 2;          // output columns per promotion thread
+  static constexpr int kTmemCols = 2 * BN;      // two accumulator buffers
+  static constexpr int kStoreBufBytes = 128 * 128;  // 128 rows x 64 two-byte columns
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + 2 * kStoreBufBytes + kBarrierBytes + 1024 /* alignment slack */;
+};
+
+struct GemmParams {
+  const float* a_scales;
+  const float* b_scales;
+  void* c;
+  int m, n, k;
+  int kb;        // K / 128
+  int nb;        // ceil(N / 128): rows of b_scales
+  int tiles_m, tiles_n, num_tiles;
+  int tma_store; // 1: epilogue goes through shared memory + TMA store
+  DeviceStatus* status;
+};
+
+// wait sites reported in DeviceStatus::code
+enum : uint32_t {
+  kSiteProducerEmpty = 0x101,
+  kSiteProducerDrain = 0x102,
+  kSiteMmaTmemEmpty = 0x201,
+  kSiteMmaFull = 0x202,
+  kSitePromoTmemFull = 0x301,
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_band = kGroupM * tiles_n;
+  const int band = t / per_band;
+  const int first_m = band * kGroupM;
+  const int band_m = min(kGroupM, tiles_m - first_m);
+  const int r = t - band * per_band;
+  tm = first_m + r % band_m;
+  tn = r / band_m;
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT to_out(float v);
+template <>
+__device__ __forceinline__ float to_out<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// two floats -> one 32-bit word of two 16-bit outputs (low half = a)
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<float>(float, float) { return 0u; }
+
+// Pin the 32 registers of a tensor-memory load behind the wait: nothing that
+// reads them may be scheduled before tcgen05.wait::ld.
+__device__ __forceinline__ void tmem_ld_wait_pin(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]),
+                 "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]),
+                 "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]),
+                 "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
+                 "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+// acc[0..31] += v[0..31] * s, two lanes per instruction (fma.rn.f32x2)
+__device__ __forceinline__ void promote32(float2* acc, const uint32_t (&v)[32], float s) {
+  const float2 s2 = make_float2(s, s);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    acc[j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), s2,
+                        acc[j]);
+  }
+}
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* store_buf = smem + C::kStages * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_buf + 2 * C::kStoreBufBytes);
+  uint64_t* full = bars;                     // [kStages]  TMA -> MMA
+  uint64_t* empty = bars + C::kStages;       // [kStages]  MMA -> TMA
+  uint64_t* tmem_full = bars + 2 * C::kStages;       // [2] MMA -> promotion
+  uint64_t* tmem_empty = bars + 2 * C::kStages + 2;  // [2] promotion -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], kPromoWarps);
+    }
+    *abort_flag = 0u;
+    mbar_init_fence();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    if (p.tma_store) tma_prefetch_desc(&map_c);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    reg_dealloc<56>();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------ TMA producer ------------------------
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t armed = 0, armed_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        for (int kb = 0; kb < p.kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * C::kStageBytes;
+          mbar_arrive_expect_tx(&full[stage], C::kStageBytes);
+          tma_load_2d(sa, &map_a, &full[stage], kb * BK, tm * BM);
+          tma_load_2d(sa + C::kBytesA, &map_b, &full[stage], kb * BK, tn * BN);
+          armed |= 1u << stage;
+          armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // wind-down: let the copies this thread started land before the CTA exits
+        for (int s = 0; s < C::kStages; ++s) {
+          if (!(armed & (1u << s))) continue;
+          const uint32_t par = (armed_phase >> s) & 1u;
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full[s], par)) {
+            if (clock64() - t0 > kWaitBudgetCycles) {
+              atomicCAS(&p.status->code, 0u, kSiteProducerDrain);
+              break;
+            }
+          }
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------ MMA issuer --------------------------
+      constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t kiter = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+        for (int kb = 0; kb < p.kb; ++kb, ++kiter) {
+          const uint32_t buf = kiter & 1u;
+          const uint32_t use = kiter >> 1;
+          if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status,
+                         kSiteMmaTmemEmpty) ||
+              !mbar_wait(&full[stage], phase, abort_flag, p.status, kSiteMmaFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + stage * C::kStageBytes);
+          const uint64_t da = umma_desc_k_sw128(a_addr);
+          const uint64_t db = umma_desc_k_sw128(a_addr + C::kBytesA);
+          const uint32_t d_tmem = tmem_base + buf * BN;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 32; ++k4) {
+            // 32 E4M3 elements = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
+            umma_f8_ss(d_tmem, da + 2u * k4, db + 2u * k4, idesc, k4 > 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          umma_commit(&tmem_full[buf]);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else {
+    reg_alloc<224>();
+    // ------------------------------ promotion + epilogue ------------------
+    const int pw = warp - 4;
+    const int quarter = pw & 3;  // == warp % 4: the TMEM lane quarter this warp may read
+    const int half = pw >> 2;    // which BN/2 column half of the tile
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    uint8_t* my_buf = store_buf + half * C::kStoreBufBytes;
+    const bool issuer = (quarter == 0 && lane == 0);
+    uint32_t kiter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const int gm = tm * BM + row;
+      const int col0 = tn * BN + half * C::kCols;  // first output column of this thread
+      const int nbi = col0 >> 7;
+      const bool have_scales = (gm < p.m) && (nbi < p.nb);
+      const float* sa_ptr = p.a_scales + static_cast<int64_t>(have_scales ? gm : 0) * p.kb;
+      const float* sb_ptr = p.b_scales + static_cast<int64_t>(have_scales ? nbi : 0) * p.kb;
+
+      float2 acc[C::kCols / 2];
+#pragma unroll
+      for (int j = 0; j < C::kCols / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
+
+      float s_next = have_scales ? __ldg(sa_ptr) * __ldg(sb_ptr) : 0.0f;
+      for (int kb = 0; kb < p.kb; ++kb, ++kiter) {
+        const float s = s_next;
+        if (kb + 1 < p.kb && have_scales) s_next = __ldg(sa_ptr + kb + 1) * __ldg(sb_ptr + kb + 1);
+        const uint32_t buf = kiter & 1u;
+        if (!mbar_wait(&tmem_full[buf], (kiter >> 1) & 1u, abort_flag, p.status,
+                       kSitePromoTmemFull)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t taddr = lane_base + buf * BN + half * C::kCols;
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32(taddr, v0);
+        tmem_ld_32x32(taddr + 32, v1);
+        tmem_ld_wait_pin(v0);
+        tmem_ld_wait_pin(v1);
+        if constexpr (C::kCols == 64) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          promote32(acc, v0, s);
+          promote32(acc + 16, v1, s);
+        } else {
+          promote32(acc, v0, s);
+          tmem_ld_32x32(taddr + 64, v0);
+          promote32(acc + 16, v1, s);
+          tmem_ld_32x32(taddr + 96, v1);
+          tmem_ld_wait_pin(v0);
+          tmem_ld_wait_pin(v1);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          promote32(acc + 32, v0, s);
+          promote32(acc + 48, v1, s);
+        }
+      }
+      if (!ok) break;
+
+      // ---- epilogue: this thread holds C[gm, col0 .. col0 + kCols) in fp32
+      const float* accf = reinterpret_cast<const float*>(acc);
+      if (sizeof(OutT) == 2 && p.tma_store) {
+#pragma unroll
+        for (int ch = 0; ch < C::kCols / 64; ++ch) {
+          // the staging buffer may still be read by the previous TMA store
+          if (issuer) tma_store_wait_read0();
+          named_bar_sync(1 + half, 128);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 w;
+            const float* a8 = accf + ch * 64 + j * 8;
+            w.x = pack2<OutT>(a8[0], a8[1]);
+            w.y = pack2<OutT>(a8[2], a8[3]);
+            w.z = pack2<OutT>(a8[4], a8[5]);
+            w.w = pack2<OutT>(a8[6], a8[7]);
+            // 128-byte swizzle: 16-byte chunk j of row r lives at chunk j ^ (r & 7)
+            *reinterpret_cast<uint4*>(my_buf + row * 128 + ((j ^ (row & 7)) << 4)) = w;
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1 + half, 128);
+          const int x = col0 + ch * 64;
+          if (issuer && x < p.n) {
+            tma_store_2d(&map_c, my_buf, x, tm * BM);
+            tma_store_commit();
+          }
+        }
+      } else if (gm < p.m) {
+        OutT* crow = static_cast<OutT*>(p.c) + static_cast<int64_t>(gm) * p.n;
+        constexpr int kVec = 16 / sizeof(OutT);
+        // fully unrolled: the accumulators must stay in registers
+#pragma unroll
+        for (int j = 0; j < C::kCols; j += kVec) {
+          const int col = col0 + j;
+          alignas(16) OutT tmp[kVec];
+#pragma unroll
+          for (int e = 0; e < kVec; ++e) tmp[e] = to_out<OutT>(accf[j + e]);
+          if (col + kVec <= p.n && (reinterpret_cast<uintptr_t>(crow + col) & 15u) == 0) {
+            *reinterpret_cast<uint4*>(crow + col) = *reinterpret_cast<const uint4*>(tmp);
+          } else {
+#pragma unroll
+            for (int e = 0; e < kVec; ++e)
+              if (col + e < p.n) crow[col + e] = tmp[e];
+          }
+        }
+      }
+    }
+    if (issuer) tma_store_wait_all();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 2) tmem_dealloc(tmem_base, C::kTmemCols);
+}
+
+template <int BN, typename OutT>
+int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+             const GemmParams& p, int ctas, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_kernel<BN, OutT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_done[dev] = true;
+  }
+  w8a8_gemm_kernel<BN, OutT><<<ctas, kThreads, C::kSmemBytes, stream>>>(ma, mb, mc, p);
+  return check_launch();
+}
+
+template <typename OutT>
+int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+              const GemmParams& p, int ctas, cudaStream_t stream) {
+  return bn == 256 ? launch_t<256, OutT>(ma, mb, mc, p, ctas, stream)
+                   : launch_t<128, OutT>(ma, mb, mc, p, ctas, stream);
+}
+
+}  // namespace
+
+int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, const void* b_q,
+                const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
+                cudaStream_t stream) {
+  const Options& opt = options();
+  int bn = opt.gemm_block_n;
+  if (bn == 0) bn = (n > 128) ? 256 : 128;
+  const int out_bytes = (out_dt == 0) ? 4 : 2;
+  bool tma_store = out_bytes == 2 && (n * out_bytes) % 16 == 0 &&
+                   (reinterpret_cast<uintptr_t>(c) % 16 == 0);
+  if (opt.gemm_tma_store == 0) tma_store = false;
+
+  GemmParams p;
+  p.a_scales = static_cast<const float*>(a_scales);
+  p.b_scales = static_cast<const float*>(b_scales);
+  p.c = c;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.kb = static_cast<int>(k / 128);
+  p.nb = static_cast<int>((n + 127) / 128);
+  p.tiles_m = static_cast<int>((m + BM - 1) / BM);
+  p.tiles_n = static_cast<int>((n + bn - 1) / bn);
+  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  if (tiles > 0x7FFFFFFF) return INFEROP_ERR_LIMIT;
+  p.num_tiles = static_cast<int>(tiles);
+  p.tma_store = tma_store ? 1 : 0;
+  p.status = ctx->status;
+
+  CUtensorMap ma, mb, mc;
+  int rc = make_tensor_map_2d(&ma, a_q, 1, m, k, k, BM, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  rc = make_tensor_map_2d(&mb, b_q, 1, n, k, k, bn, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  if (tma_store) {
+    rc = make_tensor_map_2d(&mc, c, 2, m, n, n * 2, 128, 64, true);
+    if (rc != INFEROP_OK) return rc;
+  } else {
+    mc = ma;  // unused by the kernel
+  }
+  int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
+  if (ctas > p.num_tiles) ctas = p.num_tiles;
+
+  switch (out_dt) {
+    case 0: return launch_bn<float>(bn, ma, mb, mc, p, ctas, stream);
+    case 1: return launch_bn<__half>(bn, ma, mb, mc, p, ctas, stream);
+    case 2: return launch_bn<__nv_bfloat16>(bn, ma, mb, mc, p, ctas, stream);
+    default: return INFEROP_ERR_DTYPE;
+  }
+}
+
+}  // namespace ib200

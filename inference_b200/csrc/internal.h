@@ -1,0 +1,54 @@
+// Declarations shared by the translation units of libinferop_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "inferop_b200.h"
+#include "ptx.cuh"
+
+namespace ib200 {
+
+// Records a failed CUDA call for inferop_last_cuda_error() and maps it to a status.
+int note_cuda_error(cudaError_t e);
+// cudaGetLastError() after a launch -> INFEROP_OK / INFEROP_ERR_CUDA.
+int check_launch();
+
+// Per-device facts and library-owned device objects, created on first use.
+struct DeviceCtx {
+  int ordinal = -1;
+  int sm_version = 0;
+  int sm_count = 0;
+  DeviceStatus* status = nullptr;  // device memory, zero-initialised
+};
+// Context of the current device (nullptr + *err set when there is none / wrong arch).
+DeviceCtx* current_ctx(int* err);
+
+struct Options {
+  int gemm_block_n = 0;    // 0 auto, 128, 256
+  int gemm_tma_store = -1; // -1 auto, 0 off, 1 on
+  int gemm_ctas = 0;       // 0 = one per SM
+};
+Options& options();
+
+// quant.cu
+int launch_quant(void* q, void* scales, const void* x, int32_t dt, int64_t rows, int64_t cols,
+                 int32_t gs, cudaStream_t stream, int sms);
+int launch_dequant(void* x, int32_t dt, const void* q, const void* scales, int64_t rows,
+                   int64_t cols, int32_t gs, cudaStream_t stream, int sms);
+
+int run_cvt_selftest(uint64_t lo, uint64_t hi, uint64_t* out2, int sms);
+
+// gemm_sm100.cu
+int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, const void* b_q,
+                const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
+                cudaStream_t stream);
+
+// tensormap.cu : cuTensorMapEncodeTiled through the runtime's driver entry point.
+// 2-D row-major tensor [rows, cols] of elem_bytes-wide elements with row pitch
+// pitch_bytes; box = [box_rows, box_cols]; 128-byte swizzle when swizzle128.
+int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows,
+                       uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                       bool swizzle128);
+
+}  // namespace ib200

@@ -1,0 +1,131 @@
+"""Host-side mirror of the reference's operator interface for the blockwise-FP8 path.
+
+Same operator names, argument meaning and contracts as the reference's
+``include/inferop/ops.h`` (:64-70 quant / dequant, :81-84 GEMM), over torch
+CUDA tensors instead of raw pointers.  torch is used for device memory and
+streams only; all arithmetic happens in libinferop_b200.so, reached through its
+C ABI.  Unlike the reference's ``void`` functions these raise ``InferopError``
+on a rejected call instead of doing nothing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+
+import torch
+
+from . import _capi
+from ._capi import InferopError, check, lib
+
+
+class dtype(enum.IntEnum):
+    """Element type codes of the C ABI (reference include/inferop/common.h:13)."""
+    fp32 = 0
+    fp16 = 1
+    bf16 = 2
+    fp8_e4m3 = 3
+
+
+_TORCH2CODE = {torch.float32: dtype.fp32, torch.float16: dtype.fp16, torch.bfloat16: dtype.bf16}
+_CODE2TORCH = {v: k for k, v in _TORCH2CODE.items()}
+
+
+def _stream_ptr(stream=None) -> int:
+    s = torch.cuda.current_stream() if stream is None else stream
+    return int(s.cuda_stream)
+
+
+def _dev_tensor(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t
+
+
+def has_cuda() -> bool:
+    return bool(lib.inferop_has_cuda())
+
+
+def device_count() -> int:
+    return int(lib.inferop_device_count())
+
+
+def device_name(ordinal: int = 0) -> str:
+    return lib.inferop_device_name(ordinal).decode()
+
+
+def device_sm_version(ordinal: int = 0) -> int:
+    return int(lib.inferop_device_sm_version(ordinal))
+
+
+def quant_fp8_per_token_group(x: torch.Tensor, group_size: int = 128, q: torch.Tensor | None = None,
+                              scales: torch.Tensor | None = None, stream=None):
+    """x [rows, cols] (fp32/fp16/bf16) -> (q uint8 [rows, cols], scales fp32 [rows, cols/gs])."""
+    _dev_tensor(x, "x")
+    if x.dim() != 2 or x.dtype not in _TORCH2CODE:
+        raise ValueError("x must be a 2-D fp32/fp16/bf16 tensor")
+    rows, cols = x.shape
+    if group_size <= 0 or cols % group_size != 0 or rows == 0:
+        raise InferopError(_capi.ERR_SHAPE, "quant_fp8_per_token_group")
+    with torch.cuda.device(x.device):
+        if q is None:
+            q = torch.empty((rows, cols), dtype=torch.uint8, device=x.device)
+        if scales is None:
+            scales = torch.empty((rows, cols // group_size), dtype=torch.float32, device=x.device)
+        check(lib.inferop_quant_fp8_per_token_group(q.data_ptr(), scales.data_ptr(), x.data_ptr(),
+                                                    int(_TORCH2CODE[x.dtype]), rows, cols, group_size,
+                                                    _stream_ptr(stream)),
+              "quant_fp8_per_token_group")
+    return q, scales
+
+
+def dequant_fp8_per_token_group(q: torch.Tensor, scales: torch.Tensor, out_dtype=torch.bfloat16,
+                                group_size: int = 128, stream=None) -> torch.Tensor:
+    _dev_tensor(q, "q")
+    _dev_tensor(scales, "scales")
+    rows, cols = q.shape
+    with torch.cuda.device(q.device):
+        x = torch.empty((rows, cols), dtype=out_dtype, device=q.device)
+        check(lib.inferop_dequant_fp8_per_token_group(x.data_ptr(), int(_TORCH2CODE[out_dtype]),
+                                                      q.data_ptr(), scales.data_ptr(), rows, cols,
+                                                      group_size, _stream_ptr(stream)),
+              "dequant_fp8_per_token_group")
+    return x
+
+
+def w8a8_block_fp8_gemm(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: torch.Tensor,
+                        b_scales: torch.Tensor, out_dtype=torch.bfloat16, group_size: int = 128,
+                        block_n: int = 128, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """C[M,N] = (A_q * sa) @ (B_q * sb)^T with fp32 accumulation.
+
+    a_q [M,K] uint8 (E4M3), a_scales [M,K/128] fp32, b_q [N,K] uint8,
+    b_scales [ceil(N/128), K/128] fp32.
+    """
+    for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
+        _dev_tensor(t, name)
+    m, k = a_q.shape
+    n = b_q.shape[0]
+    if b_q.shape[1] != k:
+        raise ValueError("a_q and b_q disagree on K")
+    with torch.cuda.device(a_q.device):
+        if out is None:
+            out = torch.empty((m, n), dtype=out_dtype, device=a_q.device)
+        check(lib.inferop_w8a8_block_fp8_gemm(out.data_ptr(), a_q.data_ptr(), a_scales.data_ptr(),
+                                              b_q.data_ptr(), b_scales.data_ptr(), m, n, k, group_size,
+                                              block_n, int(_TORCH2CODE[out.dtype]), _stream_ptr(stream)),
+              "w8a8_block_fp8_gemm")
+    return out
+
+
+def device_status(reset: bool = True):
+    """Synchronise and return the device-side status record (code, block, aux0, aux1)."""
+    rec = (C.c_uint32 * 4)()
+    rc = lib.inferop_device_status(rec, 1 if reset else 0)
+    if rc not in (_capi.OK, _capi.ERR_DEVICE_WAIT):
+        raise InferopError(rc, "device_status")
+    return tuple(int(v) for v in rec)
+
+
+def set_option(key: str, value: int) -> None:
+    check(lib.inferop_set_option(key.encode(), int(value)), f"set_option({key})")

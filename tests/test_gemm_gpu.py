@@ -1,0 +1,189 @@
+"""Parity of the CUDA GEMM (through the C ABI) with the fp64 golden of the oracle."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import (GEMM_FRO_TOL_BF16, GEMM_FRO_TOL_F32, GEMM_ROW_TOL, GOLDEN, config1_inputs,
+                      gemm_errors)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from inference_b200 import ops as _ops
+    assert _ops.has_cuda() and _ops.device_sm_version(0) == 100, "needs a B200"
+    yield _ops
+    _ops.set_option("gemm_block_n", 0)
+    _ops.set_option("gemm_tma_store", -1)
+
+
+def cuda(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def make_case(m, n, k, seed, w_std=0.02, outliers=False):
+    rng = np.random.default_rng(seed)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    if outliers:
+        a[:, rng.choice(k, max(1, k // 100), replace=False)] *= 20.0
+    a = oracle.bf16_widen(oracle.bf16_narrow(a))
+    w = oracle.bf16_widen(oracle.bf16_narrow((w_std * rng.standard_normal((n, k))).astype(np.float32)))
+    aq, a_s = oracle.quant_fp8_per_token_group(a)
+    bq, bs = oracle.block_quant_weights(w)
+    return aq, a_s, bq, bs
+
+
+def run(ops, aq, a_s, bq, bs, out_dtype):
+    c = ops.w8a8_block_fp8_gemm(cuda(aq), cuda(a_s), cuda(bq), cuda(bs), out_dtype)
+    code = ops.device_status()
+    assert code[0] == 0, f"a device-side wait ran out: {[hex(v) for v in code]}"
+    return c.float().cpu().numpy()
+
+
+def check(got, want, out_dtype):
+    row, fro = gemm_errors(got, want)
+    fro_tol = GEMM_FRO_TOL_F32 if out_dtype == torch.float32 else GEMM_FRO_TOL_BF16
+    assert row <= GEMM_ROW_TOL and fro <= fro_tol, f"row err {row:.3e}, frobenius {fro:.3e}"
+    return row, fro
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("tma_store", [0, 1])
+def test_single_tile_and_small_shapes(ops, bn, tma_store):
+    ops.set_option("gemm_block_n", bn)
+    ops.set_option("gemm_tma_store", tma_store)
+    for (m, n, k) in [(128, 128, 128), (128, 256, 256), (256, 256, 512), (32, 1024, 1024)]:
+        aq, a_s, bq, bs = make_case(m, n, k, seed=m + n + k)
+        want = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs, threads=8)
+        for dt in (torch.float32, torch.bfloat16):
+            check(run(ops, aq, a_s, bq, bs, dt), want, dt)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_golden_small_ragged(ops, bn):
+    ops.set_option("gemm_block_n", bn)
+    ops.set_option("gemm_tma_store", -1)
+    g = np.load(os.path.join(GOLDEN, "gemm_small_golden.npz"))
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        check(run(ops, g["aq"], g["a_scales"], g["bq"], g["b_scales"], dt), g["c"], dt)
+
+
+def test_config1_golden(ops):
+    ops.set_option("gemm_block_n", 0)
+    ops.set_option("gemm_tma_store", -1)
+    with open(os.path.join(GOLDEN, "config1_golden.json")) as f:
+        rec = json.load(f)
+    a_bits, w_bits = config1_inputs()
+    x = torch.from_numpy(a_bits.view(np.int16)).cuda().view(torch.bfloat16)
+    aq, a_s = ops.quant_fp8_per_token_group(x)
+    bq, bs = oracle.block_quant_weights(oracle.bf16_widen(w_bits))
+    aq_h, as_h = oracle.quant_fp8_per_token_group(oracle.bf16_widen(a_bits))
+    assert np.array_equal(aq.cpu().numpy(), aq_h) and np.array_equal(a_s.cpu().numpy(), as_h)
+    want = oracle.w8a8_block_fp8_gemm(aq_h, as_h, bq, bs, threads=8)
+    got = ops.w8a8_block_fp8_gemm(aq, a_s, cuda(bq), cuda(bs), torch.bfloat16).float().cpu().numpy()
+    row, fro = check(got, want, torch.bfloat16)
+    # the first 8 columns stored from the reference itself
+    import hashlib
+    if hashlib.sha256(a_bits.tobytes()).hexdigest() == rec["sha256"]["a_bf16_bits"]:
+        ref8 = np.array(rec["c_first8cols"], dtype=np.float32)
+        assert np.array_equal(want[:, :8], ref8)
+        assert gemm_errors(got[:, :8], ref8)[0] <= GEMM_ROW_TOL
+
+
+@pytest.mark.parametrize("m,n,k,dt", [
+    (100, 180, 256, torch.float32),   # the reference test's ragged case (N*2 not a multiple of 16)
+    (100, 180, 256, torch.bfloat16),
+    (1, 128, 128, torch.bfloat16),
+    (1, 1, 128, torch.float32),
+    (129, 257, 384, torch.bfloat16),
+    (300, 1000, 1536, torch.bfloat16),
+    (64, 3000, 2048, torch.float16),
+])
+def test_ragged_shapes(ops, m, n, k, dt):
+    for bn in (128, 256):
+        ops.set_option("gemm_block_n", bn)
+        ops.set_option("gemm_tma_store", -1)
+        aq, a_s, bq, bs = make_case(m, n, k, seed=m * 7 + n * 3 + k, outliers=True)
+        want = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs, threads=8)
+        check(run(ops, aq, a_s, bq, bs, dt), want, dt)
+
+
+def test_reference_test_tolerances(ops):
+    """tests/test_gemm.cpp:93-96: N(0,1) weights, rtol/atol of the reference's own cross-checks."""
+    ops.set_option("gemm_block_n", 0)
+    for (m, n, k, dt, rtol, atol) in [(256, 256, 512, torch.float32, 2e-3, 2e-2),
+                                      (256, 256, 512, torch.bfloat16, 1e-2, 3e-2),
+                                      (100, 180, 256, torch.float32, 2e-3, 2e-2)]:
+        aq, a_s, bq, bs = make_case(m, n, k, seed=99, w_std=1.0)
+        want = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs, threads=8)
+        got = run(ops, aq, a_s, bq, bs, dt)
+        assert np.all(np.abs(got - want) <= atol + rtol * np.abs(want))
+
+
+def test_untouched_outside_output_and_canaries(ops):
+    """Output rows/columns past M, N are never written (canary-padded buffer)."""
+    m, n, k = 100, 184, 256
+    aq, a_s, bq, bs = make_case(m, n, k, seed=5)
+    buf = torch.full((m * n + 4096,), -7.0, dtype=torch.bfloat16, device="cuda")
+    out = buf[:m * n].view(m, n)
+    for bn in (128, 256):
+        ops.set_option("gemm_block_n", bn)
+        ops.w8a8_block_fp8_gemm(cuda(aq), cuda(a_s), cuda(bq), cuda(bs), out=out)
+        torch.cuda.synchronize()
+        assert bool((buf[m * n:] == -7.0).all())
+    want = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs)
+    check(out.float().cpu().numpy(), want, torch.bfloat16)
+
+
+def test_rejected_calls(ops):
+    from inference_b200 import _capi
+    t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p = t.data_ptr()
+    lib = _capi.lib
+    assert lib.inferop_w8a8_block_fp8_gemm(p, p, p, p, p, 4, 4, 130, 128, 128, 2, None) == _capi.ERR_SHAPE
+    assert lib.inferop_w8a8_block_fp8_gemm(p, p + 1, p, p, p, 4, 4, 128, 128, 128, 2, None) == _capi.ERR_POINTER
+    assert lib.inferop_w8a8_block_fp8_gemm(p, None, p, p, p, 4, 4, 128, 128, 128, 2, None) == _capi.ERR_POINTER
+    # K == 0: the empty sum
+    out = torch.ones((4, 4), dtype=torch.bfloat16, device="cuda")
+    assert lib.inferop_w8a8_block_fp8_gemm(out.data_ptr(), p, p, p, p, 4, 4, 0, 128, 128, 2, None) == 0
+    torch.cuda.synchronize()
+    assert bool((out == 0).all())
+
+
+def test_repeatable_and_linear_in_scales(ops):
+    """Same inputs -> same bits; doubling every activation scale doubles C exactly."""
+    ops.set_option("gemm_block_n", 0)
+    aq, a_s, bq, bs = make_case(384, 640, 1024, seed=21)
+    c1 = ops.w8a8_block_fp8_gemm(cuda(aq), cuda(a_s), cuda(bq), cuda(bs), torch.float32)
+    c2 = ops.w8a8_block_fp8_gemm(cuda(aq), cuda(a_s), cuda(bq), cuda(bs), torch.float32)
+    c3 = ops.w8a8_block_fp8_gemm(cuda(aq), cuda(a_s * 2), cuda(bq), cuda(bs), torch.float32)
+    assert torch.equal(c1, c2) and torch.equal(c3, c1 * 2)
+
+
+@pytest.mark.parametrize("m,n,k", [(4096, 4096, 4096), (16, 18432, 7168), (4096, 18432, 7168)])
+def test_large_shapes_sampled(ops, m, n, k):
+    """Benchmark-sized shapes: sampled rows x columns against the fp64 golden, whole-matrix
+    agreement between the two tile configurations."""
+    from inference_b200 import synth
+    x = synth.activations(m, k, seed=1)
+    aq, a_s = ops.quant_fp8_per_token_group(x)
+    bq, bs = synth.quantised_weights(n, k, seed=1)
+    ops.set_option("gemm_block_n", 128)
+    c128 = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, torch.bfloat16)
+    ops.set_option("gemm_block_n", 256)
+    c256 = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, torch.bfloat16)
+    assert ops.device_status()[0] == 0
+    assert torch.equal(c128, c256)
+    rng = np.random.default_rng(m + n)
+    rows = np.sort(rng.choice(m, min(m, 24), replace=False))
+    cols = np.sort(rng.choice(n, 512, replace=False))
+    want = oracle.w8a8_block_fp8_gemm(aq.cpu().numpy(), a_s.cpu().numpy(), bq.cpu().numpy(),
+                                      bs.cpu().numpy(), rows=rows, cols=cols, threads=8)
+    got = c256[torch.from_numpy(rows).cuda()][:, torch.from_numpy(cols).cuda()].float().cpu().numpy()
+    check(got, want, torch.bfloat16)
+    ops.set_option("gemm_block_n", 0)

@@ -1,0 +1,196 @@
+"""CPU checks of the oracle: against the format definition, against the golden vectors
+generated from the reference, and against the reference's compiled CPU code when present."""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from conftest import GOLDEN, config1_inputs
+
+needs_ref = pytest.mark.skipif(not oracle.have_reference(), reason="oracle/_ref not built")
+
+
+def spec_grid():
+    """E4M3 values enumerated from the format definition (as tests/test_fp8.cpp:18-33 does)."""
+    g = np.zeros(256, dtype=np.float64)
+    for b in range(256):
+        e, m = (b >> 3) & 15, b & 7
+        if e == 15 and m == 7:
+            v = np.nan
+        elif e == 0:
+            v = m * 2.0 ** -9
+        else:
+            v = (1 + m / 8) * 2.0 ** (e - 7)
+        g[b] = -v if b & 0x80 else v
+    return g
+
+
+def nearest_code(a: float, grid) -> int:
+    """Nearest grid point, ties to the even code, saturating at 448 (tests/test_fp8.cpp:35-50)."""
+    neg = np.signbit(a)
+    a = abs(a)
+    if a >= 448.0:
+        return 0xFE if neg else 0x7E
+    d = np.abs(grid[:0x7F] - a)
+    best = int(np.argmin(d))
+    ties = np.flatnonzero(d == d[best])
+    if len(ties) > 1:
+        best = int([t for t in ties if t % 2 == 0][0])
+    return best | (0x80 if neg else 0)
+
+
+def test_decode_all_256_against_format_definition():
+    want = spec_grid()
+    got = oracle.e4m3_decode(np.arange(256, dtype=np.uint8)).astype(np.float64)
+    nan = np.isnan(want)
+    assert np.array_equal(np.isnan(got), nan)
+    assert np.array_equal(got[~nan], want[~nan])
+    assert np.array_equal(np.signbit(got[~nan]), np.signbit(want[~nan]))
+
+
+def test_encode_against_nearest_grid_point():
+    grid = spec_grid()
+    rng = np.random.default_rng(3)
+    mags = 10.0 ** rng.uniform(-9, 3, size=20000)
+    f = (mags * rng.choice([-1.0, 1.0], size=mags.size)).astype(np.float32)
+    pos = grid[:0x7F]
+    mids = (pos[:-1] + pos[1:]) / 2
+    f = np.concatenate([f, pos.astype(np.float32), mids.astype(np.float32),
+                        -pos.astype(np.float32), -mids.astype(np.float32),
+                        np.array([0.0, -0.0, 1e-45, -1e-45, 1e38, -1e38, np.inf, -np.inf, 464.0, 463.99],
+                                 dtype=np.float32)])
+    got = oracle.e4m3_encode(f)
+    want = np.array([nearest_code(float(v), grid) for v in f], dtype=np.uint8)
+    assert np.array_equal(got, want)
+
+
+def test_round_trip_relative_error():
+    # tests/test_fp8.cpp:108-118: |decode(encode(x)) - x| <= 2^-4 |x|; the bound holds on the
+    # normal range [2^-6, 448) (the reference samples [0.01, 400], whose first 0.0056 is denormal)
+    x = np.random.default_rng(5).uniform(2.0 ** -6, 400, 20000).astype(np.float32)
+    back = oracle.e4m3_decode(oracle.e4m3_encode(x))
+    assert np.all(np.abs(back - x) <= x / 16)
+
+
+def test_codec_golden():
+    g = np.load(os.path.join(GOLDEN, "codec_golden.npz"))
+    assert np.array_equal(oracle.e4m3_decode(np.arange(256, dtype=np.uint8)).view(np.uint32),
+                          g["decode_all"].view(np.uint32))
+    assert np.array_equal(oracle.e4m3_encode(g["encode_in"]), g["encode_out"])
+
+
+def test_bf16_round_to_nearest_even():
+    f = np.array([1.0, 1.00390625, 1.01171875, -1.00390625, 3.3895314e38, 1e-40, 0.0, -0.0], np.float32)
+    # 1 + 2^-8 is a tie -> even (1.0); 1 + 3*2^-8 is a tie -> even (1 + 2^-6)
+    bits = oracle.bf16_narrow(f)
+    assert bits[0] == 0x3F80 and bits[1] == 0x3F80 and bits[2] == 0x3F82 and bits[3] == 0xBF80
+    assert np.array_equal(oracle.bf16_widen(bits)[[0, 6]], np.array([1.0, 0.0], np.float32))
+
+
+def test_quant_golden_bf16_fp32_and_gs64():
+    g = np.load(os.path.join(GOLDEN, "quant_golden.npz"))
+    x = oracle.bf16_widen(g["x_bf16_bits"])
+    q, s = oracle.quant_fp8_per_token_group(x, 128)
+    assert np.array_equal(q, g["q"]) and np.array_equal(s.view(np.uint32), g["scales"].view(np.uint32))
+    q, s = oracle.quant_fp8_per_token_group(x, 64)
+    assert np.array_equal(q, g["q_gs64"]) and np.array_equal(s.view(np.uint32), g["scales_gs64"].view(np.uint32))
+    q, s = oracle.quant_fp8_per_token_group(g["x_f32"], 128)
+    assert np.array_equal(q, g["q_f32"]) and np.array_equal(s.view(np.uint32), g["scales_f32"].view(np.uint32))
+    d = oracle.dequant_fp8_per_token_group(g["q"], g["scales"], 128)
+    assert np.array_equal(d.view(np.uint32), g["dequant"].view(np.uint32))
+
+
+def test_quant_zero_group_and_error_bound():
+    # tests/test_quant.cpp:15-42
+    x = np.random.default_rng(1).standard_normal((64, 768)).astype(np.float32)
+    q, s = oracle.quant_fp8_per_token_group(x, 128)
+    dq = oracle.dequant_fp8_per_token_group(q, s, 128)
+    tol = np.maximum(np.abs(x) / 16, np.repeat(s, 128, axis=1) * 1.5e-3) + 1e-30
+    assert np.all(np.abs(dq - x) <= tol)
+    q, s = oracle.quant_fp8_per_token_group(np.zeros((1, 768), np.float32), 128)
+    assert np.all(s == 1.0) and not q.any()
+
+
+def test_quant_rejects_what_the_reference_ignores():
+    with pytest.raises(ValueError):
+        oracle.quant_fp8_per_token_group(np.zeros((2, 100), np.float32), 128)
+
+
+def test_gemm_small_golden():
+    g = np.load(os.path.join(GOLDEN, "gemm_small_golden.npz"))
+    c = oracle.w8a8_block_fp8_gemm(g["aq"], g["a_scales"], g["bq"], g["b_scales"])
+    assert np.array_equal(c.view(np.uint32), g["c"].view(np.uint32))
+    sub = oracle.w8a8_block_fp8_gemm(g["aq"], g["a_scales"], g["bq"], g["b_scales"], rows=[0, 39],
+                                     cols=[0, 127, 128, 199])
+    assert np.array_equal(sub, g["c"][[0, 39]][:, [0, 127, 128, 199]])
+
+
+def test_config1_golden_digests():
+    with open(os.path.join(GOLDEN, "config1_golden.json")) as f:
+        rec = json.load(f)
+    sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+    a_bits, w_bits = config1_inputs()
+    if sha(a_bits) != rec["sha256"]["a_bf16_bits"] or sha(w_bits) != rec["sha256"]["w_bf16_bits"]:
+        pytest.skip("numpy's generator stream differs from the one the fixture was made with")
+    aq, a_s = oracle.quant_fp8_per_token_group(oracle.bf16_widen(a_bits), 128)
+    bq, bs = oracle.block_quant_weights(oracle.bf16_widen(w_bits))
+    assert sha(aq) == rec["sha256"]["a_q"] and sha(a_s) == rec["sha256"]["a_scales"]
+    assert sha(bq) == rec["sha256"]["b_q"] and sha(bs) == rec["sha256"]["b_scales"]
+    c = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs, threads=4)
+    assert sha(c) == rec["sha256"]["c_f32"]
+    assert np.array_equal(c[:, :8], np.array(rec["c_first8cols"], dtype=np.float32))
+
+
+def test_gemm_plausible_magnitude():
+    # tests/test_gemm.cpp:52-60: N(0,1) x N(0,1) at 128^3 -> 1 < max|C| < 1e3
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((128, 128)).astype(np.float32)
+    b = rng.standard_normal((128, 128)).astype(np.float32)
+    aq, a_s = oracle.quant_fp8_per_token_group(a)
+    bq, bs = oracle.block_quant_weights(b)
+    c = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs)
+    assert 1.0 < np.abs(c).max() < 1e3
+    # and it is the dequantised product up to fp32 rounding
+    ref = oracle.dequant_fp8_per_token_group(aq, a_s).astype(np.float64) @ \
+        (oracle.e4m3_decode(bq).astype(np.float64) * bs[0, 0]).T
+    assert np.allclose(c, ref, rtol=1e-5, atol=1e-4)
+
+
+def test_topk_softmax_properties():
+    lg = np.random.default_rng(2).standard_normal((100, 256)).astype(np.float32)
+    ids, w = oracle.topk_softmax(lg, 8, True)
+    assert np.allclose(w.sum(axis=1), 1.0, atol=1e-5)
+    assert np.array_equal(ids[:, 0], lg.argmax(axis=1))
+    assert all(len(set(r)) == 8 for r in ids)
+
+
+# ------------------------------------------------------------------ against the reference itself
+@needs_ref
+def test_encoder_identical_to_reference_on_all_2_32_inputs():
+    assert oracle.reference.encode_mismatches_vs_oracle() == 0
+
+
+@needs_ref
+def test_operators_identical_to_reference():
+    R = oracle.reference
+    rng = np.random.default_rng(9)
+    x = oracle.bf16_widen(oracle.bf16_narrow((rng.standard_normal((96, 1024)) * rng.choice([1, 20], (1, 1024))).astype(np.float32)))
+    q0, s0 = oracle.quant_fp8_per_token_group(x)
+    q1, s1 = R.quant_fp8_per_token_group(x)
+    assert np.array_equal(q0, q1) and np.array_equal(s0.view(np.uint32), s1.view(np.uint32))
+    w = (0.02 * rng.standard_normal((200, 1024))).astype(np.float32)
+    bq, bs = oracle.block_quant_weights(w)
+    c0 = oracle.w8a8_block_fp8_gemm(q0, s0, bq, bs, threads=4)
+    c1 = R.w8a8_block_fp8_gemm(q0, s0, bq, bs, threads=4)
+    assert np.array_equal(c0.view(np.uint32), c1.view(np.uint32))
+    d0 = oracle.dequant_fp8_per_token_group(q0, s0)
+    d1 = R.dequant_fp8_per_token_group(q0, s0)
+    assert np.array_equal(d0.view(np.uint32), d1.view(np.uint32))
+    lg = rng.standard_normal((64, 256)).astype(np.float32)
+    i0, w0 = oracle.topk_softmax(lg, 8)
+    i1, w1 = R.topk_softmax(lg, 8)
+    assert np.array_equal(i0, i1) and np.array_equal(w0.view(np.uint32), w1.view(np.uint32))
+    assert np.array_equal(oracle.bf16_narrow(x[:4, :64] * 1.001), R.bf16_narrow(x[:4, :64] * 1.001))
