@@ -302,6 +302,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           ok = false;
           break;
         }
+        __syncwarp();
         tc_fence_after_sync();
         const uint32_t taddr = lane_base + buf * BN + half * C::kCols;
         uint32_t v0[32], v1[32];
