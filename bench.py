@@ -1,0 +1,392 @@
+#!/usr/bin/env python
+"""Benchmark of the blockwise-FP8 W8A8 path: quant_fp8_per_token_group -> w8a8_block_fp8_gemm.
+
+    python bench.py --gpus N --steps K --warmup W            # this library, N ranks (torchrun for N>1)
+    python bench.py --impl reference --gpus N ...            # the reference's CPU code on the host cores
+
+Workload (the N-sharded configuration): A bf16 [16384, 7168] replicated, W E4M3 [73728, 7168]
+with 128x128 block scales, column-parallel over the ranks (each rank owns N/G weight rows and
+their scales), C bf16 [16384, N/G] per rank.  One step = quantise A, then the GEMM.  The total
+problem is fixed while G grows ("strong" scaling); no data-path collective is involved unless
+--gather is given, which adds an NCCL all-gather of C and reports it separately.
+
+Prints ONE JSON line on stdout (rank 0).  Synthetic seeded inputs; see inference_b200/synth.py.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "block-FP8 GEMM TFLOPS (quant incl.) & % of B200 FP8 peak / HBM BW, 1-8 GPU"
+M_FULL, N_FULL, K_FULL = 16384, 73728, 7168
+NOMINAL_FP8_TFLOPS = 4500.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=M_FULL)
+    ap.add_argument("--n", type=int, default=N_FULL)
+    ap.add_argument("--k", type=int, default=K_FULL)
+    ap.add_argument("--gather", action="store_true", help="also time an NCCL all-gather of C")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU-baseline sample budget")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p["bf16_tflops_sustained"]), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+                "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with NVML while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self.error = None
+
+    def _run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = int(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            names = {
+                getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+                getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+                getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake",
+            }
+            while not self._stop.is_set():
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                    for bit, name in names.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+                time.sleep(self.period)
+        except Exception as e:  # NVML missing: report it, do not guess
+            self.error = repr(e)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=2)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                    "error": self.error}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+# ----------------------------------------------------------------------------- CPU arms
+class CpuSample:
+    """A bounded sample of the workload for the reference's CPU path: quantise `rows`
+    activation rows, then the GEMM against `cols` weight rows (inputs prepared once, untimed)."""
+
+    def __init__(self, rows: int, cols: int, k: int, seed: int = 0):
+        import numpy as np
+        import oracle
+        self.oracle = oracle
+        rng = np.random.default_rng(seed)
+        a = rng.standard_normal((rows, k)).astype(np.float32)
+        a[:, rng.choice(k, max(1, k // 100), replace=False)] *= 20.0
+        self.a = oracle.bf16_widen(oracle.bf16_narrow(a))
+        w = (0.02 * rng.standard_normal((cols, k))).astype(np.float32)
+        self.bq, self.bs = oracle.block_quant_weights(w)
+        self.rows, self.cols, self.k = rows, cols, k
+        self.flops = 2.0 * rows * cols * k
+        self.kind = "reference" if oracle.have_reference() else "port"
+
+    def run(self, threads: int) -> float:
+        """Seconds for one pass (quant + GEMM) on `threads` host threads."""
+        o = self.oracle
+        t0 = time.perf_counter()
+        if self.kind == "reference":
+            aq, a_s = o.reference.quant_fp8_per_token_group(self.a, 128, threads=threads)
+            o.reference.w8a8_block_fp8_gemm(aq, a_s, self.bq, self.bs, threads=threads)
+        else:
+            aq, a_s = o.quant_fp8_per_token_group(self.a, 128)
+            o.w8a8_block_fp8_gemm(aq, a_s, self.bq, self.bs, threads=threads)
+        return time.perf_counter() - t0
+
+    def describe(self) -> str:
+        return f"{self.rows} activation rows x {self.cols} weight rows x K={self.k} (quant + GEMM)"
+
+
+def sized_cpu_sample(k: int, threads: int, budget_s: float) -> CpuSample:
+    """A sample costing about budget_s on this host: probe the rate, then scale the rows."""
+    probe = CpuSample(max(threads, 8), 256, k)
+    rate = probe.flops / max(probe.run(threads), 1e-6)
+    cols = 2048
+    rows = int(rate * budget_s / (2.0 * cols * k))
+    rows = max(threads, (rows // threads) * threads)
+    return CpuSample(rows, cols, k)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    k = args.k
+    per_step = max(0.5, min(8.0, 120.0 / (args.steps + args.warmup)))
+    smp = sized_cpu_sample(k, threads, per_step)
+    for _ in range(args.warmup):
+        smp.run(threads)
+    t_total = sum(smp.run(threads) for _ in range(args.steps))
+    flops_total = smp.flops * args.steps
+    kind, used = smp.kind, min(threads, smp.rows)
+    val = flops_total / t_total / 1e12
+    sample = smp.describe() + " per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_total / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3",
+        "data": "synthetic",
+        "config": {"workload": f"N-sharded W8A8 block-FP8 GEMM M={args.m} N={args.n} K={k}, quant incl.",
+                   "note": "CPU arm: each step is a bounded sample of the workload"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": used, "kind": kind, "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from inference_b200 import ops, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    assert ops.has_cuda() and ops.device_sm_version(local) == 100, "needs B200 (sm_100); no fallback"
+
+    m, n, k = args.m, args.n, args.k
+    assert n % (128 * world) == 0, "N must split into 128-row blocks per rank"
+    n_loc = n // world
+    dev = torch.device("cuda", local)
+
+    # inputs: A replicated (same seed on every rank), this rank's weight shard
+    x = synth.activations(m, k, seed=0, outliers=True, device=dev)
+    bq, bs = synth.quantised_weights(n_loc, k, seed=1 + rank, device=dev)
+    aq = torch.empty((m, k), dtype=torch.uint8, device=dev)
+    a_s = torch.empty((m, k // 128), dtype=torch.float32, device=dev)
+    c = torch.empty((m, n_loc), dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        ops.quant_fp8_per_token_group(x, 128, aq, a_s)
+        ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, out=c)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sync_all()
+
+    # ---- device-timed region: exactly `steps` steps, per-kernel events inside
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        e0.record(stream)
+        for i in range(args.steps):
+            ev[i][0].record(stream)
+            ops.quant_fp8_per_token_group(x, 128, aq, a_s)
+            ev[i][1].record(stream)
+            ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, out=c)
+            ev[i][2].record(stream)
+        e1.record(stream)
+        torch.cuda.synchronize()
+    t_region = e0.elapsed_time(e1) * 1e-3
+    t_quant = sum(e[0].elapsed_time(e[1]) for e in ev) * 1e-3 / args.steps
+    t_gemm = sum(e[1].elapsed_time(e[2]) for e in ev) * 1e-3 / args.steps
+    status = ops.device_status()
+    assert status[0] == 0, f"device-side wait ran out: {status}"
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    t_region = max_over_ranks(t_region)
+    t_gemm_max = max_over_ranks(t_gemm)
+    t_quant_max = max_over_ranks(t_quant)
+    flops_total = 2.0 * m * n * k
+    t_step = t_region / args.steps
+    value = flops_total / t_step / 1e12
+
+    # ---- optional all-gather of C (reported separately)
+    gather = None
+    if args.gather and world > 1:
+        c_all = torch.empty((world, m, n_loc), dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            dist.all_gather_into_tensor(c_all, c)
+        sync_all()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        for _ in range(args.steps):
+            step()
+            dist.all_gather_into_tensor(c_all, c)
+        g1.record(stream)
+        torch.cuda.synchronize()
+        tg = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
+        gather = {"ms_per_step_with_gather": tg * 1e3, "value_with_gather": flops_total / tg / 1e12,
+                  "bytes_received_per_rank": 2 * m * n_loc * (world - 1), "layout": "[G][M][N/G] rank-blocked"}
+        del c_all
+
+    # ---- end-to-end through the public API with host buffers
+    e2e = None
+    if not args.no_e2e:
+        x_host = x.cpu().pin_memory()
+        c_host = torch.empty((m, n_loc), dtype=torch.bfloat16).pin_memory()
+        x_dev = torch.empty_like(x)
+
+        def e2e_step():
+            x_dev.copy_(x_host, non_blocking=True)
+            ops.quant_fp8_per_token_group(x_dev, 128, aq, a_s)
+            ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, out=c)
+            c_host.copy_(c, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        sync_all()
+        h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_e2e = max(3, min(args.steps, 10))
+        h0.record(stream)
+        for _ in range(n_e2e):
+            e2e_step()
+        h1.record(stream)
+        torch.cuda.synchronize()
+        te = max_over_ranks(h0.elapsed_time(h1) * 1e-3 / n_e2e)
+        e2e = {"value": flops_total / te / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2,
+               "d2h_bytes_per_step": c_host.numel() * 2, "ms_per_step": te * 1e3, "steps": n_e2e}
+        del x_host, c_host, x_dev
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    gemm_flops = 2.0 * m * n_loc * k
+    gemm_bytes = m * k + n_loc * k + 4 * m * (k // 128) + 4 * (n_loc // 128) * (k // 128) + 2 * m * n_loc
+    quant_bytes = 3 * m * k + 4 * m * (k // 128)
+    achieved = gemm_flops / t_gemm_max / 1e12
+    roofline = {
+        "bound": "tensor", "kernel": "w8a8_gemm_kernel", "achieved": achieved, "peak": fp8_peak,
+        "unit": "TFLOP/s", "frac": achieved / fp8_peak,
+        "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} peaks (no measured FP8 figure)",
+        "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
+        "traffic": None,
+        "avg_launch_ms": t_gemm_max * 1e3,
+        "quant_kernel": {"bound": "hbm", "achieved": quant_bytes / t_quant_max / 1e9, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": quant_bytes / t_quant_max / 1e9 / peaks["hbm_gbs"],
+                         "avg_launch_ms": t_quant_max * 1e3},
+        "gemm_algorithmic_bytes": gemm_bytes,
+    }
+    traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(traffic_path) as f:
+            tr = json.load(f)
+        # bytes of DRAM traffic per launch, captured once under ncu on a smaller case and scaled
+        # by flops (see profiles/); null when no capture is on file
+        roofline["traffic"] = tr["gemm_dram_bytes_per_flop"] * gemm_flops if tr.get("gemm_dram_bytes_per_flop") else None
+    except Exception:
+        pass
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": t_step * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": f"N-sharded W8A8 block-FP8 GEMM M={m} N={n} K={k}, quant incl.",
+                   "m": m, "n": n, "k": k, "n_per_gpu": n_loc, "parallelism": f"column-parallel x{world}",
+                   "out": "bf16", "l2": "inputs larger than L2 (no flush needed)",
+                   "a": "bf16 N(0,1), 1% outlier channels x20", "w": "bf16 N(0,0.02) block-quantised 128x128"},
+        "roofline": roofline, "gpu_launches": 2 * args.steps,
+        "clocks": clocks.summary(),
+        "frac_of_nominal_fp8_peak": value / (NOMINAL_FP8_TFLOPS * world),
+    }
+    if e2e:
+        line["e2e"] = e2e
+    if gather:
+        line["gather"] = gather
+    if world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        smp = sized_cpu_sample(k, threads, args.cpu_seconds)
+        dt = smp.run(threads)
+        line["cpu_baseline"] = {"value": smp.flops / dt / 1e12, "unit": "TFLOP/s",
+                                "cores": min(threads, smp.rows), "kind": smp.kind,
+                                "sample": smp.describe() + f", {dt:.1f} s"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -236,6 +236,10 @@ int inferop_set_option(const char* key, int64_t value) {
   } else if (!strcmp(key, "gemm_ctas")) {
     if (value < 0 || value > 1024) return INFEROP_ERR_SHAPE;
     o.gemm_ctas = static_cast<int>(value);
+  } else if (!strcmp(key, "gemm_debug")) {
+    o.gemm_debug = static_cast<int>(value);
+  } else if (!strcmp(key, "gemm_trace_ptr")) {
+    o.gemm_trace_ptr = value;
   } else {
     return INFEROP_ERR_SHAPE;
   }

@@ -15,9 +15,10 @@
 // CTA layout (384 threads, one CTA per SM, persistent over output tiles):
 //   warp 0      TMA producer: A tile [128 x 128 B] and B tile [BN x 128 B] per
 //               K block into a kStages-deep ring (128-byte swizzle, K-major)
-//   warp 1      MMA issuer: 4 x tcgen05.mma (M=128, N=BN, K=32) per K block into
-//               TMEM accumulator buffer (kb & 1); commits free the smem stage
-//               and publish the TMEM buffer
+//   warps 1, 3  MMA issuers (one thread each): 4 x tcgen05.mma (M=128, N=BN, K=32)
+//               per K block into TMEM accumulator buffer (kb & 1); warp 1 issues
+//               the even K blocks, warp 3 the odd ones; commits free the smem
+//               stage and publish the TMEM buffer
 //   warp 2      allocates / frees tensor memory (2 x BN columns)
 //   warps 4-11  promotion + epilogue.  Warp w reads TMEM lane quarter w % 4
 //               (its 32 rows) and column half (w - 4) / 4 of the tile; each
@@ -73,8 +74,12 @@ struct GemmParams {
   int nb;        // ceil(N / 128): rows of b_scales
   int tiles_m, tiles_n, num_tiles;
   int tma_store; // 1: epilogue goes through shared memory + TMA store
+  int debug;     // timing experiments only (results are wrong when non-zero):
+                 // 1 = promotion skips TMEM loads and FMAs, 2 = skips FMAs only, 4 = no TMA loads
   DeviceStatus* status;
+  long long* trace;  // optional: clock64 stamps of CTA 0's first kTraceIters K blocks (8 per block)
 };
+constexpr uint32_t kTraceIters = 512;
 
 // wait sites reported in DeviceStatus::code
 enum : uint32_t {
@@ -205,9 +210,13 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             break;
           }
           uint8_t* sa = smem + stage * C::kStageBytes;
-          mbar_arrive_expect_tx(&full[stage], C::kStageBytes);
-          tma_load_2d(sa, &map_a, &full[stage], kb * BK, tm * BM);
-          tma_load_2d(sa + C::kBytesA, &map_b, &full[stage], kb * BK, tn * BN);
+          if (p.debug & 4) {
+            mbar_arrive(&full[stage]);
+          } else {
+            mbar_arrive_expect_tx(&full[stage], C::kStageBytes);
+            tma_load_2d(sa, &map_a, &full[stage], kb * BK, tm * BM);
+            tma_load_2d(sa + C::kBytesA, &map_b, &full[stage], kb * BK, tn * BN);
+          }
           armed |= 1u << stage;
           armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
           if (++stage == C::kStages) {
@@ -230,40 +239,40 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
       }
-    } else if (warp == 1 && lane == 0) {
-      // ------------------------------ MMA issuer --------------------------
+    } else if ((warp == 1 || warp == 3) && lane == 0) {
+      // ------------------------------ MMA issuers -------------------------
+      // Two issuing threads: warp 1 takes the even K blocks of this CTA's work
+      // list (TMEM buffer 0), warp 3 the odd ones (buffer 1).  K blocks are
+      // independent accumulations into different buffers, so the two streams
+      // need no ordering between them, and the per-block cost of waiting,
+      // building descriptors and issuing is spread over two threads.
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN);
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t kiter = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
-        for (int kb = 0; kb < p.kb; ++kb, ++kiter) {
-          const uint32_t buf = kiter & 1u;
-          const uint32_t use = kiter >> 1;
-          if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status,
-                         kSiteMmaTmemEmpty) ||
-              !mbar_wait(&full[stage], phase, abort_flag, p.status, kSiteMmaFull)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + stage * C::kStageBytes);
-          const uint64_t da = umma_desc_k_sw128(a_addr);
-          const uint64_t db = umma_desc_k_sw128(a_addr + C::kBytesA);
-          const uint32_t d_tmem = tmem_base + buf * BN;
+      const uint32_t me = (warp == 3) ? 1u : 0u;
+      const uint32_t my_tiles = (p.num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+      const uint32_t total = my_tiles * static_cast<uint32_t>(p.kb);
+      const uint32_t d_tmem = tmem_base + me * BN;
+      for (uint32_t it = me; it < total; it += 2) {
+        const uint32_t stage = it % C::kStages;
+        const uint32_t phase = (it / C::kStages) & 1u;
+        const uint32_t use = it >> 1;
+        const bool tr = p.trace && blockIdx.x == 0 && it < kTraceIters;
+        if (tr) p.trace[it * 16 + 0] = clock64();
+        if (!mbar_wait(&tmem_empty[me], (use & 1u) ^ 1u, abort_flag, p.status, kSiteMmaTmemEmpty)) break;
+        if (tr) p.trace[it * 16 + 1] = clock64();
+        if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kSiteMmaFull)) break;
+        if (tr) p.trace[it * 16 + 2] = clock64();
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + stage * C::kStageBytes);
+        const uint64_t da = umma_desc_k_sw128(a_addr);
+        const uint64_t db = umma_desc_k_sw128(a_addr + C::kBytesA);
 #pragma unroll
-          for (int k4 = 0; k4 < BK / 32; ++k4) {
-            // 32 E4M3 elements = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
-            umma_f8_ss(d_tmem, da + 2u * k4, db + 2u * k4, idesc, k4 > 0 ? 1u : 0u);
-          }
-          umma_commit(&empty[stage]);
-          umma_commit(&tmem_full[buf]);
-          if (++stage == C::kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+        for (int k4 = 0; k4 < BK / 32; ++k4) {
+          // 32 E4M3 elements = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
+          umma_f8_ss(d_tmem, da + 2u * k4, db + 2u * k4, idesc, k4 > 0 ? 1u : 0u);
         }
+        umma_commit(&empty[stage]);
+        umma_commit(&tmem_full[me]);
+        if (tr) p.trace[it * 16 + 3] = clock64();
       }
     }
   } else {
@@ -297,14 +306,27 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const float s = s_next;
         if (kb + 1 < p.kb && have_scales) s_next = __ldg(sa_ptr + kb + 1) * __ldg(sb_ptr + kb + 1);
         const uint32_t buf = kiter & 1u;
-        if (!mbar_wait(&tmem_full[buf], (kiter >> 1) & 1u, abort_flag, p.status,
-                       kSitePromoTmemFull)) {
+        // one lane polls (256 polling threads would keep the shared-memory pipe busy that
+        // the tensor core reads its operands through); the result is broadcast by the vote
+        uint32_t got = 1u;
+        if (lane == 0 || (p.debug & 16)) {
+          got = mbar_wait(&tmem_full[buf], (kiter >> 1) & 1u, abort_flag, p.status,
+                          kSitePromoTmemFull) ? 1u : 0u;
+        }
+        if (!__all_sync(0xFFFFFFFFu, got != 0u)) {
           ok = false;
           break;
         }
-        __syncwarp();
+        const bool tr = p.trace && blockIdx.x == 0 && kiter < kTraceIters && lane == 0;
+        if (tr && pw == 0) p.trace[kiter * 16 + 4] = clock64();
         tc_fence_after_sync();
         const uint32_t taddr = lane_base + buf * BN + half * C::kCols;
+        if (p.debug & 1) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          continue;
+        }
         uint32_t v0[32], v1[32];
         tmem_ld_32x32(taddr, v0);
         tmem_ld_32x32(taddr + 32, v1);
@@ -314,20 +336,24 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-          promote32(acc, v0, s);
-          promote32(acc + 16, v1, s);
+          if (tr) p.trace[kiter * 16 + 8 + pw] = clock64();
+          if (!(p.debug & 2)) promote32(acc, v0, s);
+          if (!(p.debug & 2)) promote32(acc + 16, v1, s);
+          if (tr && pw == 0) p.trace[kiter * 16 + 6] = clock64();
         } else {
-          promote32(acc, v0, s);
+          if (!(p.debug & 2)) promote32(acc, v0, s);
           tmem_ld_32x32(taddr + 64, v0);
-          promote32(acc + 16, v1, s);
+          if (!(p.debug & 2)) promote32(acc + 16, v1, s);
           tmem_ld_32x32(taddr + 96, v1);
           tmem_ld_wait_pin(v0);
           tmem_ld_wait_pin(v1);
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-          promote32(acc + 32, v0, s);
-          promote32(acc + 48, v1, s);
+          if (tr) p.trace[kiter * 16 + 8 + pw] = clock64();
+          if (!(p.debug & 2)) promote32(acc + 32, v0, s);
+          if (!(p.debug & 2)) promote32(acc + 48, v1, s);
+          if (tr && pw == 0) p.trace[kiter * 16 + 6] = clock64();
         }
       }
       if (!ok) break;
@@ -440,6 +466,8 @@ int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, 
   if (tiles > 0x7FFFFFFF) return INFEROP_ERR_LIMIT;
   p.num_tiles = static_cast<int>(tiles);
   p.tma_store = tma_store ? 1 : 0;
+  p.debug = opt.gemm_debug;
+  p.trace = reinterpret_cast<long long*>(opt.gemm_trace_ptr);
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;

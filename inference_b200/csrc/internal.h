@@ -28,6 +28,8 @@ struct Options {
   int gemm_block_n = 0;    // 0 auto, 128, 256
   int gemm_tma_store = -1; // -1 auto, 0 off, 1 on
   int gemm_ctas = 0;       // 0 = one per SM
+  int gemm_debug = 0;      // timing experiments; non-zero gives wrong results
+  int64_t gemm_trace_ptr = 0;  // device buffer of 512*8 int64 for clock stamps, 0 = off
 };
 Options& options();
 

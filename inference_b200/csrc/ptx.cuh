@@ -22,6 +22,7 @@ struct DeviceStatus {
 };
 
 constexpr long long kWaitBudgetCycles = 1LL << 31;  // about a second at the SM's top clock
+constexpr unsigned int kProbeNs = 2000;             // longest time one mbarrier probe may park a thread
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -58,11 +59,14 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                "r"(bytes)
                : "memory");
 }
+// One probe of the barrier.  The hardware may park the thread until the phase
+// completes or a time limit passes; the limit is given explicitly (in ns) so
+// that the bounded wait below can keep its own clock.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
@@ -80,17 +84,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++polls & 63u) == 0u) {
-      if (*abort_flag != 0u) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
-        *abort_flag = 1u;
-        if (atomicCAS(&status->code, 0u, site) == 0u) {
-          status->block = blockIdx.x;
-          status->aux0 = parity;
-          status->aux1 = smem_u32(bar);
-        }
-        return false;
+    // each probe parks the thread for at most kProbeNs, so the clock needs reading only now and then
+    if ((++polls & 15u) != 0u) continue;
+    if (*abort_flag != 0u) return false;
+    if (clock64() - t0 > kWaitBudgetCycles) {
+      *abort_flag = 1u;
+      if (atomicCAS(&status->code, 0u, site) == 0u) {
+        status->block = blockIdx.x;
+        status->aux0 = parity;
+        status->aux1 = smem_u32(bar);
       }
+      return false;
     }
   }
 }
