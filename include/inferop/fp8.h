@@ -20,7 +20,7 @@
 namespace inferop {
 namespace fp8 {
 
-INFEROP_HD constexpr float kE4M3Max = 448.0f;
+constexpr float kE4M3Max = 448.0f;
 
 namespace detail {
 INFEROP_HD inline uint32_t f32_to_u32(float f) {

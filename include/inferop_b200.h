@@ -96,9 +96,18 @@ INFEROP_API int inferop_device_status(uint32_t* out4, int reset);
  * quantiser). */
 INFEROP_API int inferop_selftest_e4m3_cvt(uint64_t lo, uint64_t hi, uint64_t* out2);
 
+/* Self-test of the quantiser's reciprocal-based division for 16-bit inputs (dt = 1 fp16,
+ * 2 bf16): every finite group maximum on the fast path x every element value of that type
+ * with |x| <= maximum, E4M3 byte through the reciprocal against the byte through IEEE
+ * division (the oracle's x / scale, reference/reference.cpp:76).  Synchronous.
+ * out3 (host, 3 x uint64): [0] mismatching pairs (must be 0), [1] pairs checked, [2] one
+ * mismatching pair as (maximum bits << 32 | element bits). */
+INFEROP_API int inferop_selftest_quant_div(int32_t dt, uint64_t* out3);
+
 /* Tuning knobs for experiments and tests (process-wide, not thread-safe).
- * key: "gemm_block_n" (0 = auto, 128, 256), "gemm_tma_store" (-1 auto, 0, 1),
- *      "gemm_ctas" (0 = one per SM).  Returns INFEROP_ERR_SHAPE for an unknown key/value. */
+ * key: "gemm_tma_store" (-1 auto, 0, 1), "gemm_ctas" (0 = one per SM), "gemm_block_n"
+ *      (accepted and ignored: the kernel has one tile shape).  Returns INFEROP_ERR_SHAPE for
+ *      an unknown key/value. */
 INFEROP_API int inferop_set_option(const char* key, int64_t value);
 
 #ifdef __cplusplus

@@ -28,6 +28,7 @@ SIGNATURES = {
                                               _i32, _vp]),
     "inferop_device_status": (C.c_int, [C.POINTER(C.c_uint32), C.c_int]),
     "inferop_selftest_e4m3_cvt": (C.c_int, [_u64, _u64, C.POINTER(_u64)]),
+    "inferop_selftest_quant_div": (C.c_int, [_i32, C.POINTER(_u64)]),
     "inferop_set_option": (C.c_int, [C.c_char_p, _i64]),
 }
 

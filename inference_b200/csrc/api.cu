@@ -224,11 +224,19 @@ int inferop_selftest_e4m3_cvt(uint64_t lo, uint64_t hi, uint64_t* out2) {
   return run_cvt_selftest(lo, hi, out2, ctx->sm_count);
 }
 
+int inferop_selftest_quant_div(int32_t dt, uint64_t* out3) {
+  if (!out3 || (dt != 1 && dt != 2)) return INFEROP_ERR_SHAPE;
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return run_div_selftest(dt == 2 ? 1 : 0, out3, ctx->sm_count);
+}
+
 int inferop_set_option(const char* key, int64_t value) {
   if (!key) return INFEROP_ERR_SHAPE;
   Options& o = options();
   if (!strcmp(key, "gemm_block_n")) {
-    if (value != 0 && value != 128 && value != 256) return INFEROP_ERR_SHAPE;
+    if (value != 0 && value != 128 && value != 256) return INFEROP_ERR_SHAPE;  // kept for callers; one tile shape now
     o.gemm_block_n = static_cast<int>(value);
   } else if (!strcmp(key, "gemm_tma_store")) {
     if (value < -1 || value > 1) return INFEROP_ERR_SHAPE;
@@ -236,10 +244,6 @@ int inferop_set_option(const char* key, int64_t value) {
   } else if (!strcmp(key, "gemm_ctas")) {
     if (value < 0 || value > 1024) return INFEROP_ERR_SHAPE;
     o.gemm_ctas = static_cast<int>(value);
-  } else if (!strcmp(key, "gemm_debug")) {
-    o.gemm_debug = static_cast<int>(value);
-  } else if (!strcmp(key, "gemm_trace_ptr")) {
-    o.gemm_trace_ptr = value;
   } else {
     return INFEROP_ERR_SHAPE;
   }

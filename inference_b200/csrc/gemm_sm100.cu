@@ -12,20 +12,25 @@
 // block on the CUDA cores ("promotion"), so no scale is ever folded into a
 // reduced-precision accumulator.  Output is rounded once (RNE).
 //
+// Tile: 128 rows x 256 columns of C per CTA, K in blocks of 128.  One K block is
+// 4 MMAs (M=128, N=256, K=32) into one of two 256-column accumulator buffers in
+// tensor memory (buffer = K block parity), so the tensor core works on block
+// kb+1 while block kb is being promoted.
+//
 // CTA layout (384 threads, one CTA per SM, persistent over output tiles):
-//   warp 0      TMA producer: A tile [128 x 128 B] and B tile [BN x 128 B] per
-//               K block into a kStages-deep ring (128-byte swizzle, K-major)
-//   warps 1, 3  MMA issuers (one thread each): 4 x tcgen05.mma (M=128, N=BN, K=32)
-//               per K block into TMEM accumulator buffer (kb & 1); warp 1 issues
-//               the even K blocks, warp 3 the odd ones; commits free the smem
-//               stage and publish the TMEM buffer
-//   warp 2      allocates / frees tensor memory (2 x BN columns)
+//   warp 0      allocates / frees tensor memory; one thread is the TMA producer:
+//               A tile [128 x 128 B] and B tile [256 x 128 B] per K block into a
+//               4-deep ring (128-byte swizzle, K-major)
+//   warps 1, 2  MMA issuers: warp 1 the even K blocks of the CTA's work list,
+//               warp 2 the odd ones.  Their instruction streams write different
+//               TMEM buffers and need no ordering between them.
 //   warps 4-11  promotion + epilogue.  Warp w reads TMEM lane quarter w % 4
-//               (its 32 rows) and column half (w - 4) / 4 of the tile; each
-//               thread owns one output row segment of BN/2 columns in registers.
+//               (its 32 rows); warps 4-7 take columns 0-127 (the left
+//               weight-scale block), warps 8-11 columns 128-255.  A thread owns
+//               one output row segment of 128 columns in registers.
 //
 // Shared memory (dynamic, 1024-byte aligned):
-//   [kStages x (A 16 KiB | B BN*128 B)] [2 x 16 KiB output staging] [barriers]
+//   [4 x (A 16 KiB | B 32 KiB)] [2 x 16 KiB output staging] [barriers]
 //
 // HBM traffic per call (algorithmic): M*K + N*K operand bytes, 4*M*K/128 +
 // 4*ceil(N/128)*K/128 scale bytes, M*N*sizeof(out) output bytes; operand
@@ -46,24 +51,22 @@ namespace ib200 {
 namespace {
 
 constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BH = 128;  // columns per half = one weight-scale block = one TMEM slice
 constexpr int BK = 128;
 constexpr int kPromoWarps = 8;
 constexpr int kThreads = 128 + 32 * kPromoWarps;
 constexpr int kGroupM = 16;  // M-tiles per rasterisation band
-
-template <int BN>
-struct Cfg {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kBytesA = BM * BK;
-  static constexpr int kBytesB = BN * BK;
-  static constexpr int kStageBytes = kBytesA + kBytesB;
-  static constexpr int kCols = BN / 2;          // output columns per promotion thread
-  static constexpr int kTmemCols = 2 * BN;      // two accumulator buffers
-  static constexpr int kStoreBufBytes = 128 * 128;  // 128 rows x 64 two-byte columns
-  static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes =
-      kStages * kStageBytes + 2 * kStoreBufBytes + kBarrierBytes + 1024 /* alignment slack */;
-};
+constexpr int kStages = 4;
+constexpr int kBytesA = BM * BK;
+constexpr int kBytesB = BN * BK;
+constexpr int kStageBytes = kBytesA + kBytesB;
+constexpr int kSlices = 2;  // TMEM accumulator buffers, one K block each
+constexpr int kTmemCols = kSlices * BN;
+constexpr int kStoreBufBytes = 128 * 128;  // 128 rows x 64 two-byte columns
+constexpr int kBarrierBytes = 256;
+constexpr int kSmemBytes =
+    kStages * kStageBytes + 2 * kStoreBufBytes + kBarrierBytes + 1024 /* alignment slack */;
 
 struct GemmParams {
   const float* a_scales;
@@ -74,12 +77,8 @@ struct GemmParams {
   int nb;        // ceil(N / 128): rows of b_scales
   int tiles_m, tiles_n, num_tiles;
   int tma_store; // 1: epilogue goes through shared memory + TMA store
-  int debug;     // timing experiments only (results are wrong when non-zero):
-                 // 1 = promotion skips TMEM loads and FMAs, 2 = skips FMAs only, 4 = no TMA loads
   DeviceStatus* status;
-  long long* trace;  // optional: clock64 stamps of CTA 0's first kTraceIters K blocks (8 per block)
 };
-constexpr uint32_t kTraceIters = 512;
 
 // wait sites reported in DeviceStatus::code
 enum : uint32_t {
@@ -149,32 +148,32 @@ __device__ __forceinline__ void promote32(float2* acc, const uint32_t (&v)[32], 
   }
 }
 
-template <int BN, typename OutT>
+template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
-  using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* store_buf = smem + C::kStages * C::kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(store_buf + 2 * C::kStoreBufBytes);
-  uint64_t* full = bars;                     // [kStages]  TMA -> MMA
-  uint64_t* empty = bars + C::kStages;       // [kStages]  MMA -> TMA
-  uint64_t* tmem_full = bars + 2 * C::kStages;       // [2] MMA -> promotion
-  uint64_t* tmem_empty = bars + 2 * C::kStages + 2;  // [2] promotion -> MMA
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+  uint8_t* store_buf = smem + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_buf + 2 * kStoreBufBytes);
+  uint64_t* full = bars;                            // [kStages]  TMA -> MMA
+  uint64_t* empty = bars + kStages;                 // [kStages]  MMA (both issuers) -> TMA
+  uint64_t* tmem_full = bars + 2 * kStages;         // [kSlices]  MMA -> promotion
+  uint64_t* tmem_empty = tmem_full + kSlices;       // [kSlices]  promotion -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + kSlices);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
-  const int warp = threadIdx.x >> 5;
+  // the shuffle tells the compiler that the warp index is uniform across the warp
+  const int warp = __shfl_sync(0xFFFFFFFFu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kSlices; ++b) {
       mbar_init(&tmem_full[b], 1);
       mbar_init(&tmem_empty[b], kPromoWarps);
     }
@@ -184,14 +183,15 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tma_prefetch_desc(&map_b);
     if (p.tma_store) tma_prefetch_desc(&map_c);
   }
-  if (warp == 2) {
-    tmem_alloc(tmem_slot, C::kTmemCols);
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_slot, 0);
+  const uint32_t my_tiles = (p.num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
 
   if (warp < 4) {
     reg_dealloc<56>();
@@ -209,17 +209,13 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             ok = false;
             break;
           }
-          uint8_t* sa = smem + stage * C::kStageBytes;
-          if (p.debug & 4) {
-            mbar_arrive(&full[stage]);
-          } else {
-            mbar_arrive_expect_tx(&full[stage], C::kStageBytes);
-            tma_load_2d(sa, &map_a, &full[stage], kb * BK, tm * BM);
-            tma_load_2d(sa + C::kBytesA, &map_b, &full[stage], kb * BK, tn * BN);
-          }
+          uint8_t* sa = smem + stage * kStageBytes;
+          mbar_arrive_expect_tx(&full[stage], kStageBytes);
+          tma_load_2d(sa, &map_a, &full[stage], kb * BK, tm * BM);
+          tma_load_2d(sa + kBytesA, &map_b, &full[stage], kb * BK, tn * BN);
           armed |= 1u << stage;
           armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
-          if (++stage == C::kStages) {
+          if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -227,11 +223,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
       if (!ok) {
         // wind-down: let the copies this thread started land before the CTA exits
-        for (int s = 0; s < C::kStages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
           if (!(armed & (1u << s))) continue;
           const uint32_t par = (armed_phase >> s) & 1u;
           const long long t0 = clock64();
-          while (!mbar_try_wait(&full[s], par)) {
+          while (!mbar_test_wait(&full[s], par)) {
             if (clock64() - t0 > kWaitBudgetCycles) {
               atomicCAS(&p.status->code, 0u, kSiteProducerDrain);
               break;
@@ -239,40 +235,41 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
       }
-    } else if ((warp == 1 || warp == 3) && lane == 0) {
+    } else if (warp == 1 || warp == 2) {
       // ------------------------------ MMA issuers -------------------------
-      // Two issuing threads: warp 1 takes the even K blocks of this CTA's work
-      // list (TMEM buffer 0), warp 3 the odd ones (buffer 1).  K blocks are
-      // independent accumulations into different buffers, so the two streams
-      // need no ordering between them, and the per-block cost of waiting,
-      // building descriptors and issuing is spread over two threads.
+      // Warp 1 issues the even K blocks of this CTA's work list (TMEM buffer 0), warp 2 the
+      // odd ones (buffer 1); the two streams write different buffers and need no ordering.
+      // Each warp runs its loop with all 32 lanes: warp-uniform control flow keeps the
+      // descriptors in uniform registers, which makes issuing cheap (about 76 cycles per MMA
+      // and 92 per commit, against more than 120 per MMA from divergent single-lane code);
+      // one elected lane issues the tcgen05 instructions.
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN);
-      const uint32_t me = (warp == 3) ? 1u : 0u;
-      const uint32_t my_tiles = (p.num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
       const uint32_t total = my_tiles * static_cast<uint32_t>(p.kb);
-      const uint32_t d_tmem = tmem_base + me * BN;
-      for (uint32_t it = me; it < total; it += 2) {
-        const uint32_t stage = it % C::kStages;
-        const uint32_t phase = (it / C::kStages) & 1u;
+      const uint32_t smem_base = smem_u32(smem);
+      const uint32_t buf = warp - 1;
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (uint32_t it = buf; it < total; it += 2) {
+        const uint32_t stage = it % kStages;
+        const uint32_t phase = (it / kStages) & 1u;
         const uint32_t use = it >> 1;
-        const bool tr = p.trace && blockIdx.x == 0 && it < kTraceIters;
-        if (tr) p.trace[it * 16 + 0] = clock64();
-        if (!mbar_wait(&tmem_empty[me], (use & 1u) ^ 1u, abort_flag, p.status, kSiteMmaTmemEmpty)) break;
-        if (tr) p.trace[it * 16 + 1] = clock64();
+        // operands first (normally long there), then the accumulator buffer (the late one)
         if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kSiteMmaFull)) break;
-        if (tr) p.trace[it * 16 + 2] = clock64();
+        if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, kSiteMmaTmemEmpty)) break;
+        __syncwarp();
         tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(smem + stage * C::kStageBytes);
+        const uint32_t a_addr = smem_base + stage * kStageBytes;
         const uint64_t da = umma_desc_k_sw128(a_addr);
-        const uint64_t db = umma_desc_k_sw128(a_addr + C::kBytesA);
+        const uint64_t db = umma_desc_k_sw128(a_addr + kBytesA);
+        if (elect_one()) {
 #pragma unroll
-        for (int k4 = 0; k4 < BK / 32; ++k4) {
-          // 32 E4M3 elements = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
-          umma_f8_ss(d_tmem, da + 2u * k4, db + 2u * k4, idesc, k4 > 0 ? 1u : 0u);
+          for (int k4 = 0; k4 < BK / 32; ++k4) {
+            // 32 E4M3 elements = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
+            umma_f8_ss(d_tmem, da + 2u * k4, db + 2u * k4, idesc, k4 > 0 ? 1u : 0u);
+          }
+          umma_commit(&tmem_full[buf]);
+          umma_commit(&empty[stage]);
         }
-        umma_commit(&empty[stage]);
-        umma_commit(&tmem_full[me]);
-        if (tr) p.trace[it * 16 + 3] = clock64();
+        __syncwarp();
       }
     }
   } else {
@@ -280,10 +277,10 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // ------------------------------ promotion + epilogue ------------------
     const int pw = warp - 4;
     const int quarter = pw & 3;  // == warp % 4: the TMEM lane quarter this warp may read
-    const int half = pw >> 2;    // which BN/2 column half of the tile
+    const int half = pw >> 2;    // which 128-column half (= weight-scale block) of the tile
     const int row = quarter * 32 + lane;
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    uint8_t* my_buf = store_buf + half * C::kStoreBufBytes;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * BH;
+    uint8_t* my_buf = store_buf + half * kStoreBufBytes;
     const bool issuer = (quarter == 0 && lane == 0);
     uint32_t kiter = 0;
     bool ok = true;
@@ -291,85 +288,60 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       const int gm = tm * BM + row;
-      const int col0 = tn * BN + half * C::kCols;  // first output column of this thread
-      const int nbi = col0 >> 7;
-      const bool have_scales = (gm < p.m) && (nbi < p.nb);
-      const float* sa_ptr = p.a_scales + static_cast<int64_t>(have_scales ? gm : 0) * p.kb;
-      const float* sb_ptr = p.b_scales + static_cast<int64_t>(have_scales ? nbi : 0) * p.kb;
+      const int nbi = tn * 2 + half;
+      const bool have = gm < p.m && nbi < p.nb;
+      const float* sa_ptr = p.a_scales + static_cast<int64_t>(have ? gm : 0) * p.kb;
+      const float* sb_ptr = p.b_scales + static_cast<int64_t>(have ? nbi : 0) * p.kb;
 
-      float2 acc[C::kCols / 2];
+      float2 acc[64];
 #pragma unroll
-      for (int j = 0; j < C::kCols / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
+      for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
 
-      float s_next = have_scales ? __ldg(sa_ptr) * __ldg(sb_ptr) : 0.0f;
+      float s_next = have ? __ldg(sa_ptr) * __ldg(sb_ptr) : 0.0f;
       for (int kb = 0; kb < p.kb; ++kb, ++kiter) {
         const float s = s_next;
-        if (kb + 1 < p.kb && have_scales) s_next = __ldg(sa_ptr + kb + 1) * __ldg(sb_ptr + kb + 1);
+        if (kb + 1 < p.kb && have) s_next = __ldg(sa_ptr + kb + 1) * __ldg(sb_ptr + kb + 1);
         const uint32_t buf = kiter & 1u;
-        // one lane polls (256 polling threads would keep the shared-memory pipe busy that
-        // the tensor core reads its operands through); the result is broadcast by the vote
-        uint32_t got = 1u;
-        if (lane == 0 || (p.debug & 16)) {
-          got = mbar_wait(&tmem_full[buf], (kiter >> 1) & 1u, abort_flag, p.status,
-                          kSitePromoTmemFull) ? 1u : 0u;
-        }
-        if (!__all_sync(0xFFFFFFFFu, got != 0u)) {
+        if (!mbar_wait(&tmem_full[buf], (kiter >> 1) & 1u, abort_flag, p.status,
+                       kSitePromoTmemFull)) {
           ok = false;
           break;
         }
-        const bool tr = p.trace && blockIdx.x == 0 && kiter < kTraceIters && lane == 0;
-        if (tr && pw == 0) p.trace[kiter * 16 + 4] = clock64();
+        __syncwarp();
         tc_fence_after_sync();
-        const uint32_t taddr = lane_base + buf * BN + half * C::kCols;
-        if (p.debug & 1) {
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-          continue;
-        }
+        const uint32_t taddr = lane_base + buf * BN;
         uint32_t v0[32], v1[32];
         tmem_ld_32x32(taddr, v0);
         tmem_ld_32x32(taddr + 32, v1);
         tmem_ld_wait_pin(v0);
         tmem_ld_wait_pin(v1);
-        if constexpr (C::kCols == 64) {
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-          if (tr) p.trace[kiter * 16 + 8 + pw] = clock64();
-          if (!(p.debug & 2)) promote32(acc, v0, s);
-          if (!(p.debug & 2)) promote32(acc + 16, v1, s);
-          if (tr && pw == 0) p.trace[kiter * 16 + 6] = clock64();
-        } else {
-          if (!(p.debug & 2)) promote32(acc, v0, s);
-          tmem_ld_32x32(taddr + 64, v0);
-          if (!(p.debug & 2)) promote32(acc + 16, v1, s);
-          tmem_ld_32x32(taddr + 96, v1);
-          tmem_ld_wait_pin(v0);
-          tmem_ld_wait_pin(v1);
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-          if (tr) p.trace[kiter * 16 + 8 + pw] = clock64();
-          if (!(p.debug & 2)) promote32(acc + 32, v0, s);
-          if (!(p.debug & 2)) promote32(acc + 48, v1, s);
-          if (tr && pw == 0) p.trace[kiter * 16 + 6] = clock64();
-        }
+        promote32(acc, v0, s);
+        tmem_ld_32x32(taddr + 64, v0);
+        promote32(acc + 16, v1, s);
+        tmem_ld_32x32(taddr + 96, v1);
+        tmem_ld_wait_pin(v0);
+        tmem_ld_wait_pin(v1);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        promote32(acc + 32, v0, s);
+        promote32(acc + 48, v1, s);
       }
       if (!ok) break;
 
-      // ---- epilogue: this thread holds C[gm, col0 .. col0 + kCols) in fp32
-      const float* accf = reinterpret_cast<const float*>(acc);
-      if (sizeof(OutT) == 2 && p.tma_store) {
+      // ---- epilogue: this thread holds C[gm, col .. col + 128) in fp32
 #pragma unroll
-        for (int ch = 0; ch < C::kCols / 64; ++ch) {
+      for (int ch = 0; ch < 2; ++ch) {
+        const float* accf = reinterpret_cast<const float*>(acc) + ch * 64;
+        const int col0 = tn * BN + half * BH + ch * 64;
+        if (sizeof(OutT) == 2 && p.tma_store) {
           // the staging buffer may still be read by the previous TMA store
           if (issuer) tma_store_wait_read0();
           named_bar_sync(1 + half, 128);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             uint4 w;
-            const float* a8 = accf + ch * 64 + j * 8;
+            const float* a8 = accf + j * 8;
             w.x = pack2<OutT>(a8[0], a8[1]);
             w.y = pack2<OutT>(a8[2], a8[3]);
             w.z = pack2<OutT>(a8[4], a8[5]);
@@ -379,28 +351,27 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           fence_proxy_async_smem();
           named_bar_sync(1 + half, 128);
-          const int x = col0 + ch * 64;
-          if (issuer && x < p.n) {
-            tma_store_2d(&map_c, my_buf, x, tm * BM);
+          if (issuer && col0 < p.n) {
+            tma_store_2d(&map_c, my_buf, col0, tm * BM);
             tma_store_commit();
           }
-        }
-      } else if (gm < p.m) {
-        OutT* crow = static_cast<OutT*>(p.c) + static_cast<int64_t>(gm) * p.n;
-        constexpr int kVec = 16 / sizeof(OutT);
-        // fully unrolled: the accumulators must stay in registers
+        } else if (gm < p.m) {
+          OutT* crow = static_cast<OutT*>(p.c) + static_cast<int64_t>(gm) * p.n;
+          constexpr int kVec = 16 / sizeof(OutT);
+          // fully unrolled: the accumulators must stay in registers
 #pragma unroll
-        for (int j = 0; j < C::kCols; j += kVec) {
-          const int col = col0 + j;
-          alignas(16) OutT tmp[kVec];
+          for (int j = 0; j < 64; j += kVec) {
+            const int col = col0 + j;
+            alignas(16) OutT tmp[kVec];
 #pragma unroll
-          for (int e = 0; e < kVec; ++e) tmp[e] = to_out<OutT>(accf[j + e]);
-          if (col + kVec <= p.n && (reinterpret_cast<uintptr_t>(crow + col) & 15u) == 0) {
-            *reinterpret_cast<uint4*>(crow + col) = *reinterpret_cast<const uint4*>(tmp);
-          } else {
+            for (int e = 0; e < kVec; ++e) tmp[e] = to_out<OutT>(accf[j + e]);
+            if (col + kVec <= p.n && (reinterpret_cast<uintptr_t>(crow + col) & 15u) == 0) {
+              *reinterpret_cast<uint4*>(crow + col) = *reinterpret_cast<const uint4*>(tmp);
+            } else {
 #pragma unroll
-            for (int e = 0; e < kVec; ++e)
-              if (col + e < p.n) crow[col + e] = tmp[e];
+              for (int e = 0; e < kVec; ++e)
+                if (col + e < p.n) crow[col + e] = tmp[e];
+            }
           }
         }
       }
@@ -411,31 +382,23 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (warp == 2) tmem_dealloc(tmem_base, C::kTmemCols);
+  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-template <int BN, typename OutT>
+template <typename OutT>
 int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
              const GemmParams& p, int ctas, cudaStream_t stream) {
-  using C = Cfg<BN>;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_kernel<BN, OutT>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_kernel<OutT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return note_cuda_error(e);
     attr_done[dev] = true;
   }
-  w8a8_gemm_kernel<BN, OutT><<<ctas, kThreads, C::kSmemBytes, stream>>>(ma, mb, mc, p);
+  w8a8_gemm_kernel<OutT><<<ctas, kThreads, kSmemBytes, stream>>>(ma, mb, mc, p);
   return check_launch();
-}
-
-template <typename OutT>
-int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
-              const GemmParams& p, int ctas, cudaStream_t stream) {
-  return bn == 256 ? launch_t<256, OutT>(ma, mb, mc, p, ctas, stream)
-                   : launch_t<128, OutT>(ma, mb, mc, p, ctas, stream);
 }
 
 }  // namespace
@@ -444,8 +407,6 @@ int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, 
                 const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
                 cudaStream_t stream) {
   const Options& opt = options();
-  int bn = opt.gemm_block_n;
-  if (bn == 0) bn = (n > 128) ? 256 : 128;
   const int out_bytes = (out_dt == 0) ? 4 : 2;
   bool tma_store = out_bytes == 2 && (n * out_bytes) % 16 == 0 &&
                    (reinterpret_cast<uintptr_t>(c) % 16 == 0);
@@ -461,19 +422,17 @@ int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, 
   p.kb = static_cast<int>(k / 128);
   p.nb = static_cast<int>((n + 127) / 128);
   p.tiles_m = static_cast<int>((m + BM - 1) / BM);
-  p.tiles_n = static_cast<int>((n + bn - 1) / bn);
+  p.tiles_n = static_cast<int>((n + BN - 1) / BN);
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
-  if (tiles > 0x7FFFFFFF) return INFEROP_ERR_LIMIT;
+  if (tiles > 0x7FFFFFFF || tiles * p.kb > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
   p.num_tiles = static_cast<int>(tiles);
   p.tma_store = tma_store ? 1 : 0;
-  p.debug = opt.gemm_debug;
-  p.trace = reinterpret_cast<long long*>(opt.gemm_trace_ptr);
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;
   int rc = make_tensor_map_2d(&ma, a_q, 1, m, k, k, BM, BK, true);
   if (rc != INFEROP_OK) return rc;
-  rc = make_tensor_map_2d(&mb, b_q, 1, n, k, k, bn, BK, true);
+  rc = make_tensor_map_2d(&mb, b_q, 1, n, k, k, BN, BK, true);
   if (rc != INFEROP_OK) return rc;
   if (tma_store) {
     rc = make_tensor_map_2d(&mc, c, 2, m, n, n * 2, 128, 64, true);
@@ -485,9 +444,9 @@ int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, 
   if (ctas > p.num_tiles) ctas = p.num_tiles;
 
   switch (out_dt) {
-    case 0: return launch_bn<float>(bn, ma, mb, mc, p, ctas, stream);
-    case 1: return launch_bn<__half>(bn, ma, mb, mc, p, ctas, stream);
-    case 2: return launch_bn<__nv_bfloat16>(bn, ma, mb, mc, p, ctas, stream);
+    case 0: return launch_t<float>(ma, mb, mc, p, ctas, stream);
+    case 1: return launch_t<__half>(ma, mb, mc, p, ctas, stream);
+    case 2: return launch_t<__nv_bfloat16>(ma, mb, mc, p, ctas, stream);
     default: return INFEROP_ERR_DTYPE;
   }
 }

@@ -28,8 +28,6 @@ struct Options {
   int gemm_block_n = 0;    // 0 auto, 128, 256
   int gemm_tma_store = -1; // -1 auto, 0 off, 1 on
   int gemm_ctas = 0;       // 0 = one per SM
-  int gemm_debug = 0;      // timing experiments; non-zero gives wrong results
-  int64_t gemm_trace_ptr = 0;  // device buffer of 512*8 int64 for clock stamps, 0 = off
 };
 Options& options();
 
@@ -40,6 +38,7 @@ int launch_dequant(void* x, int32_t dt, const void* q, const void* scales, int64
                    int64_t cols, int32_t gs, cudaStream_t stream, int sms);
 
 int run_cvt_selftest(uint64_t lo, uint64_t hi, uint64_t* out2, int sms);
+int run_div_selftest(int is_bf16, uint64_t* out3, int sms);
 
 // gemm_sm100.cu
 int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, const void* b_q,

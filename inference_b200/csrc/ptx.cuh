@@ -22,7 +22,6 @@ struct DeviceStatus {
 };
 
 constexpr long long kWaitBudgetCycles = 1LL << 31;  // about a second at the SM's top clock
-constexpr unsigned int kProbeNs = 2000;             // longest time one mbarrier probe may park a thread
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -59,10 +58,33 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                "r"(bytes)
                : "memory");
 }
-// One probe of the barrier.  The hardware may park the thread until the phase
-// completes or a time limit passes; the limit is given explicitly (in ns) so
-// that the bounded wait below can keep its own clock.
+// One probe of the barrier, parking form: the hardware may suspend the thread
+// until the phase completes or an implementation-defined time limit passes.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Parking probe with an explicit upper bound (ns) on the time the thread may be suspended.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking probe.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -76,15 +98,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the budget ran out or another role of this
 // CTA already gave up (*abort_flag != 0); the caller then leaves its loop.
+// Each probe may park the thread for at most kProbeNs, so the clock and the
+// abort flag need reading only every few probes.
+constexpr unsigned int kProbeNs = 4000;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile uint32_t* abort_flag, DeviceStatus* status,
                                           uint32_t site) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait_hint(bar, parity, kProbeNs)) return true;
   const long long t0 = clock64();
   uint32_t polls = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    // each probe parks the thread for at most kProbeNs, so the clock needs reading only now and then
+    if (mbar_try_wait_hint(bar, parity, kProbeNs)) return true;
     if ((++polls & 15u) != 0u) continue;
     if (*abort_flag != 0u) return false;
     if (clock64() - t0 > kWaitBudgetCycles) {

@@ -94,10 +94,30 @@ __device__ __forceinline__ uint32_t nan_byte(float x) {
   return (x != x) ? (0x7Fu | ((__float_as_uint(x) >> 24) & 0x80u)) : 0xFFu;
 }
 
-__device__ __forceinline__ uint2 quantise8(const float (&f)[8], float scale) {
+// x / scale, correctly rounded, from a correctly rounded reciprocal rcp = RN(1/scale):
+// q0 = RN(x * rcp) is within an ulp or so of the quotient, the residual x - q0 * scale is
+// exact in one FMA, and adding residual * rcp back lands on RN(x / scale).  Used only where
+// kFastDivOk says the operands are far from overflow and underflow, and only for 16-bit
+// inputs, for which the whole domain (every group maximum x every element value) is checked
+// against __fdiv_rn by inferop_selftest_quant_div.
+__device__ __forceinline__ float div_by_rcp(float x, float scale, float rcp) {
+  const float q0 = __fmul_rn(x, rcp);
+  // the residual is kept negated (q0 * scale - x) so that a zero x keeps its sign:
+  // (-0) - (-0) * ... ends in -0 + -0 = -0, where x - q0 * scale would give +0
+  const float neg_r = __fmaf_rn(q0, scale, -x);
+  return __fmaf_rn(-neg_r, rcp, q0);
+}
+// amax in [2^-100, 2^127): scale, its reciprocal, every quotient and every residual are
+// normal numbers
+__device__ __forceinline__ bool fast_div_ok(float amax) {
+  return amax >= 7.888609052e-31f && amax < 1.701411835e38f;
+}
+
+template <bool kFast>
+__device__ __forceinline__ uint2 quantise8(const float (&f)[8], float scale, float rcp) {
   float q[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = __fdiv_rn(f[i], scale);
+  for (int i = 0; i < 8; ++i) q[i] = kFast ? div_by_rcp(f[i], scale, rcp) : __fdiv_rn(f[i], scale);
   uint32_t w0 = cvt2(q[0], q[1]) | (cvt2(q[2], q[3]) << 16);
   uint32_t w1 = cvt2(q[4], q[5]) | (cvt2(q[6], q[7]) << 16);
   // any byte equal to 0x7F / 0xFF marks a NaN quotient
@@ -150,7 +170,14 @@ quant128_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, const T* __
       for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
       const float scale = (amax == 0.0f) ? 1.0f : __fmul_rn(amax, 1.0f / 448.0f);
       if (live[u]) {
-        const uint2 bytes = quantise8(f, scale);
+        uint2 bytes;
+        // 16-bit inputs whose group maximum is far from the ends of the fp32 range divide
+        // through the reciprocal (3 FP ops per element); everything else uses IEEE division
+        if (sizeof(T) == 2 && fast_div_ok(amax)) {
+          bytes = quantise8<true>(f, scale, __frcp_rn(scale));
+        } else {
+          bytes = quantise8<false>(f, scale, 0.0f);
+        }
         *reinterpret_cast<uint2*>(q + g * 128 + sub * 8) = bytes;
         if (sub == 0) scales[g] = scale;
       }
@@ -239,6 +266,35 @@ cvt_selftest_kernel(uint64_t lo, uint64_t hi, unsigned long long* counts) {
   if (bad_nan) atomicAdd(&counts[1], bad_nan);
 }
 
+// Self-test of div_by_rcp: for every finite positive 16-bit group maximum (bf16 when
+// is_bf16, else fp16) that takes the fast path, and every 16-bit element value no larger in
+// magnitude, the E4M3 byte from the reciprocal path must equal the byte from __fdiv_rn.
+__global__ void __launch_bounds__(kThreads)
+div_selftest_kernel(int is_bf16, unsigned long long* counts) {
+  unsigned long long bad = 0, pairs = 0;
+  for (uint32_t a = blockIdx.x + 1; a < 0x8000u; a += gridDim.x) {
+    const float amax = is_bf16 ? __uint_as_float(a << 16)
+                               : __half2float(__ushort_as_half(static_cast<unsigned short>(a)));
+    if (!(amax == amax) || !fast_div_ok(amax)) continue;  // NaN / Inf / out of the fast range
+    const float scale = __fmul_rn(amax, 1.0f / 448.0f);
+    const float rcp = __frcp_rn(scale);
+    for (uint32_t xb = threadIdx.x; xb < 0x10000u; xb += kThreads) {
+      const float x = is_bf16 ? __uint_as_float(xb << 16)
+                              : __half2float(__ushort_as_half(static_cast<unsigned short>(xb)));
+      if (!(fabsf(x) <= amax)) continue;
+      ++pairs;
+      const uint32_t fast = cvt2(div_by_rcp(x, scale, rcp), 0.0f) & 0xFFu;
+      const uint32_t slow = cvt2(__fdiv_rn(x, scale), 0.0f) & 0xFFu;
+      if (fast != slow) {
+        ++bad;
+        counts[2] = (static_cast<unsigned long long>(a) << 32) | xb;  // one example: group maximum, element
+      }
+    }
+  }
+  if (bad) atomicAdd(&counts[0], bad);
+  atomicAdd(&counts[1], pairs);
+}
+
 int grid_for(int64_t work_items_per_thread_block, int sms) {
   int64_t want = work_items_per_thread_block;
   int64_t cap = static_cast<int64_t>(sms) * 8;  // 8 resident 256-thread CTAs per SM
@@ -285,6 +341,17 @@ int run_cvt_selftest(uint64_t lo, uint64_t hi, uint64_t* out2, int sms) {
   cudaMemset(d, 0, 16);
   cvt_selftest_kernel<<<sms * 8, kThreads>>>(lo, hi, d);
   e = cudaMemcpy(out2, d, 16, cudaMemcpyDeviceToHost);
+  cudaFree(d);
+  return e == cudaSuccess ? INFEROP_OK : note_cuda_error(e);
+}
+
+int run_div_selftest(int is_bf16, uint64_t* out3, int sms) {
+  unsigned long long* d = nullptr;
+  cudaError_t e = cudaMalloc(&d, 24);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  cudaMemset(d, 0, 24);
+  div_selftest_kernel<<<sms * 8, kThreads>>>(is_bf16, d);
+  e = cudaMemcpy(out3, d, 24, cudaMemcpyDeviceToHost);
   cudaFree(d);
   return e == cudaSuccess ? INFEROP_OK : note_cuda_error(e);
 }

@@ -43,6 +43,17 @@ def test_hardware_converter_equals_software_encoder_on_all_floats(ops):
     assert out[0] == 0, f"{out[0]} non-NaN inputs convert differently"
 
 
+@pytest.mark.parametrize("dt", [1, 2])
+def test_reciprocal_division_equals_ieee_division_on_the_whole_16bit_domain(ops, dt):
+    import ctypes as C
+    from inference_b200 import _capi
+    out = (C.c_uint64 * 3)()
+    _capi.check(_capi.lib.inferop_selftest_quant_div(dt, out), "selftest")
+    assert out[1] > 1 << 29, f"the sweep did not cover the domain ({out[1]} pairs)"
+    assert out[0] == 0, (f"{out[0]} of {out[1]} (group maximum, element) pairs give a different byte, "
+                         f"e.g. maximum bits {out[2] >> 32:#06x} element bits {out[2] & 0xFFFF:#06x}")
+
+
 def test_golden_vectors_bf16_gs128_gs64_fp32(ops):
     g = np.load(os.path.join(GOLDEN, "quant_golden.npz"))
     x = to_dev(g["x_bf16_bits"], torch.bfloat16)
