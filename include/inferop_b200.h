@@ -76,7 +76,10 @@ INFEROP_API int inferop_dequant_fp8_per_token_group(void* x, int32_t dt, const v
  *   b_scales [ceil(N/128), K/128] fp32, c [M,N] in out_dt (0/1/2).
  * Contract as in the reference: group_size == 128, block_n == 128, K % 128 == 0,
  * M > 0, N > 0 (else INFEROP_ERR_SHAPE).  a_q and b_q must be 16-byte aligned
- * (INFEROP_ERR_POINTER otherwise); c may have any alignment and N any value. */
+ * (INFEROP_ERR_POINTER otherwise); c may have any alignment and N any value.
+ * Calls with M <= 96 take a weight-streaming kernel that keeps a library-owned scratch
+ * buffer (about 20 MB) per stream; it is allocated by the first such call on a stream, so
+ * make that call before capturing the stream into a CUDA graph. */
 INFEROP_API int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, const void* b_q,
                                 const void* b_scales, int64_t m, int64_t n, int64_t k,
                                 int32_t group_size, int32_t block_n, int32_t out_dt,
@@ -105,7 +108,8 @@ INFEROP_API int inferop_selftest_e4m3_cvt(uint64_t lo, uint64_t hi, uint64_t* ou
 INFEROP_API int inferop_selftest_quant_div(int32_t dt, uint64_t* out3);
 
 /* Tuning knobs for experiments and tests (process-wide, not thread-safe).
- * key: "gemm_tma_store" (-1 auto, 0, 1), "gemm_ctas" (0 = one per SM), "gemm_block_n"
+ * key: "gemm_tma_store" (-1 auto, 0, 1), "gemm_ctas" (0 = one per SM), "gemm_path" (0 auto,
+ *      1 always the large-tile kernel, 2 the small-M kernel whenever M <= 128), "gemm_block_n"
  *      (accepted and ignored: the kernel has one tile shape).  Returns INFEROP_ERR_SHAPE for
  *      an unknown key/value. */
 INFEROP_API int inferop_set_option(const char* key, int64_t value);

@@ -112,6 +112,40 @@ DeviceCtx* current_ctx(int* err) {
   return c;
 }
 
+// Scratch set of `stream` on this device, created on first use.  False when none can be had.
+bool decode_scratch(DeviceCtx* ctx, cudaStream_t stream, float** ws, int** counters) {
+  static std::mutex m;
+  std::lock_guard<std::mutex> lock(m);
+  for (int i = 0; i < ctx->n_scratch; ++i) {
+    if (ctx->scratch_stream[i] == stream) {
+      *ws = ctx->scratch_ws[i];
+      *counters = ctx->scratch_counters[i];
+      return true;
+    }
+  }
+  if (ctx->n_scratch >= DeviceCtx::kMaxStreams) return false;
+  float* w = nullptr;
+  int* c = nullptr;
+  if (cudaMalloc(&w, decode_workspace_bytes(ctx->sm_count)) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  if (cudaMalloc(&c, kDecodeMaxTiles * sizeof(int)) != cudaSuccess ||
+      cudaMemset(c, 0, kDecodeMaxTiles * sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(w);
+    if (c) cudaFree(c);
+    return false;
+  }
+  const int i = ctx->n_scratch++;
+  ctx->scratch_stream[i] = stream;
+  ctx->scratch_ws[i] = w;
+  ctx->scratch_counters[i] = c;
+  *ws = w;
+  *counters = c;
+  return true;
+}
+
 }  // namespace ib200
 
 using namespace ib200;
@@ -196,6 +230,19 @@ int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, 
   if ((reinterpret_cast<uintptr_t>(a_q) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u)) {
     return INFEROP_ERR_POINTER;
   }
+  // Small M: the weight-streaming kernel, which needs scratch memory for split tiles.  The
+  // scratch is created on the first such call of each stream (a cudaMalloc: make that call
+  // before any stream capture); with more than DeviceCtx::kMaxStreams streams, or when the
+  // allocation fails, the large-tile kernel serves the call instead.
+  const int path = options().gemm_path;
+  const int64_t tiles = (n + 127) / 128;
+  if (path != 1 && m <= kDecodeMaxM && tiles <= kDecodeMaxTiles && (path == 2 || m <= 96)) {
+    float* ws = nullptr;
+    int* counters = nullptr;
+    if (decode_scratch(ctx, s, &ws, &counters)) {
+      return launch_gemm_decode(ctx, ws, counters, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
+    }
+  }
   return launch_gemm(ctx, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
 }
 
@@ -241,6 +288,12 @@ int inferop_set_option(const char* key, int64_t value) {
   } else if (!strcmp(key, "gemm_tma_store")) {
     if (value < -1 || value > 1) return INFEROP_ERR_SHAPE;
     o.gemm_tma_store = static_cast<int>(value);
+  } else if (!strcmp(key, "decode_splits")) {
+    if (value < 0 || value > 1024) return INFEROP_ERR_SHAPE;
+    o.decode_splits = static_cast<int>(value);
+  } else if (!strcmp(key, "gemm_path")) {
+    if (value < 0 || value > 2) return INFEROP_ERR_SHAPE;
+    o.gemm_path = static_cast<int>(value);
   } else if (!strcmp(key, "gemm_ctas")) {
     if (value < 0 || value > 1024) return INFEROP_ERR_SHAPE;
     o.gemm_ctas = static_cast<int>(value);

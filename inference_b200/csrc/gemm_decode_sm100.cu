@@ -1,0 +1,426 @@
+// Small-M ("decode") variant of the blockwise-FP8 W8A8 GEMM for sm_100a.
+//
+// Same arithmetic contract as gemm_sm100.cu (reference kernels/gemm/w8a8_block_fp8.cu:100-114,
+// reference/reference.cpp:93-110), different mapping.  With a handful of tokens the work is a
+// pure stream of the weight matrix from HBM, so:
+//   * operands are swapped: a 128-row weight tile is the M side of tcgen05.mma (UMMA M=128)
+//     and the tokens, padded to MP in {16, 32, 64, 128}, are its N side.  The accumulator of one
+//     K block is a [128 weight rows] x [MP tokens] slice of tensor memory; 512 / MP (at most 8)
+//     slices are in flight, so the MMA -> promotion -> MMA round trip never limits the stream.
+//   * work is dealt in whole pieces: with at least as many weight tiles as CTAs every CTA takes
+//     a contiguous run of whole tiles; with fewer, every tile's K range is cut into `splits`
+//     equal parts, one CTA each (split-K).  A CTA of a split tile writes an fp32 partial to a
+//     workspace; the last CTA to finish the tile adds the parts in a fixed order
+//     (deterministic) and writes the output.  HBM, not the SM count, bounds this kernel, so
+//     leaving a few SMs idle costs nothing, while ragged pieces would cost a second partial
+//     flush per CTA.
+//
+// CTA layout (256 threads, one CTA per SM):
+//   warp 0  allocates / frees tensor memory; one thread is the TMA producer: weight tile
+//           [128 x 128 B] + token tile [MP x 128 B] per K block into a deep ring
+//   warps 1, 3  MMA issuers (warp-uniform loops, one elected lane each, alternating units):
+//           4 x tcgen05.mma (M=128, N=MP, K=32) per unit
+//   warp 2  scale warp: writes sa[m, kb] * sb[tile, kb] for the MP tokens of each unit to a
+//           small shared ring, one vector per TMEM slice
+//   warps 4-7  promotion + epilogue: thread = one weight row (= output column), MP accumulators
+//
+// HBM traffic (algorithmic): N*K weight bytes + M*K token bytes + scales + 2*M*N output bytes;
+// split tiles add 2 x 4*128*MP bytes of workspace traffic per extra segment.
+//
+// Every wait is bounded (ptx.cuh: mbar_wait); see gemm_sm100.cu for the wind-down rules.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "internal.h"
+
+namespace ib200 {
+namespace {
+
+constexpr int TN = 128;   // weight rows per tile (UMMA M)
+constexpr int BK = 128;
+constexpr int kThreads = 256;
+constexpr int kBytesW = TN * BK;
+
+template <int MP>
+struct DCfg {
+  static constexpr int kBytesA = MP * BK;
+  static constexpr int kStageBytes = kBytesW + kBytesA;
+  static constexpr int kStages = (200 * 1024 / kStageBytes) < 10 ? (200 * 1024 / kStageBytes) : 10;
+  static constexpr int kBufs = (512 / MP) < 8 ? (512 / MP) : 8;
+  static constexpr int kTmemCols = (kBufs * MP) < 32 ? 32 : (kBufs * MP);
+  static constexpr int kScaleBytes = kBufs * MP * 4;
+  static constexpr int kBarrierBytes = 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleBytes + kBarrierBytes + 1024;
+};
+
+struct DecodeParams {
+  const float* a_scales;   // [M, KB]
+  const float* b_scales;   // [ceil(N/128), KB]
+  void* c;                 // [M, N]
+  float* workspace;        // [gridDim.x][MP][128] fp32 partials
+  int splits;              // K parts per tile (1 = whole tiles, CTAs take runs of tiles)
+  int* counters;           // [n_tiles], zero between launches
+  int m, n, kb, n_tiles;
+  long long units;         // n_tiles * kb
+  DeviceStatus* status;
+};
+
+enum : uint32_t {
+  kSiteDProducerEmpty = 0x111,
+  kSiteDMmaFull = 0x211,
+  kSiteDMmaTmemEmpty = 0x212,
+  kSiteDScaleEmpty = 0x411,
+  kSiteDPromoFull = 0x311,
+  kSiteDPromoScale = 0x312,
+};
+
+template <typename OutT>
+__device__ __forceinline__ OutT cvt_out(float v);
+template <>
+__device__ __forceinline__ float cvt_out<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half cvt_out<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]);
+template <>
+__device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_32x16(taddr, r); }
+template <>
+__device__ __forceinline__ void tmem_ld_cols<32>(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld_32x32(taddr, r); }
+
+template <int N>
+__device__ __forceinline__ void tmem_wait_pin(uint32_t (&r)[N]) {
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < N; ++i) asm volatile("" : "+r"(r[i])::"memory");
+}
+
+template <int MP, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                   const DecodeParams p) {
+  using C = DCfg<MP>;
+  constexpr int CH = (MP < 32) ? MP : 32;   // columns per tensor-memory load
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  float* sv = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);   // [kBufs][MP]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sv) + C::kScaleBytes);
+  uint64_t* full = bars;                         // [kStages] TMA -> MMA
+  uint64_t* empty = full + C::kStages;           // [kStages] MMA -> TMA
+  uint64_t* tmem_full = empty + C::kStages;      // [kBufs]   MMA -> promotion
+  uint64_t* tmem_empty = tmem_full + C::kBufs;   // [kBufs]   promotion -> MMA, scale warp
+  uint64_t* sv_full = tmem_empty + C::kBufs;     // [kBufs]   scale warp -> promotion
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sv_full + C::kBufs);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* last_flag = tmem_slot + 2;
+
+  const int warp = __shfl_sync(0xFFFFFFFFu, static_cast<int>(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < C::kBufs; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 4);
+      mbar_init(&sv_full[b], 1);
+    }
+    *abort_flag = 0u;
+    mbar_init_fence();
+    tma_prefetch_desc(&map_w);
+    tma_prefetch_desc(&map_a);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_slot, 0);
+
+  // this CTA's piece: tiles [t_first, ...) from K block kb_first, `count` units in all
+  int t_first, kb_first;
+  uint32_t count;
+  if (p.splits == 1) {
+    const long long g = gridDim.x, c = blockIdx.x;
+    t_first = static_cast<int>(c * p.n_tiles / g);
+    kb_first = 0;
+    count = static_cast<uint32_t>(((c + 1) * p.n_tiles / g - t_first) * p.kb);
+  } else {
+    const int part = blockIdx.x % p.splits;
+    t_first = blockIdx.x / p.splits;
+    kb_first = part * p.kb / p.splits;
+    count = static_cast<uint32_t>((part + 1) * p.kb / p.splits - kb_first);
+  }
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (warp-uniform loop) ------
+    int t = t_first, kb = kb_first;
+    uint32_t armed = 0;
+    bool ok = true;
+    for (uint32_t i = 0; i < count; ++i) {
+      const uint32_t stage = i % C::kStages;
+      const uint32_t phase = (i / C::kStages) & 1u;
+      if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteDProducerEmpty)) {
+        ok = false;
+        break;
+      }
+      __syncwarp();
+      uint8_t* dst = smem + stage * C::kStageBytes;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(&full[stage], C::kStageBytes);
+        tma_load_2d(dst, &map_w, &full[stage], kb * BK, t * TN);
+        tma_load_2d(dst + kBytesW, &map_a, &full[stage], kb * BK, 0);
+      }
+      __syncwarp();
+      armed = i + 1;
+      if (++kb == p.kb) {
+        kb = 0;
+        ++t;
+      }
+    }
+    if (!ok && lane == 0) {
+      // wind-down: let the copies this warp started land before the CTA exits
+      const uint32_t lo = armed > C::kStages ? armed - C::kStages : 0u;
+      for (uint32_t i = lo; i < armed; ++i) {
+        const long long t0 = clock64();
+        while (!mbar_test_wait(&full[i % C::kStages], (i / C::kStages) & 1u)) {
+          if (clock64() - t0 > kWaitBudgetCycles) break;
+        }
+      }
+    }
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------ MMA issuers (warp-uniform) ------------
+    // warp 1 issues the even units of the range, warp 3 the odd ones: waiting, building
+    // descriptors, 4 MMAs and 2 commits cost one thread about 650 cycles per unit, more than
+    // the time the unit's 18 KiB take to arrive from HBM
+    constexpr uint32_t idesc = umma_idesc_e4m3_f32(TN, MP);
+    const uint32_t smem_base = smem_u32(smem);
+    for (uint32_t i = (warp == 3) ? 1u : 0u; i < count; i += 2) {
+      const uint32_t stage = i % C::kStages;
+      const uint32_t phase = (i / C::kStages) & 1u;
+      const uint32_t buf = i % C::kBufs;
+      const uint32_t use = i / C::kBufs;
+      if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kSiteDMmaFull)) break;
+      if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, kSiteDMmaTmemEmpty)) break;
+      __syncwarp();
+      tc_fence_after_sync();
+      const uint32_t w_addr = smem_base + stage * C::kStageBytes;
+      const uint64_t dw = umma_desc_k_sw128(w_addr);
+      const uint64_t da = umma_desc_k_sw128(w_addr + kBytesW);
+      const uint32_t d_tmem = tmem_base + buf * MP;
+      if (elect_one()) {
+#pragma unroll
+        for (int k4 = 0; k4 < BK / 32; ++k4) {
+          umma_f8_ss(d_tmem, dw + 2u * k4, da + 2u * k4, idesc, k4 > 0 ? 1u : 0u);
+        }
+        umma_commit(&tmem_full[buf]);
+        umma_commit(&empty[stage]);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 2) {
+    // ------------------------------ scale warp ----------------------------
+    int t = t_first, kb = kb_first;
+    for (uint32_t i = 0; i < count; ++i) {
+      const uint32_t buf = i % C::kBufs;
+      const uint32_t use = i / C::kBufs;
+      if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, kSiteDScaleEmpty)) break;
+      const float sb = __ldg(p.b_scales + static_cast<int64_t>(t) * p.kb + kb);
+#pragma unroll
+      for (int m0 = 0; m0 < MP; m0 += 32) {
+        const int m = m0 + lane;
+        if (m < MP) {
+          const float sa = (m < p.m) ? __ldg(p.a_scales + static_cast<int64_t>(m) * p.kb + kb) : 0.0f;
+          sv[buf * MP + m] = sa * sb;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sv_full[buf]);
+      if (++kb == p.kb) {
+        kb = 0;
+        ++t;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ promotion + epilogue ------------------
+    const int quarter = warp - 4;            // == warp % 4: TMEM lane quarter
+    const int row = quarter * 32 + lane;     // weight row inside the tile
+    const int ct = threadIdx.x - 128;        // 0..127 among the promotion threads
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    float acc[MP];
+#pragma unroll
+    for (int j = 0; j < MP; ++j) acc[j] = 0.0f;
+    int t = t_first, kb = kb_first, seg_kb0 = kb_first;
+    bool ok = true;
+    for (uint32_t i = 0; ok && i < count; ++i) {
+      const uint32_t buf = i % C::kBufs;
+      const uint32_t par = (i / C::kBufs) & 1u;
+      if (!mbar_wait(&tmem_full[buf], par, abort_flag, p.status, kSiteDPromoFull) ||
+          !mbar_wait(&sv_full[buf], par, abort_flag, p.status, kSiteDPromoScale)) {
+        ok = false;
+        break;
+      }
+      __syncwarp();
+      tc_fence_after_sync();
+      const float4* svb = reinterpret_cast<const float4*>(sv + buf * MP);
+#pragma unroll
+      for (int c0 = 0; c0 < MP; c0 += CH) {
+        uint32_t v[CH];
+        tmem_ld_cols<CH>(lane_base + buf * MP + c0, v);
+        tmem_wait_pin<CH>(v);
+#pragma unroll
+        for (int j = 0; j < CH; j += 4) {
+          const float4 s4 = svb[(c0 + j) >> 2];
+          acc[c0 + j + 0] = fmaf(__uint_as_float(v[j + 0]), s4.x, acc[c0 + j + 0]);
+          acc[c0 + j + 1] = fmaf(__uint_as_float(v[j + 1]), s4.y, acc[c0 + j + 1]);
+          acc[c0 + j + 2] = fmaf(__uint_as_float(v[j + 2]), s4.z, acc[c0 + j + 2]);
+          acc[c0 + j + 3] = fmaf(__uint_as_float(v[j + 3]), s4.w, acc[c0 + j + 3]);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+
+      const bool seg_end = (kb == p.kb - 1) || (i + 1 == count);
+      if (seg_end) {
+        const int gn = t * TN + row;
+        const bool whole = (seg_kb0 == 0 && kb == p.kb - 1);
+        if (whole) {
+          if (gn < p.n) {
+#pragma unroll
+            for (int m = 0; m < MP; ++m)
+              if (m < p.m) static_cast<OutT*>(p.c)[static_cast<int64_t>(m) * p.n + gn] = cvt_out<OutT>(acc[m]);
+          }
+        } else {
+          // one K part of a split tile: this CTA's slot of the workspace
+          float* wp = p.workspace + static_cast<int64_t>(blockIdx.x) * (MP * TN);
+#pragma unroll
+          for (int m = 0; m < MP; ++m) __stcg(wp + m * TN + row, acc[m]);
+          __threadfence();
+          named_bar_sync(1, 128);
+          if (ct == 0) {
+            const int prev = atomicAdd(p.counters + t, 1);
+            *last_flag = (prev == p.splits - 1) ? 1u : 0u;
+          }
+          named_bar_sync(1, 128);
+          if (*last_flag != 0u) {
+            __threadfence();
+            float sum[MP];
+#pragma unroll
+            for (int m = 0; m < MP; ++m) sum[m] = 0.0f;
+            for (int part = 0; part < p.splits; ++part) {   // fixed order: the result does not depend on arrival order
+              const float* rp = p.workspace + (static_cast<int64_t>(t) * p.splits + part) * (MP * TN);
+#pragma unroll
+              for (int m = 0; m < MP; ++m) sum[m] += __ldcg(rp + m * TN + row);
+            }
+            if (gn < p.n) {
+#pragma unroll
+              for (int m = 0; m < MP; ++m)
+                if (m < p.m) static_cast<OutT*>(p.c)[static_cast<int64_t>(m) * p.n + gn] = cvt_out<OutT>(sum[m]);
+            }
+            if (ct == 0) p.counters[t] = 0;   // ready for the next launch
+          }
+          named_bar_sync(1, 128);   // last_flag may be rewritten only after everyone has read it
+        }
+#pragma unroll
+        for (int j = 0; j < MP; ++j) acc[j] = 0.0f;
+        seg_kb0 = 0;
+      }
+      if (++kb == p.kb) {
+        kb = 0;
+        ++t;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
+}
+
+template <int MP, typename OutT>
+int launch_decode_t(const CUtensorMap& mw, const CUtensorMap& ma, const DecodeParams& p, int ctas,
+                    cudaStream_t stream) {
+  using C = DCfg<MP>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(w8a8_decode_kernel<MP, OutT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_done[dev] = true;
+  }
+  w8a8_decode_kernel<MP, OutT><<<ctas, kThreads, C::kSmemBytes, stream>>>(mw, ma, p);
+  return check_launch();
+}
+
+template <typename OutT>
+int launch_decode_mp(int mp, const CUtensorMap& mw, const CUtensorMap& ma, const DecodeParams& p,
+                     int ctas, cudaStream_t stream) {
+  switch (mp) {
+    case 16: return launch_decode_t<16, OutT>(mw, ma, p, ctas, stream);
+    case 32: return launch_decode_t<32, OutT>(mw, ma, p, ctas, stream);
+    case 64: return launch_decode_t<64, OutT>(mw, ma, p, ctas, stream);
+    default: return launch_decode_t<128, OutT>(mw, ma, p, ctas, stream);
+  }
+}
+
+}  // namespace
+
+size_t decode_workspace_bytes(int ctas) { return static_cast<size_t>(ctas) * kDecodeMaxM * TN * 4; }
+
+int launch_gemm_decode(DeviceCtx* ctx, float* workspace, int* counters, void* c, const void* a_q,
+                       const void* a_scales, const void* b_q, const void* b_scales, int64_t m,
+                       int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream) {
+  const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
+  DecodeParams p;
+  p.a_scales = static_cast<const float*>(a_scales);
+  p.b_scales = static_cast<const float*>(b_scales);
+  p.c = c;
+  p.workspace = workspace;
+  p.counters = counters;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.kb = static_cast<int>(k / 128);
+  p.n_tiles = static_cast<int>((n + TN - 1) / TN);
+  p.units = static_cast<long long>(p.n_tiles) * p.kb;
+  p.status = ctx->status;
+
+  CUtensorMap mw, ma;
+  int rc = make_tensor_map_2d(&mw, b_q, 1, n, k, k, TN, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  rc = make_tensor_map_2d(&ma, a_q, 1, m, k, k, mp, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  const Options& opt = options();
+  int max_ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
+  if (max_ctas > ctx->sm_count) max_ctas = ctx->sm_count;   // the workspace is sized for one CTA per SM
+  int ctas;
+  if (p.n_tiles >= max_ctas) {
+    p.splits = 1;
+    ctas = max_ctas;
+  } else {
+    p.splits = max_ctas / p.n_tiles;
+    if (p.splits > p.kb) p.splits = p.kb;
+    if (opt.decode_splits > 0 && opt.decode_splits <= p.splits) p.splits = opt.decode_splits;
+    ctas = p.n_tiles * p.splits;
+  }
+  switch (out_dt) {
+    case 0: return launch_decode_mp<float>(mp, mw, ma, p, ctas, stream);
+    case 1: return launch_decode_mp<__half>(mp, mw, ma, p, ctas, stream);
+    case 2: return launch_decode_mp<__nv_bfloat16>(mp, mw, ma, p, ctas, stream);
+    default: return INFEROP_ERR_DTYPE;
+  }
+}
+
+}  // namespace ib200

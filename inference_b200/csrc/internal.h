@@ -20,6 +20,13 @@ struct DeviceCtx {
   int sm_version = 0;
   int sm_count = 0;
   DeviceStatus* status = nullptr;  // device memory, zero-initialised
+  // Scratch of the small-M GEMM path, one set per stream that has used it (launches on one
+  // stream run in order and may share a set; launches on different streams may overlap).
+  static constexpr int kMaxStreams = 16;
+  int n_scratch = 0;
+  cudaStream_t scratch_stream[kMaxStreams] = {};
+  float* scratch_ws[kMaxStreams] = {};
+  int* scratch_counters[kMaxStreams] = {};
 };
 // Context of the current device (nullptr + *err set when there is none / wrong arch).
 DeviceCtx* current_ctx(int* err);
@@ -28,8 +35,11 @@ struct Options {
   int gemm_block_n = 0;    // 0 auto, 128, 256
   int gemm_tma_store = -1; // -1 auto, 0 off, 1 on
   int gemm_ctas = 0;       // 0 = one per SM
+  int decode_splits = 0;   // 0 auto, else K parts per tile of the small-M kernel (capped by SMs / tiles)
+  int gemm_path = 0;       // 0 auto, 1 always the large-tile kernel, 2 small-M kernel whenever M <= 128
 };
 Options& options();
+bool decode_scratch(DeviceCtx* ctx, cudaStream_t stream, float** ws, int** counters);
 
 // quant.cu
 int launch_quant(void* q, void* scales, const void* x, int32_t dt, int64_t rows, int64_t cols,
@@ -44,6 +54,17 @@ int run_div_selftest(int is_bf16, uint64_t* out3, int sms);
 int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, const void* b_q,
                 const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
                 cudaStream_t stream);
+
+// gemm_decode_sm100.cu : small-M path (M <= kDecodeMaxM).  workspace holds
+// decode_workspace_bytes(sm_count) bytes, counters kDecodeMaxTiles zeroed ints; both are
+// owned by the caller of launch_gemm_decode and must not be shared by launches that can
+// overlap on the device.
+constexpr int kDecodeMaxM = 128;
+constexpr int kDecodeMaxTiles = 1 << 16;
+size_t decode_workspace_bytes(int ctas);
+int launch_gemm_decode(DeviceCtx* ctx, float* workspace, int* counters, void* c, const void* a_q,
+                       const void* a_scales, const void* b_q, const void* b_scales, int64_t m,
+                       int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream);
 
 // tensormap.cu : cuTensorMapEncodeTiled through the runtime's driver entry point.
 // 2-D row-major tensor [rows, cols] of elem_bytes-wide elements with row pitch

@@ -187,3 +187,46 @@ def test_large_shapes_sampled(ops, m, n, k):
     got = c256[torch.from_numpy(rows).cuda()][:, torch.from_numpy(cols).cuda()].float().cpu().numpy()
     check(got, want, torch.bfloat16)
     ops.set_option("gemm_block_n", 0)
+
+
+# ------------------------------------------------------------------ small-M (weight-streaming) path
+@pytest.mark.parametrize("m", [1, 4, 16, 17, 33, 64, 65, 128])
+@pytest.mark.parametrize("n,k", [(384, 512), (1000, 1536), (200, 128)])
+def test_small_m_path_matches_oracle(ops, m, n, k):
+    ops.set_option("gemm_path", 2)
+    try:
+        aq, a_s, bq, bs = make_case(m, n, k, seed=m * 31 + n + k, outliers=True)
+        want = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs, threads=8)
+        for dt in (torch.float32, torch.bfloat16):
+            check(run(ops, aq, a_s, bq, bs, dt), want, dt)
+    finally:
+        ops.set_option("gemm_path", 0)
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 18432, 7168), (4, 7168, 18432), (64, 24576, 1536), (1, 7168, 18432)])
+def test_small_m_path_on_the_decode_shapes(ops, m, n, k):
+    """Decode sweep shapes: split tiles (N/128 < SM count) included.  The streaming kernel must be
+    repeatable bit for bit (fixed reduction order) and agree with the large-tile kernel and the
+    fp64 golden on sampled columns."""
+    from inference_b200 import synth
+    x = synth.activations(m, k, seed=3)
+    aq, a_s = ops.quant_fp8_per_token_group(x)
+    bq, bs = synth.quantised_weights(n, k, seed=3)
+    try:
+        ops.set_option("gemm_path", 2)
+        c1 = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, torch.float32)
+        c2 = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, torch.float32)
+        cb = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, torch.bfloat16)
+        ops.set_option("gemm_path", 1)
+        c3 = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, torch.float32)
+    finally:
+        ops.set_option("gemm_path", 0)
+    assert ops.device_status()[0] == 0
+    assert torch.equal(c1, c2)
+    assert torch.allclose(c1, c3, rtol=1e-5, atol=1e-5 * float(c3.abs().max()))
+    cols = np.sort(np.random.default_rng(n).choice(n, 384, replace=False))
+    want = oracle.w8a8_block_fp8_gemm(aq.cpu().numpy(), a_s.cpu().numpy(), bq.cpu().numpy(),
+                                      bs.cpu().numpy(), cols=cols, threads=8)
+    idx = torch.from_numpy(cols).cuda()
+    check(c1[:, idx].cpu().numpy(), want, torch.float32)
+    check(cb[:, idx].float().cpu().numpy(), want, torch.bfloat16)
