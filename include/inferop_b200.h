@@ -85,6 +85,24 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void
                                 int32_t group_size, int32_t block_n, int32_t out_dt,
                                 void* stream);
 
+/* ---- blockwise-FP8 GEMM for a few tokens, with no allocation
+ * No counterpart in the reference: added for callers that must not trigger a device
+ * allocation, such as a server that gave all device memory to its own pool at start-up, or a
+ * latency-critical loop that cannot make an allocation call (driver locks, possible device
+ * synchronisation).  Same arguments, contract and results as inferop_w8a8_block_fp8_gemm,
+ * restricted to M <= 32, N <= 524288 and devices with at most 160 SMs (INFEROP_ERR_LIMIT
+ * beyond).  The scratch the small-M kernel needs for split tiles is a fixed array of about
+ * 2.6 MB inside the library image, resident on every GPU that loads the library until the
+ * process exits; this call uses cudaMalloc, cudaFree and allocating library routines nowhere.
+ * The first call on a device looks the array's device address up (once per device, with
+ * that device current); make that first call before any stream capture.  All calls on a
+ * device share the array: calls that can overlap on the GPU (different streams) race on it
+ * and must be ordered by the caller. */
+INFEROP_API int inferop_w8a8_block_fp8_gemm_fixed_scratch(void* c, const void* a_q, const void* a_scales,
+                                              const void* b_q, const void* b_scales, int64_t m,
+                                              int64_t n, int64_t k, int32_t group_size,
+                                              int32_t block_n, int32_t out_dt, void* stream);
+
 /* ---- diagnostics
  * Synchronises the current device and copies out the device-side status record
  * {code, block, aux0, aux1}.  code == 0 means no bounded wait has run out since

@@ -33,6 +33,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "internal.h"
 
 namespace ib200 {
@@ -424,3 +426,101 @@ int launch_gemm_decode(DeviceCtx* ctx, float* workspace, int* counters, void* c,
 }
 
 }  // namespace ib200
+
+// ---------------------------------------------------------------------------
+// Entry point that allocates nothing.
+//
+// Some callers cannot let a library call cudaMalloc on their behalf: a serving process that
+// handed all of the device's memory to its own pool at start-up (weights, KV cache) has none
+// left for the driver to give out, and a latency-critical loop cannot afford an allocation
+// call that may take driver locks or synchronise the device.  For them the split-tile scratch
+// of the small-M kernel lives in a fixed array inside the library image instead of in memory
+// obtained at run time.  Every GPU that loads the library carries the array (about 2.6 MB)
+// until the process exits, which is why it is kept small: M <= 32 tokens, at most 4096 weight
+// tiles (N <= 524288) and at most 160 SMs.
+// ---------------------------------------------------------------------------
+namespace ib200 {
+namespace {
+
+constexpr int kFixedMaxM = 32;
+constexpr int kFixedMaxCtas = 160;
+constexpr int kFixedMaxTiles = 4096;
+
+struct FixedScratch {
+  float partials[kFixedMaxCtas * kFixedMaxM * TN];  // one K part of a split tile per CTA
+  int counters[kFixedMaxTiles];                     // arrivals per tile; zero between launches
+  DeviceStatus status;                              // bounded-wait record of this entry point
+};
+
+// The scratch itself.  In host code this name is only a handle for cudaGetSymbolAddress; the
+// device address obtained from it is what the kernel receives.
+static __device__ __align__(256) unsigned char g_fixed_scratch[sizeof(FixedScratch)];
+
+struct FixedScratchPtr {
+  FixedScratch* ptr = nullptr;
+  int sm_count = 0;
+  int sm_version = 0;
+};
+
+// Device address of the scratch on the current device, resolved once per device.
+int fixed_scratch_for_current_device(FixedScratchPtr* out) {
+  static FixedScratchPtr cache[64];
+  static std::mutex m;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  if (dev < 0 || dev >= 64) return INFEROP_ERR_LIMIT;
+  std::lock_guard<std::mutex> lock(m);
+  if (!cache[dev].ptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_fixed_scratch);
+    if (e != cudaSuccess || !p) return note_cuda_error(e == cudaSuccess ? cudaErrorInvalidSymbol : e);
+    int major = 0, minor = 0, sms = 0;
+    if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) {
+      return note_cuda_error(e);
+    }
+    cache[dev].sm_version = major * 10 + minor;
+    cache[dev].sm_count = sms;
+    cache[dev].ptr = static_cast<FixedScratch*>(p);
+  }
+  *out = cache[dev];
+  return INFEROP_OK;
+}
+
+}  // namespace
+}  // namespace ib200
+
+extern "C" int inferop_w8a8_block_fp8_gemm_fixed_scratch(void* c, const void* a_q, const void* a_scales,
+                                                         const void* b_q, const void* b_scales, int64_t m,
+                                                         int64_t n, int64_t k, int32_t group_size,
+                                                         int32_t block_n, int32_t out_dt, void* stream) {
+  using namespace ib200;
+  if (group_size != 128 || block_n != 128 || k <= 0 || k % 128 != 0 || m <= 0 || n <= 0) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (out_dt < 0 || out_dt > 2) return INFEROP_ERR_DTYPE;
+  if (m > kFixedMaxM || (n + TN - 1) / TN > kFixedMaxTiles || k > 0x7FFFFF00LL) return INFEROP_ERR_LIMIT;
+  if (!c || !a_q || !a_scales || !b_q || !b_scales) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(a_q) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  FixedScratchPtr fs;
+  const int rc = fixed_scratch_for_current_device(&fs);
+  if (rc != INFEROP_OK) return rc;
+  if (fs.sm_version != 100) return INFEROP_ERR_ARCH;
+  if (fs.sm_count > kFixedMaxCtas) return INFEROP_ERR_LIMIT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the last call left: the arrival counters must start at zero
+  const int64_t tiles = (n + TN - 1) / TN;
+  const cudaError_t e = cudaMemsetAsync(fs.ptr->counters, 0, static_cast<size_t>(tiles) * sizeof(int), s);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  DeviceCtx local;  // carries the SM count and the status slot to the launcher; owns nothing
+  local.ordinal = 0;
+  local.sm_version = fs.sm_version;
+  local.sm_count = fs.sm_count;
+  local.status = &fs.ptr->status;
+  return launch_gemm_decode(&local, fs.ptr->partials, fs.ptr->counters, c, a_q, a_scales, b_q, b_scales,
+                            m, n, k, out_dt, s);
+}
