@@ -42,6 +42,7 @@ def parse_args():
     ap.add_argument("--k", type=int, default=K_FULL)
     ap.add_argument("--gather", action="store_true", help="also time an NCCL all-gather of C")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the decode / prefill shape sweep (N=1 only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU-baseline sample budget")
     return ap.parse_args()
@@ -198,6 +199,64 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------------------------------------- shape sweep
+def shape_sweep(peaks):
+    """Decode (HBM-bound) and prefill (tensor-bound) shapes of the benchmark configs, quant + GEMM,
+    device-timed.  Small shapes are replayed from a CUDA graph of 10 steps so that host launch cost
+    does not enter; weights (>= 38 MB, up to 132 MB) are larger than or comparable to L2 and every
+    step re-reads them after the other tensors of the step went through the cache."""
+    import torch
+    from inference_b200 import ops, synth
+    out = []
+    shapes = [(m, n, k) for (n, k) in ((18432, 7168), (7168, 18432), (24576, 1536)) for m in (1, 4, 16, 64)]
+    shapes += [(m, n, k) for (n, k) in ((18432, 7168), (7168, 18432)) for m in (1024, 4096)]
+    weights = {}
+    for (m, n, k) in shapes:
+        if (n, k) not in weights:
+            weights.clear()
+            weights[(n, k)] = synth.quantised_weights(n, k, seed=5)
+        bq, bs = weights[(n, k)]
+        x = synth.activations(m, k, seed=6)
+        aq = torch.empty((m, k), dtype=torch.uint8, device="cuda")
+        a_s = torch.empty((m, k // 128), dtype=torch.float32, device="cuda")
+        c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+
+        def step():
+            ops.quant_fp8_per_token_group(x, 128, aq, a_s)
+            ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, out=c)
+
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()           # warm-up; also creates this stream's GEMM scratch before capture
+            torch.cuda.synchronize()
+            reps = 10 if m <= 64 else 3
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(reps):
+                    step()
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            for _ in range(3):
+                g.replay()
+            e1.record(side)
+            torch.cuda.synchronize()
+        t = e0.elapsed_time(e1) * 1e-3 / (3 * reps)
+        flops = 2.0 * m * n * k
+        byt = 3 * m * k + 4 * m * (k // 128) + m * k + 4 * m * (k // 128) + n * k + 4 * (n // 128) * (k // 128) + 2 * m * n
+        rec = {"m": m, "n": n, "k": k, "us": round(t * 1e6, 2), "tflops": round(flops / t / 1e12, 1),
+               "gbs": round(byt / t / 1e9, 1)}
+        t_roof = max(flops / (NOMINAL_FP8_TFLOPS * 1e12), byt / (NOMINAL_HBM_GBS * 1e9))
+        rec["frac_of_nominal_roofline"] = round(t_roof / t, 3)
+        if m <= 64:
+            rec["frac_of_measured_hbm"] = round(byt / t / 1e9 / peaks["hbm_gbs"], 3)
+        out.append(rec)
+        del g
+    return out
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def run_ours(args):
     import torch
@@ -275,7 +334,7 @@ def run_ours(args):
     # ---- optional all-gather of C (reported separately)
     gather = None
     if args.gather and world > 1:
-        c_all = torch.empty((world, m, n_loc), dtype=torch.bfloat16, device=dev)
+        c_all = torch.empty((world * m, n_loc), dtype=torch.bfloat16, device=dev)  # [G][M][N/G] rank-blocked
         for _ in range(2):
             dist.all_gather_into_tensor(c_all, c)
         sync_all()
@@ -368,6 +427,11 @@ def run_ours(args):
         line["e2e"] = e2e
     if gather:
         line["gather"] = gather
+    if world == 1 and not args.no_sweep:
+        del x, bq, bs, aq, a_s, c
+        torch.cuda.empty_cache()
+        line["sweep"] = {"what": "quant + GEMM per shape, device-timed (CUDA graph replay), bf16 out",
+                         "shapes": shape_sweep(peaks)}
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         smp = sized_cpu_sample(k, threads, args.cpu_seconds)

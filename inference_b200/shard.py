@@ -1,0 +1,48 @@
+"""Column-parallel (N-sharded) use of the blockwise-FP8 GEMM across the GPUs of one box.
+
+The reference has no multi-GPU code; this is the partition the benchmark configuration asks
+for: rank g of G owns weight rows [g*N/G, (g+1)*N/G) of ``b_q`` and the matching rows of
+``b_scales``; activations are replicated and quantised by every rank; each rank produces
+``C_g [M, N/G]``.  Output columns depend only on their own weight rows, so there is no data
+exchange on the compute path; the one optional collective is an all-gather of the outputs.
+
+Everything here is plain index arithmetic plus ``torch.distributed`` calls, so it runs on
+CPU ranks (gloo) as well as on GPUs (nccl).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+BLOCK = 128
+
+
+def shard_bounds(n: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [lo, hi) of the weight matrix owned by `rank`.  N must split into whole 128-row
+    scale blocks per rank so that no scale block straddles two ranks."""
+    if n % (BLOCK * world) != 0:
+        raise ValueError(f"N={n} does not split into {world} shards of whole {BLOCK}-row blocks")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_weights(b_q: torch.Tensor, b_scales: torch.Tensor, world: int, rank: int):
+    """This rank's slice of a full (b_q [N, K], b_scales [N/128, K/128]) pair."""
+    lo, hi = shard_bounds(b_q.shape[0], world, rank)
+    return b_q[lo:hi].contiguous(), b_scales[lo // BLOCK:hi // BLOCK].contiguous()
+
+
+def gather_outputs(c_local: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather of the per-rank outputs into the rank-blocked layout [G, M, N/G]
+    (each rank's panel contiguous, which is what one all-gather produces without a copy)."""
+    world = dist.get_world_size(group)
+    m, n_loc = c_local.shape
+    out = torch.empty((world * m, n_loc), dtype=c_local.dtype, device=c_local.device)
+    dist.all_gather_into_tensor(out, c_local.contiguous(), group=group)
+    return out.view(world, m, n_loc)
+
+
+def blocked_to_row_major(c_blocked: torch.Tensor) -> torch.Tensor:
+    """[G, M, N/G] -> [M, N] (a strided copy; only for consumers that need the flat layout)."""
+    g, m, n_loc = c_blocked.shape
+    return c_blocked.permute(1, 0, 2).reshape(m, g * n_loc)

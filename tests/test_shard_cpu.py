@@ -1,0 +1,61 @@
+"""N-sharding arithmetic and the gather layout, on two gloo ranks (CPU)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from inference_b200 import shard
+
+
+def test_shard_bounds_cover_n_in_whole_scale_blocks():
+    for n, g in [(73728, 8), (73728, 4), (73728, 2), (73728, 1), (1024, 2)]:
+        spans = [shard.shard_bounds(n, g, r) for r in range(g)]
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert all(lo % 128 == 0 and hi % 128 == 0 for lo, hi in spans)
+    with pytest.raises(ValueError):
+        shard.shard_bounds(1000, 2, 0)
+    with pytest.raises(ValueError):
+        shard.shard_bounds(128 * 3, 2, 0)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, m, n, k, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rng = np.random.default_rng(0)  # same inputs on every rank: A replicated, W sharded from one matrix
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = (0.02 * rng.standard_normal((n, k))).astype(np.float32)
+    aq, a_s = oracle.quant_fp8_per_token_group(a)
+    bq, bs = oracle.block_quant_weights(w)
+    bq_l, bs_l = shard.shard_weights(torch.from_numpy(bq), torch.from_numpy(bs), world, rank)
+    # the per-rank GEMM (the oracle stands in for the GPU kernel on CPU ranks)
+    c_l = torch.from_numpy(oracle.w8a8_block_fp8_gemm(aq, a_s, bq_l.numpy(), bs_l.numpy()))
+    blocked = shard.gather_outputs(c_l)
+    full = shard.blocked_to_row_major(blocked)
+    if rank == 0:
+        want = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs)
+        np.save(os.path.join(out_dir, "ok.npy"),
+                np.array([np.array_equal(full.numpy(), want), blocked.shape == (world, m, n // world)]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_sharded_gemm_and_gather_equals_unsharded(tmp_path):
+    world, m, n, k = 2, 8, 512, 256
+    mp.spawn(_worker, args=(world, _free_port(), m, n, k, str(tmp_path)), nprocs=world, join=True)
+    ok = np.load(tmp_path / "ok.npy")
+    assert ok.all()
