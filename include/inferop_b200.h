@@ -85,6 +85,20 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void
                                 int32_t group_size, int32_t block_n, int32_t out_dt,
                                 void* stream);
 
+/* ---- grouped blockwise-FP8 GEMM (MoE expert GEMMs in one launch)
+ * Equivalent to one inferop_w8a8_block_fp8_gemm call per group (which is how the reference runs
+ * expert GEMMs: include/inferop/ops.h:81-84 once per expert; a grouped GEMM is only on its
+ * roadmap, docs/ROADMAP.md:39):
+ *   for g in 0..groups-1:  C[r_g : r_g + m_g, :] = gemm(A_q[r_g : r_g + m_g], B_q[g], ...)
+ * with r_g the running sum of m_per_group.  a_q [sum m_g, K], a_scales [sum m_g, K/128] and
+ * c [sum m_g, N] hold the groups' rows one after the other; b_q is [groups, N, K] and b_scales
+ * [groups, N/128, K/128].  m_per_group is a HOST array of `groups` entries (zeros allowed) and
+ * is read before the call returns.  N % 128 == 0 is required in addition to the GEMM contract. */
+INFEROP_API int inferop_w8a8_block_fp8_gemm_grouped(void* c, const void* a_q, const void* a_scales, const void* b_q,
+                                        const void* b_scales, const int64_t* m_per_group,
+                                        int64_t groups, int64_t n, int64_t k, int32_t group_size,
+                                        int32_t block_n, int32_t out_dt, void* stream);
+
 /* ---- blockwise-FP8 GEMM for a few tokens, with no allocation
  * No counterpart in the reference: added for callers that must not trigger a device
  * allocation, such as a server that gave all device memory to its own pool at start-up, or a

@@ -246,6 +246,34 @@ int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, 
   return launch_gemm(ctx, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
 }
 
+int inferop_w8a8_block_fp8_gemm_grouped(void* c, const void* a_q, const void* a_scales, const void* b_q,
+                                        const void* b_scales, const int64_t* m_per_group,
+                                        int64_t groups, int64_t n, int64_t k, int32_t group_size,
+                                        int32_t block_n, int32_t out_dt, void* stream) {
+  if (group_size != 128 || block_n != 128 || k <= 0 || k % 128 != 0 || n <= 0 || n % 128 != 0 ||
+      groups <= 0 || !m_per_group) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (out_dt < 0 || out_dt > 2) return INFEROP_ERR_DTYPE;
+  int64_t m_total = 0;
+  for (int64_t g = 0; g < groups; ++g) {
+    if (m_per_group[g] < 0) return INFEROP_ERR_SHAPE;
+    m_total += m_per_group[g];
+  }
+  if (m_total > 0x7FFFFF00LL || groups * n > 0x7FFFFF00LL || k > 0x7FFFFF00LL || groups >= (1 << 22)) {
+    return INFEROP_ERR_LIMIT;
+  }
+  if (!c || !a_q || !a_scales || !b_q || !b_scales) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(a_q) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_gemm_grouped(ctx, c, a_q, a_scales, b_q, b_scales, m_per_group, groups, n, k, out_dt,
+                             static_cast<cudaStream_t>(stream));
+}
+
 int inferop_device_status(uint32_t* out4, int reset) {
   int err;
   DeviceCtx* ctx = current_ctx(&err);

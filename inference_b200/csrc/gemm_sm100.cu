@@ -89,6 +89,27 @@ enum : uint32_t {
   kSitePromoTmemFull = 0x301,
 };
 
+// Grouped (MoE) launches: the rows of A and C are the concatenation of the groups' rows, the
+// weights are [groups][N][K].  The host cuts every group into 128-row M-tiles and passes the
+// list by value; tile t of the launch is M-tile t / tiles_n, N-tile t % tiles_n.
+constexpr int kMaxGroupTiles = 2040;
+struct GroupTable {
+  int row0[kMaxGroupTiles];   // first row (in A and C) of the M-tile
+  int meta[kMaxGroupTiles];   // (group << 8) | (rows - 1): which group, how many valid rows
+};
+
+struct TileInfo {
+  int a_row;     // first row of the tile in A / a_scales / C
+  int row_end;   // rows at and beyond this index are not this tile's
+  int b_row;     // first row of the tile in the (stacked) weight matrix
+  int sb_row;    // row of b_scales for the tile's left half
+  int sb_rows;   // one past the last valid b_scales row for this tile's group
+  int col;       // first output column
+};
+
+template <bool kGrouped>
+__device__ __forceinline__ TileInfo tile_info(int t, const struct GemmParams& p, const GroupTable* tab);
+
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int per_band = kGroupM * tiles_n;
   const int band = t / per_band;
@@ -97,6 +118,32 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   const int r = t - band * per_band;
   tm = first_m + r % band_m;
   tn = r / band_m;
+}
+
+template <bool kGrouped>
+__device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p, const GroupTable* tab) {
+  TileInfo ti;
+  if (kGrouped) {
+    const int mt = t / p.tiles_n, tn = t - mt * p.tiles_n;
+    const int meta = tab->meta[mt];
+    const int group = meta >> 8;
+    ti.a_row = tab->row0[mt];
+    ti.row_end = ti.a_row + (meta & 0xFF) + 1;
+    ti.b_row = group * p.n + tn * BN;
+    ti.sb_row = group * p.nb + tn * 2;
+    ti.sb_rows = (group + 1) * p.nb;
+    ti.col = tn * BN;
+  } else {
+    int tm, tn;
+    tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+    ti.a_row = tm * BM;
+    ti.row_end = p.m;
+    ti.b_row = tn * BN;
+    ti.sb_row = tn * 2;
+    ti.sb_rows = p.nb;
+    ti.col = tn * BN;
+  }
+  return ti;
 }
 
 template <typename OutT>
@@ -148,10 +195,10 @@ __device__ __forceinline__ void promote32(float2* acc, const uint32_t (&v)[32], 
   }
 }
 
-template <typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
-w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+template <typename OutT, bool kGrouped>
+__device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtensorMap* map_b,
+                                          const CUtensorMap* map_c, const GemmParams& p,
+                                          const GroupTable* tab) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -179,9 +226,9 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     *abort_flag = 0u;
     mbar_init_fence();
-    tma_prefetch_desc(&map_a);
-    tma_prefetch_desc(&map_b);
-    if (p.tma_store) tma_prefetch_desc(&map_c);
+    tma_prefetch_desc(map_a);
+    tma_prefetch_desc(map_b);
+    if (p.tma_store) tma_prefetch_desc(map_c);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -202,8 +249,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t armed = 0, armed_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
-        int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        const TileInfo ti = tile_info<kGrouped>(t, p, tab);
         for (int kb = 0; kb < p.kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty)) {
             ok = false;
@@ -211,8 +257,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           uint8_t* sa = smem + stage * kStageBytes;
           mbar_arrive_expect_tx(&full[stage], kStageBytes);
-          tma_load_2d(sa, &map_a, &full[stage], kb * BK, tm * BM);
-          tma_load_2d(sa + kBytesA, &map_b, &full[stage], kb * BK, tn * BN);
+          tma_load_2d(sa, map_a, &full[stage], kb * BK, ti.a_row);
+          tma_load_2d(sa + kBytesA, map_b, &full[stage], kb * BK, ti.b_row);
           armed |= 1u << stage;
           armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
           if (++stage == kStages) {
@@ -285,11 +331,13 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint32_t kiter = 0;
     bool ok = true;
     for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
-      int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-      const int gm = tm * BM + row;
-      const int nbi = tn * 2 + half;
-      const bool have = gm < p.m && nbi < p.nb;
+      const TileInfo ti = tile_info<kGrouped>(t, p, tab);
+      const int gm = ti.a_row + row;
+      const int nbi = ti.sb_row + half;
+      const bool have = gm < ti.row_end && nbi < ti.sb_rows;
+      // a TMA store writes whole 128-row boxes (clipped only at the end of C): a grouped tile
+      // with fewer rows must not spill into the next group's rows
+      const bool tma_store = p.tma_store && (!kGrouped || ti.row_end - ti.a_row == BM);
       const float* sa_ptr = p.a_scales + static_cast<int64_t>(have ? gm : 0) * p.kb;
       const float* sb_ptr = p.b_scales + static_cast<int64_t>(have ? nbi : 0) * p.kb;
 
@@ -333,8 +381,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         const float* accf = reinterpret_cast<const float*>(acc) + ch * 64;
-        const int col0 = tn * BN + half * BH + ch * 64;
-        if (sizeof(OutT) == 2 && p.tma_store) {
+        const int col0 = ti.col + half * BH + ch * 64;
+        if (sizeof(OutT) == 2 && tma_store) {
           // the staging buffer may still be read by the previous TMA store
           if (issuer) tma_store_wait_read0();
           named_bar_sync(1 + half, 128);
@@ -352,10 +400,10 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           fence_proxy_async_smem();
           named_bar_sync(1 + half, 128);
           if (issuer && col0 < p.n) {
-            tma_store_2d(&map_c, my_buf, col0, tm * BM);
+            tma_store_2d(map_c, my_buf, col0, ti.a_row);
             tma_store_commit();
           }
-        } else if (gm < p.m) {
+        } else if (gm < ti.row_end) {
           OutT* crow = static_cast<OutT*>(p.c) + static_cast<int64_t>(gm) * p.n;
           constexpr int kVec = 16 / sizeof(OutT);
           // fully unrolled: the accumulators must stay in registers
@@ -383,6 +431,37 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+  gemm_body<OutT, false>(&map_a, &map_b, &map_c, p, nullptr);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_c, const GemmParams p,
+                         const __grid_constant__ GroupTable tab) {
+  gemm_body<OutT, true>(&map_a, &map_b, &map_c, p, &tab);
+}
+
+template <typename OutT>
+int launch_grouped_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                     const GemmParams& p, const GroupTable& tab, int ctas, cudaStream_t stream) {
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(w8a8_grouped_gemm_kernel<OutT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_done[dev] = true;
+  }
+  w8a8_grouped_gemm_kernel<OutT><<<ctas, kThreads, kSmemBytes, stream>>>(ma, mb, mc, p, tab);
+  return check_launch();
 }
 
 template <typename OutT>
@@ -449,6 +528,76 @@ int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, 
     case 2: return launch_t<__nv_bfloat16>(ma, mb, mc, p, ctas, stream);
     default: return INFEROP_ERR_DTYPE;
   }
+}
+
+int launch_gemm_grouped(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales,
+                        const void* b_q, const void* b_scales, const int64_t* m_per_group,
+                        int64_t groups, int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream) {
+  const Options& opt = options();
+  const int out_bytes = (out_dt == 0) ? 4 : 2;
+  int64_t m_total = 0;
+  for (int64_t g = 0; g < groups; ++g) m_total += m_per_group[g];
+  if (m_total == 0) return INFEROP_OK;
+  bool tma_store = out_bytes == 2 && (n * out_bytes) % 16 == 0 &&
+                   (reinterpret_cast<uintptr_t>(c) % 16 == 0);
+  if (opt.gemm_tma_store == 0) tma_store = false;
+
+  // cut the groups into M-tiles; launch in chunks when the list outgrows one parameter block
+  static thread_local GroupTable tab;
+  GemmParams p;
+  p.a_scales = static_cast<const float*>(a_scales);
+  p.b_scales = static_cast<const float*>(b_scales);
+  p.c = c;
+  p.m = static_cast<int>(m_total);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.kb = static_cast<int>(k / 128);
+  p.nb = static_cast<int>(n / 128);
+  p.tiles_n = static_cast<int>((n + BN - 1) / BN);
+  p.tma_store = tma_store ? 1 : 0;
+  p.status = ctx->status;
+
+  CUtensorMap ma, mb, mc;
+  int rc = make_tensor_map_2d(&ma, a_q, 1, m_total, k, k, BM, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  rc = make_tensor_map_2d(&mb, b_q, 1, groups * n, k, k, BN, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  if (tma_store) {
+    rc = make_tensor_map_2d(&mc, c, 2, m_total, n, n * 2, 128, 64, true);
+    if (rc != INFEROP_OK) return rc;
+  } else {
+    mc = ma;
+  }
+  auto flush = [&](int n_mtiles) -> int {
+    if (n_mtiles == 0) return INFEROP_OK;
+    p.tiles_m = n_mtiles;
+    p.num_tiles = n_mtiles * p.tiles_n;
+    int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
+    if (ctas > p.num_tiles) ctas = p.num_tiles;
+    switch (out_dt) {
+      case 0: return launch_grouped_t<float>(ma, mb, mc, p, tab, ctas, stream);
+      case 1: return launch_grouped_t<__half>(ma, mb, mc, p, tab, ctas, stream);
+      case 2: return launch_grouped_t<__nv_bfloat16>(ma, mb, mc, p, tab, ctas, stream);
+      default: return INFEROP_ERR_DTYPE;
+    }
+  };
+  int count = 0;
+  int64_t row = 0;
+  for (int64_t g = 0; g < groups; ++g) {
+    for (int64_t r = 0; r < m_per_group[g]; r += BM) {
+      if (count == kMaxGroupTiles) {
+        rc = flush(count);
+        if (rc != INFEROP_OK) return rc;
+        count = 0;
+      }
+      const int64_t rows = (m_per_group[g] - r) < BM ? (m_per_group[g] - r) : BM;
+      tab.row0[count] = static_cast<int>(row + r);
+      tab.meta[count] = static_cast<int>((g << 8) | (rows - 1));
+      ++count;
+    }
+    row += m_per_group[g];
+  }
+  return flush(count);
 }
 
 }  // namespace ib200

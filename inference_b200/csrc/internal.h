@@ -55,6 +55,12 @@ int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, 
                 const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
                 cudaStream_t stream);
 
+// Grouped launch: group g has m_per_group[g] (host array) rows of A / C, stacked in group
+// order; b_q is [groups][n][k], b_scales [groups][n/128][k/128].
+int launch_gemm_grouped(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales,
+                        const void* b_q, const void* b_scales, const int64_t* m_per_group,
+                        int64_t groups, int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream);
+
 // gemm_decode_sm100.cu : small-M path (M <= kDecodeMaxM).  workspace holds
 // decode_workspace_bytes(sm_count) bytes, counters kDecodeMaxTiles zeroed ints; both are
 // owned by the caller of launch_gemm_decode and must not be shared by launches that can

@@ -118,6 +118,32 @@ def w8a8_block_fp8_gemm(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: torch.Te
     return out
 
 
+def w8a8_block_fp8_gemm_grouped(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: torch.Tensor,
+                                b_scales: torch.Tensor, m_per_group, out_dtype=torch.bfloat16,
+                                out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """All groups' (MoE experts') GEMMs in one launch; same result as one call per group.
+
+    a_q [sum(m_g), K], a_scales [sum(m_g), K/128]: the groups' rows stacked in group order;
+    b_q [G, N, K], b_scales [G, N/128, K/128]; m_per_group: host sequence of G row counts.
+    """
+    for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
+        _dev_tensor(t, name)
+    groups, n, k = b_q.shape
+    counts = (C.c_int64 * groups)(*[int(v) for v in m_per_group])
+    m_total = int(sum(counts))
+    if a_q.shape != (m_total, k):
+        raise ValueError("a_q does not hold sum(m_per_group) rows of K bytes")
+    with torch.cuda.device(a_q.device):
+        if out is None:
+            out = torch.empty((m_total, n), dtype=out_dtype, device=a_q.device)
+        check(lib.inferop_w8a8_block_fp8_gemm_grouped(out.data_ptr(), a_q.data_ptr(), a_scales.data_ptr(),
+                                                      b_q.data_ptr(), b_scales.data_ptr(), counts, groups,
+                                                      n, k, 128, 128, int(_TORCH2CODE[out.dtype]),
+                                                      _stream_ptr(stream)),
+              "w8a8_block_fp8_gemm_grouped")
+    return out
+
+
 def device_status(reset: bool = True):
     """Synchronise and return the device-side status record (code, block, aux0, aux1)."""
     rec = (C.c_uint32 * 4)()

@@ -230,3 +230,56 @@ def test_small_m_path_on_the_decode_shapes(ops, m, n, k):
     idx = torch.from_numpy(cols).cuda()
     check(c1[:, idx].cpu().numpy(), want, torch.float32)
     check(cb[:, idx].float().cpu().numpy(), want, torch.bfloat16)
+
+
+# ------------------------------------------------------------------ grouped (MoE) launch
+def test_grouped_launch_equals_one_call_per_group(ops):
+    """Variable rows per group incl. empty groups, tiles that end inside a 128-row box, and a
+    group larger than one tile: identical bits to per-group calls, and within tolerance of the
+    fp64 golden."""
+    rng = np.random.default_rng(77)
+    groups, n, k = 9, 512, 768
+    counts = [0, 5, 128, 200, 1, 0, 131, 64, 300]
+    m_total = sum(counts)
+    a = oracle.bf16_widen(oracle.bf16_narrow(rng.standard_normal((m_total, k)).astype(np.float32)))
+    aq, a_s = oracle.quant_fp8_per_token_group(a)
+    bqs, bss = [], []
+    for g in range(groups):
+        w = oracle.bf16_widen(oracle.bf16_narrow((0.02 * rng.standard_normal((n, k))).astype(np.float32)))
+        q, s = oracle.block_quant_weights(w)
+        bqs.append(q)
+        bss.append(s)
+    bq, bs = np.stack(bqs), np.stack(bss)
+    d_aq, d_as, d_bq, d_bs = cuda(aq), cuda(a_s), cuda(bq), cuda(bs)
+    for dt in (torch.bfloat16, torch.float32):
+        canary = torch.full((m_total * n + 1024,), -3.0, dtype=dt, device="cuda")
+        out = canary[:m_total * n].view(m_total, n)
+        ops.w8a8_block_fp8_gemm_grouped(d_aq, d_as, d_bq, d_bs, counts, out=out)
+        assert ops.device_status()[0] == 0
+        assert bool((canary[m_total * n:] == -3.0).all())
+        r = 0
+        for g, mg in enumerate(counts):
+            if mg == 0:
+                continue
+            ops.set_option("gemm_path", 1)   # the same (large-tile) kernel as the grouped launch
+            try:
+                single = ops.w8a8_block_fp8_gemm(d_aq[r:r + mg], d_as[r:r + mg], d_bq[g], d_bs[g], dt)
+            finally:
+                ops.set_option("gemm_path", 0)
+            assert torch.equal(out[r:r + mg], single), f"group {g} differs from its own call"
+            want = oracle.w8a8_block_fp8_gemm(aq[r:r + mg], a_s[r:r + mg], bq[g], bs[g], threads=8)
+            check(out[r:r + mg].float().cpu().numpy(), want, dt)
+            r += mg
+
+
+def test_grouped_launch_rejects_bad_arguments(ops):
+    import ctypes as C
+    from inference_b200 import _capi
+    t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p = t.data_ptr()
+    counts = (C.c_int64 * 2)(4, 4)
+    lib = _capi.lib
+    assert lib.inferop_w8a8_block_fp8_gemm_grouped(p, p, p, p, p, counts, 2, 200, 128, 128, 128, 2, None) == _capi.ERR_SHAPE
+    assert lib.inferop_w8a8_block_fp8_gemm_grouped(p, p, p, p, p, None, 2, 256, 128, 128, 128, 2, None) == _capi.ERR_SHAPE
+    bad = (C.c_int64 * 2)(4, -1)
+    assert lib.inferop_w8a8_block_fp8_gemm_grouped(p, p, p, p, p, bad, 2, 256, 128, 128, 128, 2, None) == _capi.ERR_SHAPE
