@@ -26,6 +26,8 @@ SIGNATURES = {
     "inferop_dequant_fp8_per_token_group": (C.c_int, [_vp, _i32, _vp, _vp, _i64, _i64, _i32, _vp]),
     "inferop_w8a8_block_fp8_gemm": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32,
                                               _i32, _vp]),
+    "inferop_w8a8_block_fp8_gemm_fused_quant": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _i32, _i32,
+                                                          _i32, _vp]),
     "inferop_w8a8_block_fp8_gemm_grouped": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.POINTER(_i64), _i64, _i64, _i64,
                                                       _i32, _i32, _i32, _vp]),
     "inferop_w8a8_block_fp8_gemm_fixed_scratch": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,

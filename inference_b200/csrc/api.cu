@@ -246,6 +246,29 @@ int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, 
   return launch_gemm(ctx, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
 }
 
+int inferop_w8a8_block_fp8_gemm_fused_quant(void* c, const void* a, int32_t a_dt, const void* b_q,
+                                            const void* b_scales, int64_t m, int64_t n, int64_t k,
+                                            int32_t group_size, int32_t block_n, int32_t out_dt,
+                                            void* stream) {
+  if (group_size != 128 || block_n != 128 || k <= 0 || k % 128 != 0 || m <= 0 || n <= 0) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (out_dt < 0 || out_dt > 2 || (a_dt != 1 && a_dt != 2)) return INFEROP_ERR_DTYPE;
+  if (m > kFusedMaxM || (n + 127) / 128 > kDecodeMaxTiles || k > 0x7FFFFF00LL) return INFEROP_ERR_LIMIT;
+  if (!c || !a || !b_q || !b_scales) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ws = nullptr;
+  int* counters = nullptr;
+  if (!decode_scratch(ctx, s, &ws, &counters)) return INFEROP_ERR_CUDA;
+  return launch_gemm_decode_fused(ctx, ws, counters, c, a, a_dt, b_q, b_scales, m, n, k, out_dt, s);
+}
+
 int inferop_w8a8_block_fp8_gemm_grouped(void* c, const void* a_q, const void* a_scales, const void* b_q,
                                         const void* b_scales, const int64_t* m_per_group,
                                         int64_t groups, int64_t n, int64_t k, int32_t group_size,

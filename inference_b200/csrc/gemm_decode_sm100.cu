@@ -34,8 +34,10 @@
 #include <stdint.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "internal.h"
+#include "quant_math.cuh"
 
 namespace ib200 {
 namespace {
@@ -43,6 +45,7 @@ namespace {
 constexpr int TN = 128;   // weight rows per tile (UMMA M)
 constexpr int BK = 128;
 constexpr int kThreads = 256;
+constexpr int kFusedThreads = 384;   // fused prologue: four more warps that quantise the token tile
 constexpr int kBytesW = TN * BK;
 
 template <int MP>
@@ -59,6 +62,7 @@ struct DCfg {
 
 struct DecodeParams {
   const float* a_scales;   // [M, KB]
+  const void* a_src;       // fused prologue only: unquantised activations [M, K] (bf16 / fp16)
   const float* b_scales;   // [ceil(N/128), KB]
   void* c;                 // [M, N]
   float* workspace;        // [gridDim.x][MP][128] fp32 partials
@@ -76,6 +80,8 @@ enum : uint32_t {
   kSiteDScaleEmpty = 0x411,
   kSiteDPromoFull = 0x311,
   kSiteDPromoScale = 0x312,
+  kSiteDQuantEmpty = 0x511,
+  kSiteDQuantTmem = 0x512,
 };
 
 template <typename OutT>
@@ -101,11 +107,43 @@ __device__ __forceinline__ void tmem_wait_pin(uint32_t (&r)[N]) {
   for (int i = 0; i < N; ++i) asm volatile("" : "+r"(r[i])::"memory");
 }
 
-template <int MP, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+// 8 consecutive 16-bit activations -> 8 floats
+template <typename AT>
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]);
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& raw, float (&f)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4& raw, float (&f)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <>
+__device__ __forceinline__ void unpack8<void>(const uint4&, float (&)[8]) {}
+
+// AT = void: the token tile arrives quantised through TMA and a scale warp prepares the scale
+// vectors.  AT = bf16 / fp16 (the fused prologue): warps 8-11 quantise the token tile of
+// every unit themselves, straight from the unquantised activations, into the swizzled layout a
+// TMA load would have produced, and write the scale vectors; the stand-alone quantisation
+// kernel and its q / scales round trip through HBM disappear.
+template <int MP, typename OutT, typename AT>
+__global__ void __launch_bounds__(std::is_same<AT, void>::value ? kThreads : kFusedThreads, 1)
 w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                    const DecodeParams p) {
   using C = DCfg<MP>;
+  constexpr bool kFused = !std::is_same<AT, void>::value;
+  constexpr int kQuantWarps = 4;
   constexpr int CH = (MP < 32) ? MP : 32;   // columns per tensor-memory load
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -126,7 +164,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], kFused ? 2 : 1);
       mbar_init(&empty[s], 1);
     }
     for (int b = 0; b < C::kBufs; ++b) {
@@ -137,7 +175,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     *abort_flag = 0u;
     mbar_init_fence();
     tma_prefetch_desc(&map_w);
-    tma_prefetch_desc(&map_a);
+    if (!kFused) tma_prefetch_desc(&map_a);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, C::kTmemCols);
@@ -178,9 +216,9 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       __syncwarp();
       uint8_t* dst = smem + stage * C::kStageBytes;
       if (elect_one()) {
-        mbar_arrive_expect_tx(&full[stage], C::kStageBytes);
+        mbar_arrive_expect_tx(&full[stage], kFused ? kBytesW : C::kStageBytes);
         tma_load_2d(dst, &map_w, &full[stage], kb * BK, t * TN);
-        tma_load_2d(dst + kBytesW, &map_a, &full[stage], kb * BK, 0);
+        if (!kFused) tma_load_2d(dst + kBytesW, &map_a, &full[stage], kb * BK, 0);
       }
       __syncwarp();
       armed = i + 1;
@@ -229,7 +267,77 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
       __syncwarp();
     }
-  } else if (warp == 2) {
+  } else if (kFused && warp >= 8) {
+    // ------------------------------ quantising prologue (fused) -----------
+    // A half warp owns one token row of the unit: 16 lanes x 8 elements = the 128-wide group.
+    // Row r of step s: r = 2 * (qw + kQuantWarps * s) + half_warp.  The activations of the
+    // next two units are always in flight (registers cur / nx1 / nx2), because the round trip
+    // to L2 is longer than the time one unit takes.
+    if constexpr (kFused) {
+      // Each of the four warps takes every fourth unit whole (all MP token rows, two per
+      // step), so that the per-unit costs (barrier probes, proxy fence, arrivals) are paid by
+      // one warp per unit, and it has four unit times to do the work.  The activations of its
+      // next unit are in flight while it quantises the current one.
+      constexpr int STEPS = MP / 2;
+      const int qw = warp - 8, hw = lane >> 4, sub = lane & 15;
+      const AT* src = static_cast<const AT*>(p.a_src);
+      const int64_t ld = static_cast<int64_t>(p.kb) * BK;
+      uint4 cur[STEPS], nxt[STEPS];
+      auto fetch = [&](uint4 (&dst)[STEPS], uint32_t unit) {
+        // unit -> K block (the token tile does not depend on the weight tile)
+        const int kbx = static_cast<int>((static_cast<uint32_t>(kb_first) + unit) % static_cast<uint32_t>(p.kb));
+#pragma unroll
+        for (int s2 = 0; s2 < STEPS; ++s2) {
+          const int r = 2 * s2 + hw;
+          dst[s2] = (r < p.m && unit < count)
+                        ? __ldg(reinterpret_cast<const uint4*>(src + r * ld + kbx * BK + sub * 8))
+                        : make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      fetch(cur, qw);
+      for (uint32_t i = qw; i < count; i += kQuantWarps) {
+        fetch(nxt, i + kQuantWarps);
+        const uint32_t stage = i % C::kStages;
+        const uint32_t phase = (i / C::kStages) & 1u;
+        const uint32_t buf = i % C::kBufs;
+        const uint32_t use = i / C::kBufs;
+        const uint32_t lin = static_cast<uint32_t>(kb_first) + i;
+        const int t = t_first + static_cast<int>(lin / static_cast<uint32_t>(p.kb));
+        const int kb = static_cast<int>(lin % static_cast<uint32_t>(p.kb));
+        const float sb = __ldg(p.b_scales + static_cast<int64_t>(t) * p.kb + kb);
+        if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteDQuantEmpty)) break;
+        if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, kSiteDQuantTmem)) break;
+        __syncwarp();
+        uint8_t* tile = smem + stage * C::kStageBytes + kBytesW;
+#pragma unroll
+        for (int s2 = 0; s2 < STEPS; ++s2) {
+          const int r = 2 * s2 + hw;
+          float f[8];
+          unpack8<AT>(cur[s2], f);
+          float amax = 0.0f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+          const float scale = group_scale(amax);
+          const uint2 bytes = fast_div_ok(amax) ? quantise8<true>(f, scale, __frcp_rn(scale))
+                                                : quantise8<false>(f, scale, 0.0f);
+          // swizzled K-major layout of a TMA SWIZZLE_128B load: 16-byte chunk c of row r sits at
+          // chunk c ^ (r & 7); this lane's 8 bytes are half of chunk sub / 2
+          *reinterpret_cast<uint2*>(tile + r * 128 + (((sub >> 1) ^ (r & 7)) << 4) + ((sub & 1) << 3)) = bytes;
+          if (sub == 0) sv[buf * MP + r] = (r < p.m) ? scale * sb : 0.0f;
+        }
+        fence_proxy_async_smem();   // the tensor core reads the tile through the async proxy
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&full[stage]);
+          mbar_arrive(&sv_full[buf]);
+        }
+#pragma unroll
+        for (int s2 = 0; s2 < STEPS; ++s2) cur[s2] = nxt[s2];
+      }
+    }
+  } else if (!kFused && warp == 2) {
     // ------------------------------ scale warp ----------------------------
     int t = t_first, kb = kb_first;
     for (uint32_t i = 0; i < count; ++i) {
@@ -252,7 +360,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         ++t;
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 4 && warp < 8) {
     // ------------------------------ promotion + epilogue ------------------
     const int quarter = warp - 4;            // == warp % 4: TMEM lane quarter
     const int row = quarter * 32 + lane;     // weight row inside the tile
@@ -274,18 +382,31 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       __syncwarp();
       tc_fence_after_sync();
       const float4* svb = reinterpret_cast<const float4*>(sv + buf * MP);
+      // all loads of up to 64 columns are issued before the single wait, so that their
+      // latencies overlap; 128 columns go in two such halves (register budget)
+      constexpr int HALF = (MP < 64) ? MP : 64;
 #pragma unroll
-      for (int c0 = 0; c0 < MP; c0 += CH) {
-        uint32_t v[CH];
-        tmem_ld_cols<CH>(lane_base + buf * MP + c0, v);
-        tmem_wait_pin<CH>(v);
+      for (int h0 = 0; h0 < MP; h0 += HALF) {
+        uint32_t v[HALF / CH][CH];
 #pragma unroll
-        for (int j = 0; j < CH; j += 4) {
-          const float4 s4 = svb[(c0 + j) >> 2];
-          acc[c0 + j + 0] = fmaf(__uint_as_float(v[j + 0]), s4.x, acc[c0 + j + 0]);
-          acc[c0 + j + 1] = fmaf(__uint_as_float(v[j + 1]), s4.y, acc[c0 + j + 1]);
-          acc[c0 + j + 2] = fmaf(__uint_as_float(v[j + 2]), s4.z, acc[c0 + j + 2]);
-          acc[c0 + j + 3] = fmaf(__uint_as_float(v[j + 3]), s4.w, acc[c0 + j + 3]);
+        for (int q = 0; q < HALF / CH; ++q) tmem_ld_cols<CH>(lane_base + buf * MP + h0 + q * CH, v[q]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < HALF / CH; ++q) {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) asm volatile("" : "+r"(v[q][j])::"memory");
+        }
+#pragma unroll
+        for (int q = 0; q < HALF / CH; ++q) {
+#pragma unroll
+          for (int j = 0; j < CH; j += 4) {
+            const int c = h0 + q * CH + j;
+            const float4 s4 = svb[c >> 2];
+            acc[c + 0] = fmaf(__uint_as_float(v[q][j + 0]), s4.x, acc[c + 0]);
+            acc[c + 1] = fmaf(__uint_as_float(v[q][j + 1]), s4.y, acc[c + 1]);
+            acc[c + 2] = fmaf(__uint_as_float(v[q][j + 2]), s4.z, acc[c + 2]);
+            acc[c + 3] = fmaf(__uint_as_float(v[q][j + 3]), s4.w, acc[c + 3]);
+          }
         }
       }
       tc_fence_before_sync();
@@ -350,7 +471,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
 }
 
-template <int MP, typename OutT>
+template <int MP, typename OutT, typename AT = void>
 int launch_decode_t(const CUtensorMap& mw, const CUtensorMap& ma, const DecodeParams& p, int ctas,
                     cudaStream_t stream) {
   using C = DCfg<MP>;
@@ -358,13 +479,30 @@ int launch_decode_t(const CUtensorMap& mw, const CUtensorMap& ma, const DecodePa
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(w8a8_decode_kernel<MP, OutT>,
+    cudaError_t e = cudaFuncSetAttribute(w8a8_decode_kernel<MP, OutT, AT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return note_cuda_error(e);
     attr_done[dev] = true;
   }
-  w8a8_decode_kernel<MP, OutT><<<ctas, kThreads, C::kSmemBytes, stream>>>(mw, ma, p);
+  w8a8_decode_kernel<MP, OutT, AT><<<ctas, std::is_same<AT, void>::value ? kThreads : kFusedThreads, C::kSmemBytes, stream>>>(mw, ma, p);
   return check_launch();
+}
+
+template <typename OutT, typename AT>
+int launch_decode_fused_mp(int mp, const CUtensorMap& mw, const DecodeParams& p, int ctas,
+                           cudaStream_t stream) {
+  return mp == 16 ? launch_decode_t<16, OutT, AT>(mw, mw, p, ctas, stream)
+                  : launch_decode_t<32, OutT, AT>(mw, mw, p, ctas, stream);
+}
+template <typename AT>
+int launch_decode_fused_out(int out_dt, int mp, const CUtensorMap& mw, const DecodeParams& p, int ctas,
+                            cudaStream_t stream) {
+  switch (out_dt) {
+    case 0: return launch_decode_fused_mp<float, AT>(mp, mw, p, ctas, stream);
+    case 1: return launch_decode_fused_mp<__half, AT>(mp, mw, p, ctas, stream);
+    case 2: return launch_decode_fused_mp<__nv_bfloat16, AT>(mp, mw, p, ctas, stream);
+    default: return INFEROP_ERR_DTYPE;
+  }
 }
 
 template <typename OutT>
@@ -382,11 +520,50 @@ int launch_decode_mp(int mp, const CUtensorMap& mw, const CUtensorMap& ma, const
 
 size_t decode_workspace_bytes(int ctas) { return static_cast<size_t>(ctas) * kDecodeMaxM * TN * 4; }
 
+int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, void* c, const void* a,
+                             int32_t a_dt, const void* b_q, const void* b_scales, int64_t m, int64_t n,
+                             int64_t k, int32_t out_dt, cudaStream_t stream) {
+  const int mp = m <= 16 ? 16 : 32;
+  DecodeParams p;
+  p.a_scales = nullptr;
+  p.a_src = a;
+  p.b_scales = static_cast<const float*>(b_scales);
+  p.c = c;
+  p.workspace = workspace;
+  p.counters = counters;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.kb = static_cast<int>(k / 128);
+  p.n_tiles = static_cast<int>((n + TN - 1) / TN);
+  p.units = static_cast<long long>(p.n_tiles) * p.kb;
+  p.status = ctx->status;
+  CUtensorMap mw;
+  const int rc = make_tensor_map_2d(&mw, b_q, 1, n, k, k, TN, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  const Options& opt = options();
+  int max_ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
+  if (max_ctas > ctx->sm_count) max_ctas = ctx->sm_count;
+  int ctas;
+  if (p.n_tiles >= max_ctas) {
+    p.splits = 1;
+    ctas = max_ctas;
+  } else {
+    p.splits = max_ctas / p.n_tiles;
+    if (p.splits > p.kb) p.splits = p.kb;
+    if (opt.decode_splits > 0 && opt.decode_splits <= p.splits) p.splits = opt.decode_splits;
+    ctas = p.n_tiles * p.splits;
+  }
+  if (a_dt == 2) return launch_decode_fused_out<__nv_bfloat16>(out_dt, mp, mw, p, ctas, stream);
+  if (a_dt == 1) return launch_decode_fused_out<__half>(out_dt, mp, mw, p, ctas, stream);
+  return INFEROP_ERR_DTYPE;
+}
+
 int launch_gemm_decode(DeviceCtx* ctx, float* workspace, int* counters, void* c, const void* a_q,
                        const void* a_scales, const void* b_q, const void* b_scales, int64_t m,
                        int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream) {
   const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
   DecodeParams p;
+  p.a_src = nullptr;
   p.a_scales = static_cast<const float*>(a_scales);
   p.b_scales = static_cast<const float*>(b_scales);
   p.c = c;

@@ -72,6 +72,12 @@ int launch_gemm_decode(DeviceCtx* ctx, float* workspace, int* counters, void* c,
                        const void* a_scales, const void* b_q, const void* b_scales, int64_t m,
                        int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream);
 
+// Fused prologue: `a` holds unquantised activations (a_dt 1 = fp16, 2 = bf16), M <= kFusedMaxM.
+constexpr int kFusedMaxM = 32;
+int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, void* c, const void* a,
+                             int32_t a_dt, const void* b_q, const void* b_scales, int64_t m, int64_t n,
+                             int64_t k, int32_t out_dt, cudaStream_t stream);
+
 // tensormap.cu : cuTensorMapEncodeTiled through the runtime's driver entry point.
 // 2-D row-major tensor [rows, cols] of elem_bytes-wide elements with row pitch
 // pitch_bytes; box = [box_rows, box_cols]; 128-byte swizzle when swizzle128.

@@ -26,6 +26,7 @@
 
 #include "inferop/fp8.h"
 #include "internal.h"
+#include "quant_math.cuh"
 
 namespace ib200 {
 namespace {
@@ -80,60 +81,6 @@ struct Vec8<float> {
   }
 };
 
-// Two floats -> two E4M3 bytes (low byte = a) with the hardware converter:
-// round to nearest even, saturate to +-448.
-__device__ __forceinline__ uint32_t cvt2(float a, float b) {
-  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
-}
-
-// Rare path: a quotient was NaN.  The hardware converter writes 0x7F for any
-// NaN; the reference keeps the sign of a NaN input and, for the invalid
-// operation Inf/Inf (an infinite group maximum), produces the x86 default NaN,
-// whose sign bit is set.
-__device__ __forceinline__ uint32_t nan_byte(float x) {
-  return (x != x) ? (0x7Fu | ((__float_as_uint(x) >> 24) & 0x80u)) : 0xFFu;
-}
-
-// x / scale, correctly rounded, from a correctly rounded reciprocal rcp = RN(1/scale):
-// q0 = RN(x * rcp) is within an ulp or so of the quotient, the residual x - q0 * scale is
-// exact in one FMA, and adding residual * rcp back lands on RN(x / scale).  Used only where
-// kFastDivOk says the operands are far from overflow and underflow, and only for 16-bit
-// inputs, for which the whole domain (every group maximum x every element value) is checked
-// against __fdiv_rn by inferop_selftest_quant_div.
-__device__ __forceinline__ float div_by_rcp(float x, float scale, float rcp) {
-  const float q0 = __fmul_rn(x, rcp);
-  // the residual is kept negated (q0 * scale - x) so that a zero x keeps its sign:
-  // (-0) - (-0) * ... ends in -0 + -0 = -0, where x - q0 * scale would give +0
-  const float neg_r = __fmaf_rn(q0, scale, -x);
-  return __fmaf_rn(-neg_r, rcp, q0);
-}
-// amax in [2^-100, 2^127): scale, its reciprocal, every quotient and every residual are
-// normal numbers
-__device__ __forceinline__ bool fast_div_ok(float amax) {
-  return amax >= 7.888609052e-31f && amax < 1.701411835e38f;
-}
-
-template <bool kFast>
-__device__ __forceinline__ uint2 quantise8(const float (&f)[8], float scale, float rcp) {
-  float q[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = kFast ? div_by_rcp(f[i], scale, rcp) : __fdiv_rn(f[i], scale);
-  uint32_t w0 = cvt2(q[0], q[1]) | (cvt2(q[2], q[3]) << 16);
-  uint32_t w1 = cvt2(q[4], q[5]) | (cvt2(q[6], q[7]) << 16);
-  // any byte equal to 0x7F / 0xFF marks a NaN quotient
-  if (__vcmpeq4(w0 & 0x7F7F7F7Fu, 0x7F7F7F7Fu) | __vcmpeq4(w1 & 0x7F7F7F7Fu, 0x7F7F7F7Fu)) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (q[i] != q[i]) {
-        uint32_t& w = (i < 4) ? w0 : w1;
-        const int sh = (i & 3) * 8;
-        w = (w & ~(0xFFu << sh)) | (nan_byte(f[i]) << sh);
-      }
-    }
-  }
-  return make_uint2(w0, w1);
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 quant128_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, const T* __restrict__ x,
@@ -168,7 +115,7 @@ quant128_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, const T* __
       for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-      const float scale = (amax == 0.0f) ? 1.0f : __fmul_rn(amax, 1.0f / 448.0f);
+      const float scale = group_scale(amax);
       if (live[u]) {
         uint2 bytes;
         // 16-bit inputs whose group maximum is far from the ends of the fp32 range divide
@@ -209,7 +156,7 @@ quant_any_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, const T* _
     for (int i = lane; i < gs; i += 32) amax = fmaxf(amax, fabsf(widen(gx[i])));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    const float scale = (amax == 0.0f) ? 1.0f : __fmul_rn(amax, 1.0f / 448.0f);
+    const float scale = group_scale(amax);
     if (lane == 0) scales[g] = scale;
     for (int i = lane; i < gs; i += 32) {
       const float xv = widen(gx[i]);
@@ -272,11 +219,11 @@ cvt_selftest_kernel(uint64_t lo, uint64_t hi, unsigned long long* counts) {
 __global__ void __launch_bounds__(kThreads)
 div_selftest_kernel(int is_bf16, unsigned long long* counts) {
   unsigned long long bad = 0, pairs = 0;
-  for (uint32_t a = blockIdx.x + 1; a < 0x8000u; a += gridDim.x) {
+  for (uint32_t a = blockIdx.x; a < 0x8000u; a += gridDim.x) {   // a == 0: the all-zero group
     const float amax = is_bf16 ? __uint_as_float(a << 16)
                                : __half2float(__ushort_as_half(static_cast<unsigned short>(a)));
     if (!(amax == amax) || !fast_div_ok(amax)) continue;  // NaN / Inf / out of the fast range
-    const float scale = __fmul_rn(amax, 1.0f / 448.0f);
+    const float scale = group_scale(amax);
     const float rcp = __frcp_rn(scale);
     for (uint32_t xb = threadIdx.x; xb < 0x10000u; xb += kThreads) {
       const float x = is_bf16 ? __uint_as_float(xb << 16)

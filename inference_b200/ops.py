@@ -118,6 +118,27 @@ def w8a8_block_fp8_gemm(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: torch.Te
     return out
 
 
+def w8a8_block_fp8_gemm_fused_quant(a: torch.Tensor, b_q: torch.Tensor, b_scales: torch.Tensor,
+                                    out_dtype=torch.bfloat16, out: torch.Tensor | None = None,
+                                    stream=None) -> torch.Tensor:
+    """quant_fp8_per_token_group(a) followed by w8a8_block_fp8_gemm, fused into one launch
+    (M <= 32, a in bf16 / fp16).  Bit-identical to the two separate calls."""
+    for t, name in ((a, "a"), (b_q, "b_q"), (b_scales, "b_scales")):
+        _dev_tensor(t, name)
+    if a.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("a must be fp16 or bf16")
+    m, k = a.shape
+    n = b_q.shape[0]
+    with torch.cuda.device(a.device):
+        if out is None:
+            out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+        check(lib.inferop_w8a8_block_fp8_gemm_fused_quant(out.data_ptr(), a.data_ptr(), int(_TORCH2CODE[a.dtype]),
+                                                          b_q.data_ptr(), b_scales.data_ptr(), m, n, k, 128,
+                                                          128, int(_TORCH2CODE[out.dtype]), _stream_ptr(stream)),
+              "w8a8_block_fp8_gemm_fused_quant")
+    return out
+
+
 def w8a8_block_fp8_gemm_grouped(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: torch.Tensor,
                                 b_scales: torch.Tensor, m_per_group, out_dtype=torch.bfloat16,
                                 out: torch.Tensor | None = None, stream=None) -> torch.Tensor:

@@ -283,3 +283,41 @@ def test_grouped_launch_rejects_bad_arguments(ops):
     assert lib.inferop_w8a8_block_fp8_gemm_grouped(p, p, p, p, p, None, 2, 256, 128, 128, 128, 2, None) == _capi.ERR_SHAPE
     bad = (C.c_int64 * 2)(4, -1)
     assert lib.inferop_w8a8_block_fp8_gemm_grouped(p, p, p, p, p, bad, 2, 256, 128, 128, 128, 2, None) == _capi.ERR_SHAPE
+
+
+# ------------------------------------------------------------------ quantisation fused as the A prologue
+@pytest.mark.parametrize("m", [1, 3, 16, 17, 32])
+@pytest.mark.parametrize("n,k", [(384, 512), (1000, 1536), (18432, 7168)])
+def test_fused_quant_prologue_is_bit_identical_to_the_two_calls(ops, m, n, k):
+    from inference_b200 import synth
+    x = synth.activations(m, k, seed=m + n)
+    x[0, :128] = 0                      # an all-zero group
+    if m > 1:
+        x[1, 5] = float("nan")
+    bq, bs = synth.quantised_weights(n, k, seed=2)
+    aq, a_s = ops.quant_fp8_per_token_group(x)
+    for dt in (torch.bfloat16, torch.float32):
+        ops.set_option("gemm_path", 2)
+        try:
+            two = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, dt)
+        finally:
+            ops.set_option("gemm_path", 0)
+        one = ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs, dt)
+        assert ops.device_status()[0] == 0
+        assert torch.equal(one.view(torch.int16 if dt == torch.bfloat16 else torch.int32),
+                           two.view(torch.int16 if dt == torch.bfloat16 else torch.int32))
+    xh = x.half()
+    aq, a_s = ops.quant_fp8_per_token_group(xh)
+    two = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, torch.float32)
+    one = ops.w8a8_block_fp8_gemm_fused_quant(xh, bq, bs, torch.float32)
+    assert torch.equal(one.view(torch.int32), two.view(torch.int32))
+
+
+def test_fused_quant_prologue_limits(ops):
+    from inference_b200 import _capi
+    t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p = t.data_ptr()
+    lib = _capi.lib
+    assert lib.inferop_w8a8_block_fp8_gemm_fused_quant(p, p, 2, p, p, 33, 256, 128, 128, 128, 2, None) == _capi.ERR_LIMIT
+    assert lib.inferop_w8a8_block_fp8_gemm_fused_quant(p, p, 0, p, p, 4, 256, 128, 128, 128, 2, None) == _capi.ERR_DTYPE
+    assert lib.inferop_w8a8_block_fp8_gemm_fused_quant(p, p, 2, p, p, 4, 256, 100, 128, 128, 2, None) == _capi.ERR_SHAPE
