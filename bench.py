@@ -257,6 +257,67 @@ def shape_sweep(peaks):
     return out
 
 
+def moe_config(peaks, experts=256, hidden=7168, inter=2048, tokens=4096, topk=8):
+    """MoE expert GEMMs (256 experts, top-8 of 4096 tokens): gate_up [4096 x 7168] and down
+    [7168 x 2048] per expert, variable rows per expert from a seeded softmax + top-k routing.
+    Times one grouped launch per projection against one GEMM call per expert (the reference's way)."""
+    import numpy as np
+    import torch
+    from inference_b200 import ops, synth
+    g = torch.Generator(device="cpu")
+    g.manual_seed(11)
+    logits = torch.randn((tokens, experts), generator=g, dtype=torch.float32)
+    ids = torch.topk(torch.softmax(logits, dim=1), topk, dim=1).indices   # routing: softmax + top-k
+    counts = torch.bincount(ids.flatten(), minlength=experts).tolist()
+    order = torch.argsort(ids.flatten(), stable=True)                      # token copies grouped by expert
+    token_of = (order // topk).cuda()
+    m_total = tokens * topk
+    out = {"experts": experts, "rows_total": m_total, "rows_per_expert_min_max": [min(counts), max(counts)]}
+    x = synth.activations(tokens, hidden, seed=12)
+    for name, n, k, a_src in (("gate_up", 2 * inter, hidden, x[token_of]),
+                              ("down", hidden, inter, synth.activations(m_total, inter, seed=13))):
+        aq, a_s = ops.quant_fp8_per_token_group(a_src.contiguous())
+        bq = torch.empty((experts, n, k), dtype=torch.uint8, device="cuda")
+        bs = torch.empty((experts, n // 128, k // 128), dtype=torch.float32, device="cuda")
+        for e0 in range(0, experts, 32):   # generate in chunks: all experts share one distribution
+            q, s_ = synth.quantised_weights(32 * n, k, seed=100 + e0)
+            bq[e0:e0 + 32] = q.view(32, n, k)
+            bs[e0:e0 + 32] = s_.view(32, n // 128, k // 128)
+            del q, s_
+        c = torch.empty((m_total, n), dtype=torch.bfloat16, device="cuda")
+
+        def grouped():
+            ops.w8a8_block_fp8_gemm_grouped(aq, a_s, bq, bs, counts, out=c)
+
+        def looped():
+            r = 0
+            for e, me in enumerate(counts):
+                if me:
+                    ops.w8a8_block_fp8_gemm(aq[r:r + me], a_s[r:r + me], bq[e], bs[e], out=c[r:r + me])
+                r += me
+
+        res = {}
+        for label, fn, iters in (("grouped", grouped, 5), ("per_expert_calls", looped, 2)):
+            fn()
+            torch.cuda.synchronize()
+            e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0_.record()
+            for _ in range(iters):
+                fn()
+            e1_.record()
+            torch.cuda.synchronize()
+            res[label + "_ms"] = round(e0_.elapsed_time(e1_) / iters, 3)
+        flops = 2.0 * m_total * n * k
+        byt = experts * n * k + m_total * k + 2 * m_total * n
+        t = res["grouped_ms"] * 1e-3
+        res.update({"n": n, "k": k, "tflops": round(flops / t / 1e12, 1), "gbs": round(byt / t / 1e9, 1),
+                    "frac_of_measured_hbm": round(byt / t / 1e9 / peaks["hbm_gbs"], 3)})
+        out[name] = res
+        del bq, bs, c, aq, a_s
+        torch.cuda.empty_cache()
+    return out
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def run_ours(args):
     import torch
@@ -432,6 +493,8 @@ def run_ours(args):
         torch.cuda.empty_cache()
         line["sweep"] = {"what": "quant + GEMM per shape, device-timed (CUDA graph replay), bf16 out",
                          "shapes": shape_sweep(peaks)}
+        torch.cuda.empty_cache()
+        line["moe"] = moe_config(peaks)
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         smp = sized_cpu_sample(k, threads, args.cpu_seconds)
