@@ -31,6 +31,9 @@ NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
 
 
+print_result = print
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -64,7 +67,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU with NVML while a region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.01):
+    def __init__(self, index: int, period_s: float = 0.002):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -196,7 +199,7 @@ def run_reference(args):
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": used, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    print_result(json.dumps(line))
 
 
 # ----------------------------------------------------------------------------- shape sweep
@@ -502,17 +505,33 @@ def run_ours(args):
         line["cpu_baseline"] = {"value": smp.flops / dt / 1e12, "unit": "TFLOP/s",
                                 "cores": min(threads, smp.rows), "kind": smp.kind,
                                 "sample": smp.describe() + f", {dt:.1f} s"}
-    print(json.dumps(line), flush=True)
+    print_result(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
 def main():
     args = parse_args()
-    if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_ours(args)
+    # Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line
+    # there.  Everything else goes to stderr: fd 1 is pointed at fd 2 for the duration of the run
+    # and the result line is written to the saved descriptor.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    captured = []
+    global print_result
+    print_result = lambda text: captured.append(text)
+    try:
+        if args.impl == "reference":
+            run_reference(args)
+        else:
+            run_ours(args)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    for text in captured:
+        print(text, flush=True)
 
 
 if __name__ == "__main__":

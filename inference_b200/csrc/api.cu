@@ -339,6 +339,8 @@ int inferop_set_option(const char* key, int64_t value) {
   } else if (!strcmp(key, "gemm_tma_store")) {
     if (value < -1 || value > 1) return INFEROP_ERR_SHAPE;
     o.gemm_tma_store = static_cast<int>(value);
+  } else if (!strcmp(key, "decode_pdl")) {
+    o.decode_pdl = value != 0;
   } else if (!strcmp(key, "decode_splits")) {
     if (value < 0 || value > 1024) return INFEROP_ERR_SHAPE;
     o.decode_splits = static_cast<int>(value);

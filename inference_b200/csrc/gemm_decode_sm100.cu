@@ -203,10 +203,43 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   if (warp == 0) {
     // ------------------------------ TMA producer (warp-uniform loop) ------
+    // The weights never depend on the kernel queued before this one, the token tile may (it
+    // is usually the output of the quantisation kernel).  So the first ring-full of weight
+    // tiles is requested at once, then the producer waits for the preceding kernel
+    // (programmatic dependent launch; a no-op otherwise) and only then asks for token tiles.
     int t = t_first, kb = kb_first;
     uint32_t armed = 0;
     bool ok = true;
-    for (uint32_t i = 0; i < count; ++i) {
+    const uint32_t head = count < static_cast<uint32_t>(C::kStages) ? count : static_cast<uint32_t>(C::kStages);
+    if (!kFused) {
+      int th = t, kh = kb;
+      for (uint32_t i = 0; i < head; ++i) {
+        uint8_t* dst = smem + i * C::kStageBytes;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(&full[i], C::kStageBytes);
+          tma_load_2d(dst, &map_w, &full[i], kh * BK, th * TN);
+        }
+        __syncwarp();
+        if (++kh == p.kb) {
+          kh = 0;
+          ++th;
+        }
+      }
+      armed = head;
+      pdl_wait();
+      for (uint32_t i = 0; i < head; ++i) {
+        uint8_t* dst = smem + i * C::kStageBytes;
+        if (elect_one()) tma_load_2d(dst + kBytesW, &map_a, &full[i], kb * BK, 0);
+        __syncwarp();
+        if (++kb == p.kb) {
+          kb = 0;
+          ++t;
+        }
+      }
+    } else {
+      pdl_wait();
+    }
+    for (uint32_t i = (kFused ? 0u : head); i < count; ++i) {
       const uint32_t stage = i % C::kStages;
       const uint32_t phase = (i / C::kStages) & 1u;
       if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteDProducerEmpty)) {
@@ -283,6 +316,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const AT* src = static_cast<const AT*>(p.a_src);
       const int64_t ld = static_cast<int64_t>(p.kb) * BK;
       uint4 cur[STEPS], nxt[STEPS];
+      pdl_wait();   // the activations may come from the kernel queued before this one
       auto fetch = [&](uint4 (&dst)[STEPS], uint32_t unit) {
         // unit -> K block (the token tile does not depend on the weight tile)
         const int kbx = static_cast<int>((static_cast<uint32_t>(kb_first) + unit) % static_cast<uint32_t>(p.kb));
@@ -339,6 +373,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
   } else if (!kFused && warp == 2) {
     // ------------------------------ scale warp ----------------------------
+    pdl_wait();   // a_scales may come from the kernel queued before this one
     int t = t_first, kb = kb_first;
     for (uint32_t i = 0; i < count; ++i) {
       const uint32_t buf = i % C::kBufs;
@@ -369,6 +404,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     float acc[MP];
 #pragma unroll
     for (int j = 0; j < MP; ++j) acc[j] = 0.0f;
+    pdl_wait();   // the output, workspace and counters may still be in use by the preceding kernel
     int t = t_first, kb = kb_first, seg_kb0 = kb_first;
     bool ok = true;
     for (uint32_t i = 0; ok && i < count; ++i) {
@@ -484,7 +520,20 @@ int launch_decode_t(const CUtensorMap& mw, const CUtensorMap& ma, const DecodePa
     if (e != cudaSuccess) return note_cuda_error(e);
     attr_done[dev] = true;
   }
-  w8a8_decode_kernel<MP, OutT, AT><<<ctas, std::is_same<AT, void>::value ? kThreads : kFusedThreads, C::kSmemBytes, stream>>>(mw, ma, p);
+  // programmatic dependent launch: the preamble and the weight prefetch of this kernel may
+  // overlap the tail of the kernel queued before it (in practice the quantisation kernel)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctas);
+  cfg.blockDim = dim3(std::is_same<AT, void>::value ? kThreads : kFusedThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = options().decode_pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, w8a8_decode_kernel<MP, OutT, AT>, mw, ma, p);
+  if (e != cudaSuccess) return note_cuda_error(e);
   return check_launch();
 }
 

@@ -123,6 +123,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   }
 }
 
+// ------------------------------ programmatic dependent launch --------------
+// launch_dependents: kernels queued behind this one (and launched with the programmatic
+// stream-serialisation attribute) may start their preamble now.  wait: block until every
+// kernel this one depends on has completed and its writes are visible; a no-op for a kernel
+// launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ------------------------------ fences ------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -85,6 +85,9 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 quant128_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, const T* __restrict__ x,
                 int64_t groups) {
+  // a GEMM queued behind this kernel may begin its preamble (barriers, tensor memory, weight
+  // prefetch); it waits for this kernel's completion before it reads q or scales
+  pdl_launch_dependents();
   const int sub = threadIdx.x & 15;
   const int64_t hw = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 4;
   const int64_t hw_total = (static_cast<int64_t>(gridDim.x) * kThreads) >> 4;
