@@ -339,6 +339,9 @@ int inferop_set_option(const char* key, int64_t value) {
   } else if (!strcmp(key, "gemm_tma_store")) {
     if (value < -1 || value > 1) return INFEROP_ERR_SHAPE;
     o.gemm_tma_store = static_cast<int>(value);
+  } else if (!strcmp(key, "gemm_group_m")) {
+    if (value < 0 || value > 4096) return INFEROP_ERR_SHAPE;
+    o.gemm_group_m = static_cast<int>(value);
   } else if (!strcmp(key, "decode_pdl")) {
     o.decode_pdl = value != 0;
   } else if (!strcmp(key, "decode_splits")) {

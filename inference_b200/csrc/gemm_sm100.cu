@@ -35,7 +35,7 @@
 // HBM traffic per call (algorithmic): M*K + N*K operand bytes, 4*M*K/128 +
 // 4*ceil(N/128)*K/128 scale bytes, M*N*sizeof(out) output bytes; operand
 // re-reads by other tiles are served by L2 (tiles are rasterised in bands of
-// 16 M-tiles so that concurrently running CTAs share A and B panels).
+// 32 M-tiles: a band's A panel stays in L2 while the weights stream past it once).
 //
 // Every wait is bounded (ptx.cuh: mbar_wait).  A wait that runs out sets the
 // CTA's abort flag and the device status record; all roles then fall through
@@ -56,7 +56,6 @@ constexpr int BH = 128;  // columns per half = one weight-scale block = one TMEM
 constexpr int BK = 128;
 constexpr int kPromoWarps = 8;
 constexpr int kThreads = 128 + 32 * kPromoWarps;
-constexpr int kGroupM = 16;  // M-tiles per rasterisation band
 constexpr int kStages = 4;
 constexpr int kBytesA = BM * BK;
 constexpr int kBytesB = BN * BK;
@@ -76,6 +75,7 @@ struct GemmParams {
   int kb;        // K / 128
   int nb;        // ceil(N / 128): rows of b_scales
   int tiles_m, tiles_n, num_tiles;
+  int group_m;   // M-tiles per rasterisation band: a band's A panel stays in L2 while W streams past once
   int tma_store; // 1: epilogue goes through shared memory + TMA store
   DeviceStatus* status;
 };
@@ -110,11 +110,11 @@ struct TileInfo {
 template <bool kGrouped>
 __device__ __forceinline__ TileInfo tile_info(int t, const struct GemmParams& p, const GroupTable* tab);
 
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int per_band = kGroupM * tiles_n;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int per_band = group_m * tiles_n;
   const int band = t / per_band;
-  const int first_m = band * kGroupM;
-  const int band_m = min(kGroupM, tiles_m - first_m);
+  const int first_m = band * group_m;
+  const int band_m = min(group_m, tiles_m - first_m);
   const int r = t - band * per_band;
   tm = first_m + r % band_m;
   tn = r / band_m;
@@ -135,7 +135,7 @@ __device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p, const 
     ti.col = tn * BN;
   } else {
     int tm, tn;
-    tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+    tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
     ti.a_row = tm * BM;
     ti.row_end = p.m;
     ti.b_row = tn * BN;
@@ -506,6 +506,7 @@ int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, 
   if (tiles > 0x7FFFFFFF || tiles * p.kb > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
   p.num_tiles = static_cast<int>(tiles);
   p.tma_store = tma_store ? 1 : 0;
+  p.group_m = opt.gemm_group_m > 0 ? opt.gemm_group_m : 32;
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;
@@ -555,6 +556,7 @@ int launch_gemm_grouped(DeviceCtx* ctx, void* c, const void* a_q, const void* a_
   p.nb = static_cast<int>(n / 128);
   p.tiles_n = static_cast<int>((n + BN - 1) / BN);
   p.tma_store = tma_store ? 1 : 0;
+  p.group_m = 32;
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;

@@ -35,6 +35,7 @@ struct Options {
   int gemm_block_n = 0;    // 0 auto, 128, 256
   int gemm_tma_store = -1; // -1 auto, 0 off, 1 on
   int gemm_ctas = 0;       // 0 = one per SM
+  int gemm_group_m = 0;    // M-tiles per rasterisation band of the large-tile kernel (0 = default 32)
   int decode_pdl = 1;      // small-M kernel: launch with programmatic stream serialisation
   int decode_splits = 0;   // 0 auto, else K parts per tile of the small-M kernel (capped by SMs / tiles)
   int gemm_path = 0;       // 0 auto, 1 always the large-tile kernel, 2 small-M kernel whenever M <= 128
