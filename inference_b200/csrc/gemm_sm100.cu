@@ -345,10 +345,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
 #pragma unroll
       for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
 
-      float s_next = have ? __ldg(sa_ptr) * __ldg(sb_ptr) : 0.0f;
+      // the scales of block kb+1 are requested at the top of block kb and first touched (the
+      // product) at the top of block kb+1, so their latency never stalls this warp
+      float sa_n = have ? __ldg(sa_ptr) : 0.0f;
+      float sb_n = have ? __ldg(sb_ptr) : 0.0f;
       for (int kb = 0; kb < p.kb; ++kb, ++kiter) {
-        const float s = s_next;
-        if (kb + 1 < p.kb && have) s_next = __ldg(sa_ptr + kb + 1) * __ldg(sb_ptr + kb + 1);
+        const float s = sa_n * sb_n;
+        if (kb + 1 < p.kb && have) {
+          sa_n = __ldg(sa_ptr + kb + 1);
+          sb_n = __ldg(sb_ptr + kb + 1);
+        }
         const uint32_t buf = kiter & 1u;
         if (!mbar_wait(&tmem_full[buf], (kiter >> 1) & 1u, abort_flag, p.status,
                        kSitePromoTmemFull)) {
