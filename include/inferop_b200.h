@@ -78,7 +78,7 @@ INFEROP_API int inferop_dequant_fp8_per_token_group(void* x, int32_t dt, const v
  * M > 0, N > 0 (else INFEROP_ERR_SHAPE).  a_q and b_q must be 16-byte aligned
  * (INFEROP_ERR_POINTER otherwise); c may have any alignment and N any value.
  * Calls with M <= 96 take a weight-streaming kernel that keeps a library-owned scratch
- * buffer (about 20 MB) per stream; it is allocated by the first such call on a stream, so
+ * buffer (about 10 MB) per stream; it is allocated by the first such call on a stream, so
  * make that call before capturing the stream into a CUDA graph. */
 INFEROP_API int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, const void* b_q,
                                 const void* b_scales, int64_t m, int64_t n, int64_t k,
