@@ -354,7 +354,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
           for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
           const float scale = group_scale(amax);
-          const uint2 bytes = fast_div_ok(amax) ? quantise8<true>(f, scale, __frcp_rn(scale))
+          const uint2 bytes = fast_div_ok(amax) ? quantise8_fast16(cur[s2], f, scale, __frcp_rn(scale))
                                                 : quantise8<false>(f, scale, 0.0f);
           // swizzled K-major layout of a TMA SWIZZLE_128B load: 16-byte chunk c of row r sits at
           // chunk c ^ (r & 7); this lane's 8 bytes are half of chunk sub / 2

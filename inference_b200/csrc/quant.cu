@@ -32,7 +32,14 @@ namespace ib200 {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kUnroll = 4;
+#ifndef IB200_QUANT_UNROLL
+#define IB200_QUANT_UNROLL 4
+#endif
+#ifndef IB200_QUANT_MIN_CTAS
+#define IB200_QUANT_MIN_CTAS 4
+#endif
+constexpr int kUnroll = IB200_QUANT_UNROLL;        // groups in flight per half warp
+constexpr int kMinCtas = IB200_QUANT_MIN_CTAS;     // resident CTAs per SM the register budget allows
 
 template <typename T>
 struct Vec8;
@@ -82,7 +89,7 @@ struct Vec8<float> {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, kMinCtas)
 quant128_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, const T* __restrict__ x,
                 int64_t groups) {
   // a GEMM queued behind this kernel may begin its preamble (barriers, tensor memory, weight
@@ -113,18 +120,25 @@ quant128_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, const T* __
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = 0.0f;
       }
-      float amax = 0.0f;
+      float amax;
+      if constexpr (sizeof(T) == 2) {
+        using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+        amax = live[u] ? absmax8_packed<T2>(v[u].raw) : 0.0f;
+      } else {
+        amax = 0.0f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+      }
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
       const float scale = group_scale(amax);
       if (live[u]) {
         uint2 bytes;
         // 16-bit inputs whose group maximum is far from the ends of the fp32 range divide
-        // through the reciprocal (3 FP ops per element); everything else uses IEEE division
-        if (sizeof(T) == 2 && fast_div_ok(amax)) {
-          bytes = quantise8<true>(f, scale, __frcp_rn(scale));
+        // through the reciprocal, two elements per instruction; everything else uses IEEE division
+        if constexpr (sizeof(T) == 2) {
+          bytes = fast_div_ok(amax) ? quantise8_fast16(v[u].raw, f, scale, __frcp_rn(scale))
+                                    : quantise8<false>(f, scale, 0.0f);
         } else {
           bytes = quantise8<false>(f, scale, 0.0f);
         }
@@ -233,7 +247,10 @@ div_selftest_kernel(int is_bf16, unsigned long long* counts) {
                               : __half2float(__ushort_as_half(static_cast<unsigned short>(xb)));
       if (!(fabsf(x) <= amax)) continue;
       ++pairs;
-      const uint32_t fast = cvt2(div_by_rcp(x, scale, rcp), 0.0f) & 0xFFu;
+      // the kernels' fast path, element 0 of the eight (the other seven are zeros)
+      const uint4 raw = make_uint4(xb, 0u, 0u, 0u);
+      const float f8[8] = {x, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+      const uint32_t fast = quantise8_fast16(raw, f8, scale, rcp).x & 0xFFu;
       const uint32_t slow = cvt2(__fdiv_rn(x, scale), 0.0f) & 0xFFu;
       if (fast != slow) {
         ++bad;

@@ -3,9 +3,13 @@
 // produce the bytes and scales of reference/reference.cpp:65-80 bit for bit.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <type_traits>
 
 namespace ib200 {
 
@@ -64,6 +68,45 @@ __device__ __forceinline__ uint2 quantise8(const float (&f)[8], float scale, flo
   return make_uint2(w0, w1);
 }
 
+// Fast path for eight 16-bit inputs (raw = the four bf16x2 / f16x2 words, f = the same values
+// widened): the division through the reciprocal, two elements per instruction
+// (mul.f32x2 / fma.f32x2), the hardware converter, and the sign of every byte taken from its
+// input.  The quotient of x by a positive scale has the sign of x, so overriding the sign bit
+// is exact; it also restores what the arithmetic and the converter lose: the sign of a -0
+// input (x - q0 * scale gives +0) and the sign of a NaN input.  Valid under fast_div_ok only.
+__device__ __forceinline__ uint2 quantise8_fast16(const uint4& raw, const float (&f)[8], float scale,
+                                                 float rcp) {
+  const float2 rcp2 = make_float2(rcp, rcp);
+  const float2 nscale2 = make_float2(-scale, -scale);
+  uint32_t c[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = make_float2(f[2 * i], f[2 * i + 1]);
+    const float2 q0 = __fmul2_rn(x, rcp2);
+    const float2 r = __ffma2_rn(q0, nscale2, x);   // x - q0 * scale, exact
+    const float2 q1 = __ffma2_rn(r, rcp2, q0);
+    c[i] = cvt2(q1.x, q1.y);
+  }
+  // the high byte of every 16-bit input carries its sign in bit 7
+  const uint32_t s0 = __byte_perm(raw.x, raw.y, 0x7531) & 0x80808080u;
+  const uint32_t s1 = __byte_perm(raw.z, raw.w, 0x7531) & 0x80808080u;
+  return make_uint2(((c[0] | (c[1] << 16)) & 0x7F7F7F7Fu) | s0, ((c[2] | (c[3] << 16)) & 0x7F7F7F7Fu) | s1);
+}
+
+// max |x| over the eight 16-bit inputs of a lane, on the packed words (a NaN never wins:
+// __hmax2 returns the other operand)
+template <typename T2>
+__device__ __forceinline__ float absmax8_packed(const uint4& raw) {
+  const T2 a = __habs2(*reinterpret_cast<const T2*>(&raw.x));
+  const T2 b = __habs2(*reinterpret_cast<const T2*>(&raw.y));
+  const T2 c = __habs2(*reinterpret_cast<const T2*>(&raw.z));
+  const T2 d = __habs2(*reinterpret_cast<const T2*>(&raw.w));
+  const T2 m = __hmax2(__hmax2(a, b), __hmax2(c, d));
+  const float2 mf = (sizeof(T2) == sizeof(__half2) && std::is_same<T2, __half2>::value)
+                        ? __half22float2(*reinterpret_cast<const __half2*>(&m))
+                        : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&m));
+  return fmaxf(0.0f, fmaxf(mf.x, mf.y));   // fmaxf drops a NaN that survived (all eight NaN)
+}
 
 // scale of a group from its maximum magnitude (reference/reference.cpp:73)
 __device__ __forceinline__ float group_scale(float amax) {
