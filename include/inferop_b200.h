@@ -111,6 +111,26 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm_grouped(void* c, const void* a_q, co
                                         int64_t groups, int64_t n, int64_t k, int32_t group_size,
                                         int32_t block_n, int32_t out_dt, void* stream);
 
+/* ---- blockwise-FP8 GEMM of one column shard, all-gathered by its own epilogue
+ * Column-parallel use of inferop_w8a8_block_fp8_gemm (reference include/inferop/ops.h:81-84; the
+ * reference is single-GPU and has no collective): rank `rank` of `n_peers` holds the weight rows
+ * b_q [n, K] / b_scales [n/128, K/128] of its shard and the full activations, and the result
+ * [M, n] is written to columns [rank * n, (rank + 1) * n) of the row-major [M, n * n_peers]
+ * buffer of EVERY rank, straight from the kernel's epilogue (one TMA store per destination over
+ * NVLink), instead of a local store followed by an all-gather.
+ * c_peers is a HOST array of n_peers device addresses, entry d = the base of rank d's buffer as
+ * mapped into this process (CUDA IPC, virtual-memory export or symmetric memory; entry `rank` is
+ * the local buffer), each 16-byte aligned; it is read before the call returns.  n % 128 == 0,
+ * n_peers <= 8, out_dt 1 (fp16) or 2 (bf16).  The call does not synchronise the ranks: a rank's
+ * buffer is complete when every rank's call has finished, so the ranks must meet (a barrier, a
+ * collective, or stream-ordered signals) after the call before any of them reads its buffer, and
+ * before the call overwrites a buffer that a peer may still be reading. */
+INFEROP_API int inferop_w8a8_block_fp8_gemm_allgather(void* const* c_peers, int32_t n_peers, int32_t rank,
+                                          const void* a_q, const void* a_scales, const void* b_q,
+                                          const void* b_scales, int64_t m, int64_t n, int64_t k,
+                                          int32_t group_size, int32_t block_n, int32_t out_dt,
+                                          void* stream);
+
 /* ---- blockwise-FP8 GEMM for a few tokens, with no allocation
  * No counterpart in the reference: added for callers that must not trigger a device
  * allocation, such as a server that gave all device memory to its own pool at start-up, or a

@@ -30,6 +30,8 @@ SIGNATURES = {
                                                           _i32, _vp]),
     "inferop_w8a8_block_fp8_gemm_grouped": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.POINTER(_i64), _i64, _i64, _i64,
                                                       _i32, _i32, _i32, _vp]),
+    "inferop_w8a8_block_fp8_gemm_allgather": (C.c_int, [C.POINTER(_vp), _i32, _i32, _vp, _vp, _vp, _vp, _i64, _i64,
+                                                        _i64, _i32, _i32, _i32, _vp]),
     "inferop_w8a8_block_fp8_gemm_fixed_scratch": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
                                                             _i32, _i32, _i32, _vp]),
     "inferop_device_status": (C.c_int, [C.POINTER(C.c_uint32), C.c_int]),

@@ -297,6 +297,28 @@ int inferop_w8a8_block_fp8_gemm_grouped(void* c, const void* a_q, const void* a_
                              static_cast<cudaStream_t>(stream));
 }
 
+int inferop_w8a8_block_fp8_gemm_allgather(void* const* c_peers, int32_t n_peers, int32_t rank,
+                                          const void* a_q, const void* a_scales, const void* b_q,
+                                          const void* b_scales, int64_t m, int64_t n, int64_t k,
+                                          int32_t group_size, int32_t block_n, int32_t out_dt,
+                                          void* stream) {
+  if (group_size != 128 || block_n != 128 || k <= 0 || k % 128 != 0 || m <= 0 || n <= 0 ||
+      n % 128 != 0 || n_peers < 1 || n_peers > 8 || rank < 0 || rank >= n_peers) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (out_dt != 1 && out_dt != 2) return INFEROP_ERR_DTYPE;
+  if (m > 0x7FFFFF00LL || n * n_peers > 0x7FFFFF00LL || k > 0x7FFFFF00LL) return INFEROP_ERR_LIMIT;
+  if (!c_peers || !a_q || !a_scales || !b_q || !b_scales) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(a_q) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_gemm_allgather(ctx, c_peers, n_peers, rank, a_q, a_scales, b_q, b_scales, m, n, k,
+                               out_dt, static_cast<cudaStream_t>(stream));
+}
+
 int inferop_device_status(uint32_t* out4, int reset) {
   int err;
   DeviceCtx* ctx = current_ctx(&err);

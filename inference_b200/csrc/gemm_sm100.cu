@@ -98,6 +98,20 @@ struct GroupTable {
   int meta[kMaxGroupTiles];   // (group << 8) | (rows - 1): which group, how many valid rows
 };
 
+// All-gather launches (column-parallel sharding): this rank's [M, n] result is written into the
+// full [M, n * ranks] row-major result of EVERY rank, at column offset rank * n, by one TMA store
+// per destination from the same staging buffer.  The destinations are peer-mapped device
+// addresses; the list is rotated on the host (first destination = rank + 1, own buffer last) so
+// that the ranks do not all write to the same GPU at the same moment.
+constexpr int kMaxPeers = 8;
+struct PeerMaps {
+  CUtensorMap map[kMaxPeers];  // [M, n * ranks] two-byte row-major, box 128 rows x 64 columns
+  int count;
+  int col_offset;              // rank * n
+};
+
+enum : int { kModePlain = 0, kModeGrouped = 1, kModeGather = 2 };
+
 struct TileInfo {
   int a_row;     // first row of the tile in A / a_scales / C
   int row_end;   // rows at and beyond this index are not this tile's
@@ -195,10 +209,12 @@ __device__ __forceinline__ void promote32(float2* acc, const uint32_t (&v)[32], 
   }
 }
 
-template <typename OutT, bool kGrouped>
+template <typename OutT, int kMode>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtensorMap* map_b,
                                           const CUtensorMap* map_c, const GemmParams& p,
-                                          const GroupTable* tab) {
+                                          const GroupTable* tab, const PeerMaps* peers) {
+  constexpr bool kGrouped = kMode == kModeGrouped;
+  constexpr bool kGather = kMode == kModeGather;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -228,7 +244,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
     mbar_init_fence();
     tma_prefetch_desc(map_a);
     tma_prefetch_desc(map_b);
-    if (p.tma_store) tma_prefetch_desc(map_c);
+    if constexpr (kGather) {
+      for (int d = 0; d < peers->count; ++d) tma_prefetch_desc(&peers->map[d]);
+    } else {
+      if (p.tma_store) tma_prefetch_desc(map_c);
+    }
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -406,7 +426,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           fence_proxy_async_smem();
           named_bar_sync(1 + half, 128);
           if (issuer && col0 < p.n) {
-            tma_store_2d(map_c, my_buf, col0, ti.a_row);
+            if constexpr (kGather) {
+              for (int d = 0; d < peers->count; ++d)
+                tma_store_2d(&peers->map[d], my_buf, peers->col_offset + col0, ti.a_row);
+            } else {
+              tma_store_2d(map_c, my_buf, col0, ti.a_row);
+            }
             tma_store_commit();
           }
         } else if (gm < ti.row_end) {
@@ -443,7 +468,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
-  gemm_body<OutT, false>(&map_a, &map_b, &map_c, p, nullptr);
+  gemm_body<OutT, kModePlain>(&map_a, &map_b, &map_c, p, nullptr, nullptr);
 }
 
 template <typename OutT>
@@ -451,7 +476,30 @@ __global__ void __launch_bounds__(kThreads, 1)
 w8a8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_c, const GemmParams p,
                          const __grid_constant__ GroupTable tab) {
-  gemm_body<OutT, true>(&map_a, &map_b, &map_c, p, &tab);
+  gemm_body<OutT, kModeGrouped>(&map_a, &map_b, &map_c, p, &tab, nullptr);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_gather_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const GemmParams p, const __grid_constant__ PeerMaps peers) {
+  gemm_body<OutT, kModeGather>(&map_a, &map_b, nullptr, p, nullptr, &peers);
+}
+
+template <typename OutT>
+int launch_gather_t(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
+                    const PeerMaps& peers, int ctas, cudaStream_t stream) {
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(w8a8_gather_gemm_kernel<OutT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_done[dev] = true;
+  }
+  w8a8_gather_gemm_kernel<OutT><<<ctas, kThreads, kSmemBytes, stream>>>(ma, mb, p, peers);
+  return check_launch();
 }
 
 template <typename OutT>
@@ -606,6 +654,61 @@ int launch_gemm_grouped(DeviceCtx* ctx, void* c, const void* a_q, const void* a_
     row += m_per_group[g];
   }
   return flush(count);
+}
+
+int launch_gemm_allgather(DeviceCtx* ctx, void* const* c_peers, int32_t n_peers, int32_t rank,
+                          const void* a_q, const void* a_scales, const void* b_q,
+                          const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
+                          cudaStream_t stream) {
+  const Options& opt = options();
+  if (out_dt != 1 && out_dt != 2) return INFEROP_ERR_DTYPE;
+  if (n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return INFEROP_ERR_SHAPE;
+  // a store box is 64 columns wide and must not reach into the next rank's columns; the weight
+  // scales of a shard are whole 128-row blocks
+  if (n % 128 != 0) return INFEROP_ERR_SHAPE;
+  const int64_t n_total = n * n_peers;
+  if (n_total > 0x7FFFFFFF) return INFEROP_ERR_LIMIT;
+  for (int d = 0; d < n_peers; ++d) {
+    if (c_peers[d] == nullptr) return INFEROP_ERR_POINTER;
+    if (reinterpret_cast<uintptr_t>(c_peers[d]) % 16 != 0) return INFEROP_ERR_POINTER;
+  }
+
+  GemmParams p;
+  p.a_scales = static_cast<const float*>(a_scales);
+  p.b_scales = static_cast<const float*>(b_scales);
+  p.c = nullptr;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.kb = static_cast<int>(k / 128);
+  p.nb = static_cast<int>(n / 128);
+  p.tiles_m = static_cast<int>((m + BM - 1) / BM);
+  p.tiles_n = static_cast<int>((n + BN - 1) / BN);
+  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  if (tiles > 0x7FFFFFFF || tiles * p.kb > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
+  p.num_tiles = static_cast<int>(tiles);
+  p.tma_store = 1;
+  p.group_m = opt.gemm_group_m > 0 ? opt.gemm_group_m : 32;
+  p.status = ctx->status;
+
+  CUtensorMap ma, mb;
+  int rc = make_tensor_map_2d(&ma, a_q, 1, m, k, k, BM, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  rc = make_tensor_map_2d(&mb, b_q, 1, n, k, k, BN, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  static thread_local PeerMaps peers;
+  peers.count = n_peers;
+  peers.col_offset = static_cast<int>(rank * n);
+  for (int i = 0; i < n_peers; ++i) {
+    const int d = (rank + 1 + i) % n_peers;  // own buffer last
+    rc = make_tensor_map_2d(&peers.map[i], c_peers[d], 2, m, n_total, n_total * 2, 128, 64, true);
+    if (rc != INFEROP_OK) return rc;
+  }
+  for (int i = n_peers; i < kMaxPeers; ++i) peers.map[i] = peers.map[0];
+  int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
+  if (ctas > p.num_tiles) ctas = p.num_tiles;
+  return out_dt == 1 ? launch_gather_t<__half>(ma, mb, p, peers, ctas, stream)
+                     : launch_gather_t<__nv_bfloat16>(ma, mb, p, peers, ctas, stream);
 }
 
 }  // namespace ib200

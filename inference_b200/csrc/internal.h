@@ -63,6 +63,14 @@ int launch_gemm_grouped(DeviceCtx* ctx, void* c, const void* a_q, const void* a_
                         const void* b_q, const void* b_scales, const int64_t* m_per_group,
                         int64_t groups, int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream);
 
+// All-gather launch (column-parallel sharding): this rank's [m, n] result goes to columns
+// [rank * n, (rank + 1) * n) of the [m, n * n_peers] two-byte row-major buffer of every peer;
+// c_peers (host array) holds the n_peers base addresses as mapped in this process.
+int launch_gemm_allgather(DeviceCtx* ctx, void* const* c_peers, int32_t n_peers, int32_t rank,
+                          const void* a_q, const void* a_scales, const void* b_q,
+                          const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
+                          cudaStream_t stream);
+
 // gemm_decode_sm100.cu : small-M path (M <= kDecodeMaxM).  workspace holds
 // decode_workspace_bytes(sm_count) bytes, counters kDecodeMaxTiles zeroed ints; both are
 // owned by the caller of launch_gemm_decode and must not be shared by launches that can

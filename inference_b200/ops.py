@@ -165,6 +165,29 @@ def w8a8_block_fp8_gemm_grouped(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: 
     return out
 
 
+def w8a8_block_fp8_gemm_allgather(peer_ptrs, rank: int, a_q: torch.Tensor, a_scales: torch.Tensor,
+                                  b_q: torch.Tensor, b_scales: torch.Tensor, out_dtype=torch.bfloat16,
+                                  stream=None) -> None:
+    """GEMM of this rank's column shard whose epilogue writes the result into every rank's buffer.
+
+    peer_ptrs: one device address per rank (entry `rank` = the local buffer), each the base of
+    that rank's row-major [M, N_shard * ranks] result in `out_dtype`; this call fills columns
+    [rank * N_shard, (rank + 1) * N_shard) of all of them.  The ranks must meet after the call
+    (``shard.PeerOutput.barrier``) before any of them reads its buffer.
+    """
+    for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
+        _dev_tensor(t, name)
+    m, k = a_q.shape
+    n = b_q.shape[0]
+    ptrs = (C.c_void_p * len(peer_ptrs))(*[int(p) for p in peer_ptrs])
+    with torch.cuda.device(a_q.device):
+        check(lib.inferop_w8a8_block_fp8_gemm_allgather(ptrs, len(peer_ptrs), int(rank), a_q.data_ptr(),
+                                                        a_scales.data_ptr(), b_q.data_ptr(),
+                                                        b_scales.data_ptr(), m, n, k, 128, 128,
+                                                        int(_TORCH2CODE[out_dtype]), _stream_ptr(stream)),
+              "w8a8_block_fp8_gemm_allgather")
+
+
 def device_status(reset: bool = True):
     """Synchronise and return the device-side status record (code, block, aux0, aux1)."""
     rec = (C.c_uint32 * 4)()

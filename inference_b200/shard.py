@@ -46,3 +46,48 @@ def blocked_to_row_major(c_blocked: torch.Tensor) -> torch.Tensor:
     """[G, M, N/G] -> [M, N] (a strided copy; only for consumers that need the flat layout)."""
     g, m, n_loc = c_blocked.shape
     return c_blocked.permute(1, 0, 2).reshape(m, g * n_loc)
+
+
+def peer_columns(n_shard: int, rank: int) -> tuple[int, int]:
+    """Columns [lo, hi) of the full [M, N_shard * G] result that `rank`'s GEMM epilogue fills
+    in every rank's buffer (the all-gather variant of the GEMM)."""
+    return rank * n_shard, (rank + 1) * n_shard
+
+
+class PeerOutput:
+    """The full [M, N] result buffer of this rank, mapped into every rank of the group, and the
+    other ranks' buffers mapped into this one.
+
+    `ptrs[d]` is the address of rank d's buffer in this process: what the all-gather variant of
+    the GEMM takes as its destinations.  The mapping uses torch's symmetric memory (CUDA virtual
+    memory handles exchanged over the process group's store); multicast binding is switched off
+    because only plain peer stores are used.  Without an initialised process group the object
+    degrades to a single local buffer (one destination).
+    """
+
+    def __init__(self, m: int, n_total: int, dtype=torch.bfloat16, device=None, group=None):
+        import os
+        self.m, self.n_total = m, n_total
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+            self.group = group if group is not None else dist.group.WORLD
+            self.local = symm.empty((m, n_total), dtype=dtype, device=device)
+            self._handle = symm.rendezvous(self.local, self.group)
+            self.rank = self._handle.rank
+            self.world = self._handle.world_size
+            self.ptrs = [int(p) for p in self._handle.buffer_ptrs]
+            self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        else:
+            self.group = None
+            self.local = torch.empty((m, n_total), dtype=dtype, device=device)
+            self._handle = None
+            self.rank, self.world = 0, 1
+            self.ptrs = [self.local.data_ptr()]
+            self._flag = None
+
+    def barrier(self) -> None:
+        """Stream-ordered meeting point of the ranks: enqueued after a rank's GEMM, it completes
+        only when every rank's GEMM (and with it every store into this rank's buffer) has."""
+        if self._flag is not None:
+            dist.all_reduce(self._flag, group=self.group)
