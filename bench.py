@@ -8,7 +8,8 @@ Workload (the N-sharded configuration): A bf16 [16384, 7168] replicated, W E4M3 
 with 128x128 block scales, column-parallel over the ranks (each rank owns N/G weight rows and
 their scales), C bf16 [16384, N/G] per rank.  One step = quantise A, then the GEMM.  The total
 problem is fixed while G grows ("strong" scaling); no data-path collective is involved unless
---gather is given, which adds an NCCL all-gather of C and reports it separately.
+--gather is given, which adds an all-gather of C (by NCCL, and by the GEMM's own epilogue
+over peer-mapped buffers) and reports both separately.
 
 Prints ONE JSON line on stdout (rank 0).  Synthetic seeded inputs; see inference_b200/synth.py.
 """
@@ -412,7 +413,34 @@ def run_ours(args):
         tg = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
         gather = {"ms_per_step_with_gather": tg * 1e3, "value_with_gather": flops_total / tg / 1e12,
                   "bytes_received_per_rank": 2 * m * n_loc * (world - 1), "layout": "[G][M][N/G] rank-blocked"}
-        del c_all
+        # the same step with the gather done by the GEMM's own epilogue (peer stores into every
+        # rank's row-major [M, N] buffer), then a stream-ordered meeting of the ranks
+        from inference_b200 import shard
+        po = shard.PeerOutput(m, n, torch.bfloat16, dev)
+
+        def fused_step():
+            ops.quant_fp8_per_token_group(x, 128, aq, a_s)
+            ops.w8a8_block_fp8_gemm_allgather(po.ptrs, rank, aq, a_s, bq, bs)
+            po.barrier()
+
+        for _ in range(2):
+            fused_step()
+        sync_all()
+        g0.record(stream)
+        for _ in range(args.steps):
+            fused_step()
+        g1.record(stream)
+        torch.cuda.synchronize()
+        tf = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
+        blocked = c_all.view(world, m, n_loc)
+        same = all(torch.equal(po.local[:, r * n_loc:(r + 1) * n_loc], blocked[r]) for r in range(world))
+        gather["fused"] = {"ms_per_step": tf * 1e3, "value": flops_total / tf / 1e12,
+                           "layout": "[M][N] row-major on every rank",
+                           "equals_nccl_gather": bool(same),
+                           "link_gbs_out_per_rank": 2 * m * n_loc * (world - 1) / tf / 1e9}
+        status = ops.device_status()
+        assert status[0] == 0, f"device-side wait ran out: {status}"
+        del c_all, po
 
     # ---- end-to-end through the public API with host buffers
     e2e = None

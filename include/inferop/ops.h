@@ -2,8 +2,8 @@
 //
 // Drop-in for the part of the reference's include/inferop/ops.h that this
 // library implements: identical names, namespaces, argument order, defaults
-// and error behaviour (reference: ops.h:19-25 device queries, :64-70 quant /
-// dequant, :81-84 GEMM).  Tensor arguments are caller-owned device pointers on
+// and error behaviour (reference: ops.h:19-25 device queries, :54-55 SwiGLU,
+// :64-70 quant / dequant, :81-84 GEMM, :108-110 MoE routing).  Tensor arguments are caller-owned device pointers on
 // the current device; `stream` is a cudaStream_t passed as void* (nullptr = the
 // default stream); calls enqueue work and return without synchronising.
 //
@@ -55,5 +55,16 @@ INFEROP_EXPORT void w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_
                          const void* b_scales, int64_t m, int64_t n, int64_t k,
                          int group_size = 128, int block_n = 128, dtype out_dt = dtype::bf16,
                          void* stream = nullptr);
+
+// out[t, i] = silu(gate_up[t, i]) * gate_up[t, d + i];  gate_up [tokens, 2d], out [tokens, d] in dt.
+INFEROP_EXPORT void silu_and_mul(void* out, const void* gate_up, dtype dt, int64_t tokens, int64_t d,
+                  void* stream = nullptr);
+
+// MoE routing: softmax over logits [tokens, num_experts] (fp32) + top-k.
+//   topk_weights fp32 [tokens, topk] (softmax probability, renormalised over the k when asked)
+//   topk_ids     int32 [tokens, topk]; equal probabilities: the lower expert index first
+// num_experts <= 1024, topk <= num_experts; anything else is a silent no-op.
+INFEROP_EXPORT void topk_softmax(int32_t* topk_ids, void* topk_weights, const void* logits, int tokens,
+                  int num_experts, int topk, bool renormalize = true, void* stream = nullptr);
 
 }  // namespace inferop

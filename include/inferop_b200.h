@@ -131,6 +131,81 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm_allgather(void* const* c_peers, int3
                                           int32_t group_size, int32_t block_n, int32_t out_dt,
                                           void* stream);
 
+/* ---- mixture-of-experts layer around the grouped GEMM
+ * Every step stays on the device: the experts' row counts are never copied to the host, the
+ * grouped GEMM reads the M-tile list that inferop_moe_align wrote.  The steps of a layer:
+ *   inferop_topk_softmax -> inferop_moe_align -> inferop_moe_scatter_quant ->
+ *   inferop_w8a8_block_fp8_gemm_grouped_tiles (gate_up) -> inferop_silu_and_mul_quant ->
+ *   inferop_w8a8_block_fp8_gemm_grouped_tiles (down) -> inferop_moe_combine
+ */
+
+/* Routing (reference include/inferop/ops.h:108-110, kernels/moe/topk_softmax.cu:18-97, CPU
+ * reference/reference.cpp:152-181): softmax over logits [tokens, num_experts] (fp32), the topk
+ * experts by probability (lower index first on equal probabilities) into topk_ids
+ * [tokens, topk] (int32) and their probabilities into topk_weights [tokens, topk] (fp32),
+ * divided by their sum when `renormalize`.  num_experts <= 1024, topk <= num_experts;
+ * anything else is INFEROP_ERR_SHAPE (the reference: silent no-op).  Logits must be finite. */
+INFEROP_API int inferop_topk_softmax(int32_t* topk_ids, void* topk_weights, const void* logits, int32_t tokens,
+                         int32_t num_experts, int32_t topk, int32_t renormalize, void* stream);
+
+/* SwiGLU (reference include/inferop/ops.h:54-55, kernels/silu_mul.cu:16-28, CPU
+ * reference/reference.cpp:55-63): out[t, i] = silu(gate_up[t, i]) * gate_up[t, d + i] for
+ * gate_up [tokens, 2d] and out [tokens, d] in dt (0 fp32, 1 fp16, 2 bf16), computed in fp32. */
+INFEROP_API int inferop_silu_and_mul(void* out, const void* gate_up, int32_t dt, int64_t tokens, int64_t d,
+                         void* stream);
+
+/* inferop_silu_and_mul followed by inferop_quant_fp8_per_token_group in one pass, bit for bit
+ * the result of the two calls (reference ops.h:54-55 then :64-65): q [tokens, d] E4M3 and scales
+ * [tokens, d/128] from gate_up [tokens, 2d] in dt (1 fp16, 2 bf16; the SwiGLU value is rounded
+ * to dt before it is quantised, as the separate kernels store it).  d % 128 == 0, group 128,
+ * gate_up 16-byte and q 8-byte aligned. */
+INFEROP_API int inferop_silu_and_mul_quant(void* q, void* scales, const void* gate_up, int32_t dt, int64_t tokens,
+                               int64_t d, int32_t group_size, void* stream);
+
+/* Upper bound on the M-tiles inferop_moe_align can produce: size of tile_row0 / tile_meta. */
+INFEROP_API int64_t inferop_moe_max_mtiles(int64_t tokens, int32_t topk, int32_t num_experts);
+
+/* Expert-sorted layout of a routing (no reference counterpart: the reference runs one GEMM per
+ * expert from the host).  From topk_ids [tokens, topk] (device):
+ *   counts [num_experts]       rows per expert
+ *   offsets [num_experts + 1]  first sorted row of each expert, offsets[num_experts] = pairs
+ *   pos [tokens * topk]        sorted row of pair (token, k); pairs of one expert keep their
+ *                              (token, k) order; -1 for an id outside [0, num_experts)
+ *   src_token [tokens * topk]  token of each sorted row
+ *   tile_row0 / tile_meta [inferop_moe_max_mtiles]  M-tiles of up to 128 rows that never span
+ *                              two experts: first row, and (expert << 8) | (rows - 1)
+ *   num_mtiles [1]             how many tiles were written
+ * all int32 device arrays.  One CTA; num_experts <= 1024. */
+INFEROP_API int inferop_moe_align(const int32_t* topk_ids, int64_t tokens, int32_t topk, int32_t num_experts,
+                      int32_t* counts, int32_t* offsets, int32_t* pos, int32_t* src_token,
+                      int32_t* tile_row0, int32_t* tile_meta, int32_t* num_mtiles, void* stream);
+
+/* Quantise x [tokens, cols] (dt 1 fp16 / 2 bf16) per 1x128 group, exactly as
+ * inferop_quant_fp8_per_token_group does, and write every token's bytes and scales to the
+ * sorted rows pos[token * topk + k] of q [tokens * topk, cols] and scales
+ * [tokens * topk, cols/128] (rows with pos < 0 are skipped). */
+INFEROP_API int inferop_moe_scatter_quant(void* q, void* scales, const void* x, int32_t dt, const int32_t* pos,
+                              int64_t tokens, int64_t cols, int32_t topk, int32_t group_size,
+                              void* stream);
+
+/* out[t, :] = sum_k topk_weights[t, k] * y[pos[t * topk + k], :] for y [tokens * topk, hidden]
+ * and out [tokens, hidden] in dt (1 fp16 / 2 bf16): products and sums in fp32, each rounded, in
+ * the order of k, the result rounded once.  hidden % 8 == 0; out and y 16-byte aligned. */
+INFEROP_API int inferop_moe_combine(void* out, const void* y, const void* topk_weights, const int32_t* pos, int32_t dt,
+                        int64_t tokens, int64_t hidden, int32_t topk, void* stream);
+
+/* inferop_w8a8_block_fp8_gemm_grouped with the tile list in device memory (as written by
+ * inferop_moe_align) instead of host row counts: nothing is read on the host, so the call can
+ * follow the routing kernels on the stream without a synchronisation.  a_q / c have m_total
+ * rows; max_mtiles bounds the list (inferop_moe_max_mtiles), *num_mtiles is its length. */
+INFEROP_API int inferop_w8a8_block_fp8_gemm_grouped_tiles(void* c, const void* a_q, const void* a_scales,
+                                              const void* b_q, const void* b_scales,
+                                              const int32_t* tile_row0, const int32_t* tile_meta,
+                                              const int32_t* num_mtiles, int64_t max_mtiles,
+                                              int64_t m_total, int64_t groups, int64_t n, int64_t k,
+                                              int32_t group_size, int32_t block_n, int32_t out_dt,
+                                              void* stream);
+
 /* ---- blockwise-FP8 GEMM for a few tokens, with no allocation
  * No counterpart in the reference: added for callers that must not trigger a device
  * allocation, such as a server that gave all device memory to its own pool at start-up, or a

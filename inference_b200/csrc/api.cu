@@ -319,6 +319,121 @@ int inferop_w8a8_block_fp8_gemm_allgather(void* const* c_peers, int32_t n_peers,
                                out_dt, static_cast<cudaStream_t>(stream));
 }
 
+int inferop_topk_softmax(int32_t* topk_ids, void* topk_weights, const void* logits, int32_t tokens,
+                         int32_t num_experts, int32_t topk, int32_t renormalize, void* stream) {
+  if (tokens <= 0 || num_experts <= 0 || num_experts > 1024 || topk <= 0 || topk > num_experts) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (!topk_ids || !topk_weights || !logits) return INFEROP_ERR_POINTER;
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_topk_softmax(topk_ids, static_cast<float*>(topk_weights), static_cast<const float*>(logits),
+                             tokens, num_experts, topk, renormalize ? 1 : 0,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int inferop_silu_and_mul(void* out, const void* gate_up, int32_t dt, int64_t tokens, int64_t d,
+                         void* stream) {
+  if (tokens <= 0 || d <= 0) return INFEROP_ERR_SHAPE;
+  if (dt < 0 || dt > 2) return INFEROP_ERR_DTYPE;
+  if (!out || !gate_up) return INFEROP_ERR_POINTER;
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_silu_and_mul(out, gate_up, dt, tokens, d, static_cast<cudaStream_t>(stream), ctx->sm_count);
+}
+
+int inferop_silu_and_mul_quant(void* q, void* scales, const void* gate_up, int32_t dt, int64_t tokens,
+                               int64_t d, int32_t group_size, void* stream) {
+  if (tokens <= 0 || d <= 0 || group_size != 128 || d % 128 != 0) return INFEROP_ERR_SHAPE;
+  if (dt != 1 && dt != 2) return INFEROP_ERR_DTYPE;
+  if (!q || !scales || !gate_up) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(gate_up) & 15u) || (reinterpret_cast<uintptr_t>(q) & 7u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_silu_and_mul_quant(q, scales, gate_up, dt, tokens, d, static_cast<cudaStream_t>(stream),
+                                   ctx->sm_count);
+}
+
+int64_t inferop_moe_max_mtiles(int64_t tokens, int32_t topk, int32_t num_experts) {
+  if (tokens < 0 || topk <= 0 || num_experts <= 0) return 0;
+  return moe_max_mtiles(tokens * topk, num_experts);
+}
+
+int inferop_moe_align(const int32_t* topk_ids, int64_t tokens, int32_t topk, int32_t num_experts,
+                      int32_t* counts, int32_t* offsets, int32_t* pos, int32_t* src_token,
+                      int32_t* tile_row0, int32_t* tile_meta, int32_t* num_mtiles, void* stream) {
+  if (tokens <= 0 || topk <= 0 || num_experts <= 0 || num_experts > 1024) return INFEROP_ERR_SHAPE;
+  if (tokens * topk > 0x7FFFFF00LL || num_experts >= (1 << 22)) return INFEROP_ERR_LIMIT;
+  if (!topk_ids || !counts || !offsets || !pos || !src_token || !tile_row0 || !tile_meta || !num_mtiles) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_moe_align(topk_ids, tokens, topk, num_experts, counts, offsets, pos, src_token, tile_row0,
+                          tile_meta, num_mtiles, static_cast<cudaStream_t>(stream));
+}
+
+int inferop_moe_scatter_quant(void* q, void* scales, const void* x, int32_t dt, const int32_t* pos,
+                              int64_t tokens, int64_t cols, int32_t topk, int32_t group_size,
+                              void* stream) {
+  if (tokens <= 0 || cols <= 0 || topk <= 0 || group_size != 128 || cols % 128 != 0) return INFEROP_ERR_SHAPE;
+  if (dt != 1 && dt != 2) return INFEROP_ERR_DTYPE;
+  if (!q || !scales || !x || !pos) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(q) & 7u)) return INFEROP_ERR_POINTER;
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_moe_scatter_quant(q, scales, x, dt, pos, tokens, cols, topk,
+                                  static_cast<cudaStream_t>(stream), ctx->sm_count);
+}
+
+int inferop_moe_combine(void* out, const void* y, const void* topk_weights, const int32_t* pos, int32_t dt,
+                        int64_t tokens, int64_t hidden, int32_t topk, void* stream) {
+  if (tokens <= 0 || hidden <= 0 || topk <= 0 || hidden % 8 != 0) return INFEROP_ERR_SHAPE;
+  if (dt != 1 && dt != 2) return INFEROP_ERR_DTYPE;
+  if (!out || !y || !topk_weights || !pos) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(out) & 15u) || (reinterpret_cast<uintptr_t>(y) & 15u)) return INFEROP_ERR_POINTER;
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_moe_combine(out, y, static_cast<const float*>(topk_weights), pos, dt, tokens, hidden, topk,
+                            static_cast<cudaStream_t>(stream), ctx->sm_count);
+}
+
+int inferop_w8a8_block_fp8_gemm_grouped_tiles(void* c, const void* a_q, const void* a_scales,
+                                              const void* b_q, const void* b_scales,
+                                              const int32_t* tile_row0, const int32_t* tile_meta,
+                                              const int32_t* num_mtiles, int64_t max_mtiles,
+                                              int64_t m_total, int64_t groups, int64_t n, int64_t k,
+                                              int32_t group_size, int32_t block_n, int32_t out_dt,
+                                              void* stream) {
+  if (group_size != 128 || block_n != 128 || k <= 0 || k % 128 != 0 || n <= 0 || n % 128 != 0 ||
+      groups <= 0 || m_total <= 0 || max_mtiles <= 0) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (out_dt < 0 || out_dt > 2) return INFEROP_ERR_DTYPE;
+  if (m_total > 0x7FFFFF00LL || groups * n > 0x7FFFFF00LL || k > 0x7FFFFF00LL || groups >= (1 << 22)) {
+    return INFEROP_ERR_LIMIT;
+  }
+  if (!c || !a_q || !a_scales || !b_q || !b_scales || !tile_row0 || !tile_meta || !num_mtiles) {
+    return INFEROP_ERR_POINTER;
+  }
+  if ((reinterpret_cast<uintptr_t>(a_q) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_gemm_grouped_dev(ctx, c, a_q, a_scales, b_q, b_scales, tile_row0, tile_meta, num_mtiles,
+                                 max_mtiles, m_total, groups, n, k, out_dt, static_cast<cudaStream_t>(stream));
+}
+
 int inferop_device_status(uint32_t* out4, int reset) {
   int err;
   DeviceCtx* ctx = current_ctx(&err);
@@ -430,6 +545,16 @@ void w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, const v
             static_cast<long long>(k));
   }
   report("w8a8_block_fp8_gemm", rc);
+}
+
+void topk_softmax(int32_t* topk_ids, void* topk_weights, const void* logits, int tokens,
+                  int num_experts, int topk, bool renormalize, void* stream) {
+  report("topk_softmax", inferop_topk_softmax(topk_ids, topk_weights, logits, tokens, num_experts, topk,
+                                              renormalize ? 1 : 0, stream));
+}
+
+void silu_and_mul(void* out, const void* gate_up, dtype dt, int64_t tokens, int64_t d, void* stream) {
+  report("silu_and_mul", inferop_silu_and_mul(out, gate_up, static_cast<int32_t>(dt), tokens, d, stream));
 }
 
 }  // namespace inferop

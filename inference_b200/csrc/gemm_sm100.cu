@@ -121,8 +121,12 @@ struct TileInfo {
   int col;       // first output column
 };
 
-template <bool kGrouped>
-__device__ __forceinline__ TileInfo tile_info(int t, const struct GemmParams& p, const GroupTable* tab);
+// The tile list of a grouped launch as the kernel sees it: either the by-value GroupTable or
+// arrays that a kernel wrote to device memory (no host round trip for the experts' row counts).
+struct TileList {
+  const int* row0;
+  const int* meta;
+};
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
   const int per_band = group_m * tiles_n;
@@ -135,13 +139,13 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 }
 
 template <bool kGrouped>
-__device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p, const GroupTable* tab) {
+__device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p, const TileList& tab) {
   TileInfo ti;
   if (kGrouped) {
     const int mt = t / p.tiles_n, tn = t - mt * p.tiles_n;
-    const int meta = tab->meta[mt];
+    const int meta = tab.meta[mt];
     const int group = meta >> 8;
-    ti.a_row = tab->row0[mt];
+    ti.a_row = tab.row0[mt];
     ti.row_end = ti.a_row + (meta & 0xFF) + 1;
     ti.b_row = group * p.n + tn * BN;
     ti.sb_row = group * p.nb + tn * 2;
@@ -212,9 +216,14 @@ __device__ __forceinline__ void promote32(float2* acc, const uint32_t (&v)[32], 
 template <typename OutT, int kMode>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtensorMap* map_b,
                                           const CUtensorMap* map_c, const GemmParams& p,
-                                          const GroupTable* tab, const PeerMaps* peers) {
+                                          const TileList tab, const PeerMaps* peers,
+                                          const int* num_mtiles_dev) {
   constexpr bool kGrouped = kMode == kModeGrouped;
   constexpr bool kGather = kMode == kModeGather;
+  // a device-built tile list comes with its length in device memory (at most p.tiles_m entries)
+  const int num_tiles =
+      (kGrouped && num_mtiles_dev != nullptr) ? min(__ldg(num_mtiles_dev), p.tiles_m) * p.tiles_n
+                                              : p.num_tiles;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -258,7 +267,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_slot, 0);
-  const uint32_t my_tiles = (p.num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+  const uint32_t my_tiles =
+      static_cast<int>(blockIdx.x) < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
 
   if (warp < 4) {
     reg_dealloc<56>();
@@ -268,7 +278,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       uint32_t phase = 0;
       uint32_t armed = 0, armed_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
         const TileInfo ti = tile_info<kGrouped>(t, p, tab);
         for (int kb = 0; kb < p.kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty)) {
@@ -350,7 +360,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
     const bool issuer = (quarter == 0 && lane == 0);
     uint32_t kiter = 0;
     bool ok = true;
-    for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+    for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
       const TileInfo ti = tile_info<kGrouped>(t, p, tab);
       const int gm = ti.a_row + row;
       const int nbi = ti.sb_row + half;
@@ -468,7 +478,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
-  gemm_body<OutT, kModePlain>(&map_a, &map_b, &map_c, p, nullptr, nullptr);
+  gemm_body<OutT, kModePlain>(&map_a, &map_b, &map_c, p, TileList{nullptr, nullptr}, nullptr, nullptr);
 }
 
 template <typename OutT>
@@ -476,14 +486,42 @@ __global__ void __launch_bounds__(kThreads, 1)
 w8a8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_c, const GemmParams p,
                          const __grid_constant__ GroupTable tab) {
-  gemm_body<OutT, kModeGrouped>(&map_a, &map_b, &map_c, p, &tab, nullptr);
+  gemm_body<OutT, kModeGrouped>(&map_a, &map_b, &map_c, p, TileList{tab.row0, tab.meta}, nullptr, nullptr);
+}
+
+// grouped launch whose tile list (and its length) was written to device memory by moe_align
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_grouped_dev_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                             const __grid_constant__ CUtensorMap map_c, const GemmParams p,
+                             const int* __restrict__ row0, const int* __restrict__ meta,
+                             const int* __restrict__ num_mtiles) {
+  gemm_body<OutT, kModeGrouped>(&map_a, &map_b, &map_c, p, TileList{row0, meta}, nullptr, num_mtiles);
+}
+
+template <typename OutT>
+int launch_grouped_dev_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                         const GemmParams& p, const int* row0, const int* meta, const int* num_mtiles,
+                         int ctas, cudaStream_t stream) {
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(w8a8_grouped_dev_gemm_kernel<OutT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_done[dev] = true;
+  }
+  w8a8_grouped_dev_gemm_kernel<OutT><<<ctas, kThreads, kSmemBytes, stream>>>(ma, mb, mc, p, row0, meta,
+                                                                             num_mtiles);
+  return check_launch();
 }
 
 template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_gather_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const GemmParams p, const __grid_constant__ PeerMaps peers) {
-  gemm_body<OutT, kModeGather>(&map_a, &map_b, nullptr, p, nullptr, &peers);
+  gemm_body<OutT, kModeGather>(&map_a, &map_b, nullptr, p, TileList{nullptr, nullptr}, &peers, nullptr);
 }
 
 template <typename OutT>
@@ -709,6 +747,55 @@ int launch_gemm_allgather(DeviceCtx* ctx, void* const* c_peers, int32_t n_peers,
   if (ctas > p.num_tiles) ctas = p.num_tiles;
   return out_dt == 1 ? launch_gather_t<__half>(ma, mb, p, peers, ctas, stream)
                      : launch_gather_t<__nv_bfloat16>(ma, mb, p, peers, ctas, stream);
+}
+
+int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales,
+                            const void* b_q, const void* b_scales, const int32_t* tile_row0,
+                            const int32_t* tile_meta, const int32_t* num_mtiles, int64_t max_mtiles,
+                            int64_t m_total, int64_t groups, int64_t n, int64_t k, int32_t out_dt,
+                            cudaStream_t stream) {
+  const Options& opt = options();
+  const int out_bytes = (out_dt == 0) ? 4 : 2;
+  bool tma_store = out_bytes == 2 && (n * out_bytes) % 16 == 0 &&
+                   (reinterpret_cast<uintptr_t>(c) % 16 == 0);
+  if (opt.gemm_tma_store == 0) tma_store = false;
+  GemmParams p;
+  p.a_scales = static_cast<const float*>(a_scales);
+  p.b_scales = static_cast<const float*>(b_scales);
+  p.c = c;
+  p.m = static_cast<int>(m_total);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.kb = static_cast<int>(k / 128);
+  p.nb = static_cast<int>(n / 128);
+  p.tiles_n = static_cast<int>((n + BN - 1) / BN);
+  p.tiles_m = static_cast<int>(max_mtiles);   // upper bound; the real count is read on the device
+  const int64_t tiles = max_mtiles * p.tiles_n;
+  if (tiles > 0x7FFFFFFF || tiles * p.kb > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
+  p.num_tiles = static_cast<int>(tiles);
+  p.tma_store = tma_store ? 1 : 0;
+  p.group_m = 32;
+  p.status = ctx->status;
+
+  CUtensorMap ma, mb, mc;
+  int rc = make_tensor_map_2d(&ma, a_q, 1, m_total, k, k, BM, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  rc = make_tensor_map_2d(&mb, b_q, 1, groups * n, k, k, BN, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  if (tma_store) {
+    rc = make_tensor_map_2d(&mc, c, 2, m_total, n, n * 2, 128, 64, true);
+    if (rc != INFEROP_OK) return rc;
+  } else {
+    mc = ma;
+  }
+  int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
+  if (ctas > p.num_tiles) ctas = p.num_tiles;
+  switch (out_dt) {
+    case 0: return launch_grouped_dev_t<float>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
+    case 1: return launch_grouped_dev_t<__half>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
+    case 2: return launch_grouped_dev_t<__nv_bfloat16>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
+    default: return INFEROP_ERR_DTYPE;
+  }
 }
 
 }  // namespace ib200

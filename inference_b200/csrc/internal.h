@@ -71,6 +71,30 @@ int launch_gemm_allgather(DeviceCtx* ctx, void* const* c_peers, int32_t n_peers,
                           const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
                           cudaStream_t stream);
 
+// Grouped launch whose M-tile list and its length live in device memory (written by moe_align);
+// max_mtiles bounds the list, m_total is the number of rows of a_q / c.
+int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales,
+                            const void* b_q, const void* b_scales, const int32_t* tile_row0,
+                            const int32_t* tile_meta, const int32_t* num_mtiles, int64_t max_mtiles,
+                            int64_t m_total, int64_t groups, int64_t n, int64_t k, int32_t out_dt,
+                            cudaStream_t stream);
+
+// moe.cu
+int launch_topk_softmax(int32_t* ids, float* weights, const float* logits, int32_t tokens,
+                        int32_t experts, int32_t topk, int32_t renorm, cudaStream_t stream);
+int launch_silu_and_mul(void* out, const void* gate_up, int32_t dt, int64_t rows, int64_t d,
+                        cudaStream_t stream, int sms);
+int launch_silu_and_mul_quant(void* q, void* scales, const void* gate_up, int32_t dt, int64_t rows,
+                              int64_t d, cudaStream_t stream, int sms);
+int64_t moe_max_mtiles(int64_t pairs, int64_t experts);
+int launch_moe_align(const int32_t* ids, int64_t tokens, int32_t topk, int32_t experts, int32_t* counts,
+                     int32_t* offsets, int32_t* pos, int32_t* src_token, int32_t* tile_row0,
+                     int32_t* tile_meta, int32_t* num_mtiles, cudaStream_t stream);
+int launch_moe_scatter_quant(void* q, void* scales, const void* x, int32_t dt, const int32_t* pos,
+                             int64_t tokens, int64_t cols, int32_t topk, cudaStream_t stream, int sms);
+int launch_moe_combine(void* out, const void* y, const float* w, const int32_t* pos, int32_t dt,
+                       int64_t tokens, int64_t hidden, int32_t topk, cudaStream_t stream, int sms);
+
 // gemm_decode_sm100.cu : small-M path (M <= kDecodeMaxM).  workspace holds
 // decode_workspace_bytes(sm_count) bytes, counters kDecodeMaxTiles zeroed ints; both are
 // owned by the caller of launch_gemm_decode and must not be shared by launches that can

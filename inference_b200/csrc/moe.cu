@@ -1,0 +1,548 @@
+// Mixture-of-experts kernels around the grouped blockwise-FP8 GEMM, for sm_100a:
+//
+//   topk_softmax           routing: softmax over the expert logits + top-k
+//                          (reference kernels/moe/topk_softmax.cu:18-97, CPU reference/reference.cpp:152-181)
+//   moe_align              expert histogram, row offsets, M-tile table and the stable
+//                          expert-sorted position of every (token, k) pair, all on the device
+//   moe_scatter_quant      quantise each token row once (1x128 groups, bit-identical to
+//                          quant_fp8_per_token_group) and write it to its top-k sorted positions
+//   silu_and_mul           SwiGLU between the two expert GEMMs
+//                          (reference kernels/silu_mul.cu:16-28, CPU reference/reference.cpp:55-63)
+//   silu_and_mul_quant     the same followed by the per-token-group quantisation, in one pass
+//   moe_combine            out[t] = sum_k w[t,k] * y[position(t,k)]
+//
+// All of them are HBM-bound (or latency-bound at these sizes); none touches the tensor cores.
+// Nothing here synchronises with the host: the row counts of the experts never leave the
+// device, the grouped GEMM reads the tile table that moe_align wrote.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "internal.h"
+#include "quant_math.cuh"
+
+namespace ib200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------------------------------------
+// Routing.  One warp per token; lane l holds experts l, l + 32, ... in registers, so the row is
+// read once with coalesced loads and nothing goes through shared memory.  Ordering rule of the
+// reference (reference.cpp:166-170): higher probability first, lower expert index on equal
+// probabilities; the comparison is made on the fp32 probabilities exp(logit - max), as there.
+// weight = p / sum(p), divided again by the sum of the k weights when `renorm`.
+template <int kPerLane>
+__global__ void __launch_bounds__(kThreads)
+topk_softmax_kernel(int32_t* __restrict__ ids, float* __restrict__ weights,
+                    const float* __restrict__ logits, int tokens, int experts, int topk, int renorm) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const float* row = logits + static_cast<int64_t>(t) * experts;
+  float p[kPerLane];
+  float mx = -CUDART_INF_F;
+#pragma unroll
+  for (int j = 0; j < kPerLane; ++j) {
+    const int e = j * 32 + lane;
+    p[j] = e < experts ? __ldg(row + e) : -CUDART_INF_F;
+    mx = fmaxf(mx, p[j]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+  float l = 0.0f;
+#pragma unroll
+  for (int j = 0; j < kPerLane; ++j) {
+    const int e = j * 32 + lane;
+    if (e < experts) {
+      p[j] = expf(p[j] - mx);
+      l += p[j];
+    } else {
+      p[j] = -1.0f;  // below every probability: never selected
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xFFFFFFFFu, l, o);
+
+  float wsum = 0.0f;
+  int32_t* my_ids = ids + static_cast<int64_t>(t) * topk;
+  float* my_w = weights + static_cast<int64_t>(t) * topk;
+  for (int k = 0; k < topk; ++k) {
+    float bv = -1.0f;
+    int bi = 0x7FFFFFFF;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      if (p[j] > bv) {  // ascending index inside the lane: the lower index keeps a tie
+        bv = p[j];
+        bi = j * 32 + lane;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+      const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    // every lane now holds the winner; its owner retires it
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      if (j * 32 + lane == bi) p[j] = -1.0f;
+    }
+    const float w = bv / l;
+    wsum += w;
+    if (lane == 0) {
+      my_ids[k] = bi;
+      my_w[k] = w;
+    }
+  }
+  if (renorm && wsum > 0.0f) {
+    __syncwarp();
+    for (int k = lane; k < topk; k += 32) my_w[k] = my_w[k] / wsum;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU.  gate_up [rows, 2d]: out[r, i] = silu(gate_up[r, i]) * gate_up[r, d + i], computed in
+// fp32 (silu(g) = g / (1 + exp(-g))) and rounded once to the output type.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  return (g / (1.0f + expf(-g))) * u;
+}
+
+template <typename T>
+__device__ __forceinline__ float ld_f32(const T* p);
+template <>
+__device__ __forceinline__ float ld_f32(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ld_f32(const __half* p) { return __half2float(*p); }
+template <>
+__device__ __forceinline__ float ld_f32(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T>
+__device__ __forceinline__ T st_from_f32(float v);
+template <>
+__device__ __forceinline__ float st_from_f32(float v) { return v; }
+template <>
+__device__ __forceinline__ __half st_from_f32(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 st_from_f32(float v) { return __float2bfloat16_rn(v); }
+
+// eight 16-bit values of one 16-byte word <-> floats
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]);
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& raw, float (&f)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4& raw, float (&f)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack2_rn(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2_rn<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2_rn<__half>(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// eight SwiGLU outputs from eight gates and eight ups, rounded to T and packed
+template <typename T>
+__device__ __forceinline__ uint4 silu_mul8(const uint4& g_raw, const uint4& u_raw) {
+  float g[8], u[8];
+  unpack8<T>(g_raw, g);
+  unpack8<T>(u_raw, u);
+  uint4 o;
+  o.x = pack2_rn<T>(silu_mul(g[0], u[0]), silu_mul(g[1], u[1]));
+  o.y = pack2_rn<T>(silu_mul(g[2], u[2]), silu_mul(g[3], u[3]));
+  o.z = pack2_rn<T>(silu_mul(g[4], u[4]), silu_mul(g[5], u[5]));
+  o.w = pack2_rn<T>(silu_mul(g[6], u[6]), silu_mul(g[7], u[7]));
+  return o;
+}
+
+// 16-bit types, d % 8 == 0, 16-byte aligned: one thread per 8 outputs
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int64_t rows, int64_t d8) {
+  const int64_t total = rows * d8;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t r = i / d8, c = i - r * d8;
+    const uint4* row = reinterpret_cast<const uint4*>(gate_up) + r * 2 * d8;
+    const uint4 g = __ldg(row + c);
+    const uint4 u = __ldg(row + d8 + c);
+    reinterpret_cast<uint4*>(out)[i] = silu_mul8<T>(g, u);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+silu_mul_any_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int64_t rows, int64_t d) {
+  const int64_t total = rows * d;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t r = i / d, c = i - r * d;
+    const T* row = gate_up + r * 2 * d;
+    out[i] = st_from_f32<T>(silu_mul(ld_f32(row + c), ld_f32(row + d + c)));
+  }
+}
+
+// SwiGLU + per-token-group quantisation (groups of 128 outputs): sixteen lanes own one group,
+// each lane 8 outputs.  The SwiGLU result is rounded to T first, exactly as the two separate
+// kernels would store and reload it, so bytes and scales equal theirs bit for bit.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+silu_mul_quant_kernel(uint8_t* __restrict__ q, float* __restrict__ scales,
+                      const T* __restrict__ gate_up, int64_t rows, int64_t d) {
+  using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+  const int sub = threadIdx.x & 15;
+  const int64_t gpr = d / 128;  // groups per row
+  const int64_t groups = rows * gpr;
+  const int64_t hw = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 4;
+  const int64_t hw_total = (static_cast<int64_t>(gridDim.x) * kThreads) >> 4;
+  const int64_t warp_first = hw & ~int64_t(1);
+  for (int64_t base = 0; warp_first + base < groups; base += hw_total) {
+    const int64_t g = hw + base;
+    const bool live = g < groups;
+    uint4 h = make_uint4(0u, 0u, 0u, 0u);
+    if (live) {
+      const int64_t r = g / gpr, c = g - r * gpr;
+      const T* row = gate_up + r * 2 * d + c * 128 + sub * 8;
+      h = silu_mul8<T>(__ldg(reinterpret_cast<const uint4*>(row)), __ldg(reinterpret_cast<const uint4*>(row + d)));
+    }
+    float f[8];
+    unpack8<T>(h, f);
+    float amax = absmax8_packed<T2>(h);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    const float scale = group_scale(amax);
+    if (live) {
+      const uint2 bytes = fast_div_ok(amax) ? quantise8_fast16(h, f, scale, __frcp_rn(scale))
+                                            : quantise8<false>(f, scale, 0.0f);
+      *reinterpret_cast<uint2*>(q + g * 128 + sub * 8) = bytes;
+      if (sub == 0) scales[g] = scale;
+    }
+  }
+}
+
+int grid_for(int64_t blocks, int sms, int per_sm) {
+  const int64_t cap = static_cast<int64_t>(sms) * per_sm;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks);
+}
+
+}  // namespace
+
+int launch_topk_softmax(int32_t* ids, float* weights, const float* logits, int32_t tokens,
+                        int32_t experts, int32_t topk, int32_t renorm, cudaStream_t stream) {
+  const int grid = (tokens + kThreads / 32 - 1) / (kThreads / 32);
+#define IB200_TOPK(N)                                                                            \
+  topk_softmax_kernel<N><<<grid, kThreads, 0, stream>>>(ids, weights, logits, tokens, experts, \
+                                                        topk, renorm)
+  if (experts <= 32) IB200_TOPK(1);
+  else if (experts <= 64) IB200_TOPK(2);
+  else if (experts <= 128) IB200_TOPK(4);
+  else if (experts <= 256) IB200_TOPK(8);
+  else if (experts <= 512) IB200_TOPK(16);
+  else IB200_TOPK(32);
+#undef IB200_TOPK
+  return check_launch();
+}
+
+int launch_silu_and_mul(void* out, const void* gate_up, int32_t dt, int64_t rows, int64_t d,
+                        cudaStream_t stream, int sms) {
+  const bool vec = dt != 0 && d % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(gate_up) % 16 == 0;
+  if (vec) {
+    const int64_t d8 = d / 8;
+    const int grid = grid_for((rows * d8 + kThreads - 1) / kThreads, sms, 8);
+    if (dt == 1) {
+      silu_mul_vec_kernel<__half><<<grid, kThreads, 0, stream>>>(
+          static_cast<__half*>(out), static_cast<const __half*>(gate_up), rows, d8);
+    } else {
+      silu_mul_vec_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(
+          static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(gate_up), rows, d8);
+    }
+    return check_launch();
+  }
+  const int grid = grid_for((rows * d + kThreads - 1) / kThreads, sms, 8);
+  switch (dt) {
+    case 0: silu_mul_any_kernel<float><<<grid, kThreads, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(gate_up), rows, d); break;
+    case 1: silu_mul_any_kernel<__half><<<grid, kThreads, 0, stream>>>(static_cast<__half*>(out), static_cast<const __half*>(gate_up), rows, d); break;
+    case 2: silu_mul_any_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(gate_up), rows, d); break;
+    default: return INFEROP_ERR_DTYPE;
+  }
+  return check_launch();
+}
+
+int launch_silu_and_mul_quant(void* q, void* scales, const void* gate_up, int32_t dt, int64_t rows,
+                              int64_t d, cudaStream_t stream, int sms) {
+  const int64_t groups = rows * (d / 128);
+  const int grid = grid_for((groups + kThreads / 16 - 1) / (kThreads / 16), sms, 8);
+  if (dt == 1) {
+    silu_mul_quant_kernel<__half><<<grid, kThreads, 0, stream>>>(
+        static_cast<uint8_t*>(q), static_cast<float*>(scales), static_cast<const __half*>(gate_up), rows, d);
+  } else if (dt == 2) {
+    silu_mul_quant_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(
+        static_cast<uint8_t*>(q), static_cast<float*>(scales), static_cast<const __nv_bfloat16*>(gate_up), rows, d);
+  } else {
+    return INFEROP_ERR_DTYPE;
+  }
+  return check_launch();
+}
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// moe_align: everything the grouped GEMM and the scatter / combine kernels need to know about a
+// routing, computed by one CTA of 1024 threads without leaving the device.
+//   counts[e]        rows routed to expert e
+//   offsets[e]       first row of expert e in the expert-sorted order (offsets[experts] = pairs)
+//   pos[i]           sorted row of pair i = token * topk + k; inside an expert the pairs keep
+//                    their order of i (a stable counting sort), so the layout is deterministic
+//   src_token[r]     token whose copy sits in sorted row r
+//   tile_row0/meta   the experts' rows cut into M-tiles of up to 128 rows (first row, and
+//                    (expert << 8) | (rows - 1)); num_mtiles[0] = how many
+// The 32 warps take contiguous chunks of the pairs.  A per-warp histogram, an exclusive scan over
+// the experts and a scan over the warps give every (warp, expert) its first row; each warp then
+// walks its chunk in order, 32 pairs at a time, ranking equal experts by lane.
+constexpr int kAlignThreads = 1024;
+constexpr int kAlignWarps = kAlignThreads / 32;
+
+__global__ void __launch_bounds__(kAlignThreads, 1)
+moe_align_kernel(const int32_t* __restrict__ ids, int pairs, int topk, int experts,
+                 int32_t* __restrict__ counts, int32_t* __restrict__ offsets, int32_t* __restrict__ pos,
+                 int32_t* __restrict__ src_token, int32_t* __restrict__ tile_row0,
+                 int32_t* __restrict__ tile_meta, int32_t* __restrict__ num_mtiles) {
+  extern __shared__ int32_t align_smem[];
+  int32_t* hist = align_smem;                                   // [kAlignWarps][experts]
+  unsigned long long* scan = reinterpret_cast<unsigned long long*>(hist + kAlignWarps * experts);  // [1024]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int i = tid; i < kAlignWarps * experts; i += kAlignThreads) hist[i] = 0;
+  __syncthreads();
+
+  const int chunk = ((pairs + kAlignWarps - 1) / kAlignWarps + 31) & ~31;
+  const int begin = min(pairs, warp * chunk), end = min(pairs, begin + chunk);
+  int32_t* my_hist = hist + warp * experts;
+  for (int i = begin + lane; i < end; i += 32) {
+    const int e = __ldg(ids + i);
+    if (e >= 0 && e < experts) atomicAdd(&my_hist[e], 1);
+  }
+  __syncthreads();
+
+  // per expert: rows of the warps before this one, and the expert's total
+  int count = 0;
+  if (tid < experts) {
+    for (int w = 0; w < kAlignWarps; ++w) {
+      const int c = hist[w * experts + tid];
+      hist[w * experts + tid] = count;
+      count += c;
+    }
+  }
+  const int tiles = (count + 127) >> 7;
+  // inclusive scan over the experts of (tiles, rows) packed into one 64-bit word
+  unsigned long long v = (static_cast<unsigned long long>(tiles) << 32) | static_cast<unsigned>(count);
+  scan[tid] = v;
+  __syncthreads();
+  for (int o = 1; o < kAlignThreads; o <<= 1) {
+    const unsigned long long add = tid >= o ? scan[tid - o] : 0ull;
+    __syncthreads();
+    v += add;
+    scan[tid] = v;
+    __syncthreads();
+  }
+  const int row_first = static_cast<int>(v & 0xFFFFFFFFull) - count;   // exclusive
+  const int tile_first = static_cast<int>(v >> 32) - tiles;
+  if (tid < experts) {
+    counts[tid] = count;
+    offsets[tid] = row_first;
+    for (int w = 0; w < kAlignWarps; ++w) hist[w * experts + tid] += row_first;
+    for (int j = 0; j < tiles; ++j) {
+      tile_row0[tile_first + j] = row_first + j * 128;
+      tile_meta[tile_first + j] = (tid << 8) | (min(128, count - j * 128) - 1);
+    }
+  }
+  if (tid == kAlignThreads - 1) {
+    offsets[experts] = static_cast<int>(v & 0xFFFFFFFFull);
+    num_mtiles[0] = static_cast<int>(v >> 32);
+  }
+  __syncthreads();
+
+  for (int i0 = begin; i0 < end; i0 += 32) {
+    const int i = i0 + lane;
+    int e = i < end ? __ldg(ids + i) : -1;
+    if (e >= experts) e = -1;
+    // lanes without a valid expert get distinct keys so that they match nobody
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e >= 0 ? e : -1 - lane);
+    int row = -1;
+    if (e >= 0) row = my_hist[e] + __popc(peers & ((1u << lane) - 1u));
+    __syncwarp();
+    if (e >= 0 && lane == 31 - __clz(peers)) my_hist[e] = row + 1;   // the last of the equals
+    __syncwarp();
+    if (i < end) {
+      pos[i] = row;
+      if (row >= 0) src_token[row] = i / topk;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// moe_scatter_quant: x [tokens, cols] (bf16 / fp16) -> q [pairs, cols], scales [pairs, cols/128]
+// in expert-sorted row order.  A token row is quantised once (the arithmetic of quant128_kernel)
+// and its bytes and scales are written to the sorted rows of its top-k copies.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+moe_scatter_quant_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, const T* __restrict__ x,
+                         const int32_t* __restrict__ pos, int64_t tokens, int64_t cols, int topk) {
+  using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+  constexpr int kUnroll = 2;
+  const int sub = threadIdx.x & 15;
+  const int64_t gpr = cols / 128;
+  const int64_t groups = tokens * gpr;
+  const int64_t hw = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 4;
+  const int64_t hw_total = (static_cast<int64_t>(gridDim.x) * kThreads) >> 4;
+  const int64_t warp_first = hw & ~int64_t(1);
+  for (int64_t base = 0; warp_first + base < groups; base += hw_total * kUnroll) {
+    uint4 raw[kUnroll];
+    bool live[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t g = hw + base + u * hw_total;
+      live[u] = g < groups;
+      raw[u] = live[u] ? __ldg(reinterpret_cast<const uint4*>(x + g * 128 + sub * 8)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t g = hw + base + u * hw_total;
+      float f[8];
+      unpack8<T>(raw[u], f);
+      float amax = absmax8_packed<T2>(raw[u]);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      const float scale = group_scale(amax);
+      if (live[u]) {
+        const uint2 bytes = fast_div_ok(amax) ? quantise8_fast16(raw[u], f, scale, __frcp_rn(scale))
+                                              : quantise8<false>(f, scale, 0.0f);
+        const int64_t t = g / gpr, c = g - t * gpr;
+        for (int k = 0; k < topk; ++k) {
+          const int64_t r = __ldg(pos + t * topk + k);
+          if (r < 0) continue;
+          *reinterpret_cast<uint2*>(q + r * cols + c * 128 + sub * 8) = bytes;
+          if (sub == 0) scales[r * gpr + c] = scale;
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// moe_combine: out[t, :] = sum over k (in order) of w[t, k] * y[pos[t, k], :], every product and
+// every sum rounded to fp32, the result rounded once to the output type.  One thread per 8 columns.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+moe_combine_kernel(T* __restrict__ out, const T* __restrict__ y, const float* __restrict__ w,
+                   const int32_t* __restrict__ pos, int64_t tokens, int64_t h8, int topk) {
+  const int64_t total = tokens * h8;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t t = i / h8, c = i - t * h8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    for (int k = 0; k < topk; ++k) {
+      const int64_t r = __ldg(pos + t * topk + k);
+      if (r < 0) continue;
+      const float wk = __ldg(w + t * topk + k);
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(y) + r * h8 + c);
+      float f[8];
+      unpack8<T>(raw, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(wk, f[j]));
+    }
+    uint4 o;
+    o.x = pack2_rn<T>(acc[0], acc[1]);
+    o.y = pack2_rn<T>(acc[2], acc[3]);
+    o.z = pack2_rn<T>(acc[4], acc[5]);
+    o.w = pack2_rn<T>(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+}  // namespace
+
+int64_t moe_max_mtiles(int64_t pairs, int64_t experts) {
+  // every expert adds at most one partly filled tile to the full ones
+  return pairs / 128 + experts;
+}
+
+int launch_moe_align(const int32_t* ids, int64_t tokens, int32_t topk, int32_t experts, int32_t* counts,
+                     int32_t* offsets, int32_t* pos, int32_t* src_token, int32_t* tile_row0,
+                     int32_t* tile_meta, int32_t* num_mtiles, cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(kAlignWarps) * experts * 4 + kAlignThreads * 8;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(moe_align_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kAlignWarps * 1024 * 4 + kAlignThreads * 8);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_done[dev] = true;
+  }
+  moe_align_kernel<<<1, kAlignThreads, smem, stream>>>(ids, static_cast<int>(tokens * topk), topk, experts,
+                                                       counts, offsets, pos, src_token, tile_row0,
+                                                       tile_meta, num_mtiles);
+  return check_launch();
+}
+
+int launch_moe_scatter_quant(void* q, void* scales, const void* x, int32_t dt, const int32_t* pos,
+                             int64_t tokens, int64_t cols, int32_t topk, cudaStream_t stream, int sms) {
+  const int64_t groups = tokens * (cols / 128);
+  const int grid = grid_for((groups + (kThreads / 16) * 2 - 1) / ((kThreads / 16) * 2), sms, 8);
+  if (dt == 1) {
+    moe_scatter_quant_kernel<__half><<<grid, kThreads, 0, stream>>>(
+        static_cast<uint8_t*>(q), static_cast<float*>(scales), static_cast<const __half*>(x), pos, tokens, cols, topk);
+  } else if (dt == 2) {
+    moe_scatter_quant_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(
+        static_cast<uint8_t*>(q), static_cast<float*>(scales), static_cast<const __nv_bfloat16*>(x), pos, tokens, cols, topk);
+  } else {
+    return INFEROP_ERR_DTYPE;
+  }
+  return check_launch();
+}
+
+int launch_moe_combine(void* out, const void* y, const float* w, const int32_t* pos, int32_t dt,
+                       int64_t tokens, int64_t hidden, int32_t topk, cudaStream_t stream, int sms) {
+  const int64_t h8 = hidden / 8;
+  const int grid = grid_for((tokens * h8 + kThreads - 1) / kThreads, sms, 8);
+  if (dt == 1) {
+    moe_combine_kernel<__half><<<grid, kThreads, 0, stream>>>(static_cast<__half*>(out), static_cast<const __half*>(y), w, pos, tokens, h8, topk);
+  } else if (dt == 2) {
+    moe_combine_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(y), w, pos, tokens, h8, topk);
+  } else {
+    return INFEROP_ERR_DTYPE;
+  }
+  return check_launch();
+}
+
+}  // namespace ib200
+

@@ -188,6 +188,135 @@ def w8a8_block_fp8_gemm_allgather(peer_ptrs, rank: int, a_q: torch.Tensor, a_sca
               "w8a8_block_fp8_gemm_allgather")
 
 
+# --------------------------------------------------------------------------- mixture of experts
+def topk_softmax(logits: torch.Tensor, topk: int, renormalize: bool = True, ids: torch.Tensor | None = None,
+                 weights: torch.Tensor | None = None, stream=None):
+    """Routing: softmax over logits [tokens, experts] (fp32) + top-k -> (ids int32, weights fp32),
+    both [tokens, topk] (reference include/inferop/ops.h:108-110)."""
+    _dev_tensor(logits, "logits")
+    if logits.dtype != torch.float32:
+        raise ValueError("logits must be fp32")
+    tokens, experts = logits.shape
+    with torch.cuda.device(logits.device):
+        if ids is None:
+            ids = torch.empty((tokens, topk), dtype=torch.int32, device=logits.device)
+        if weights is None:
+            weights = torch.empty((tokens, topk), dtype=torch.float32, device=logits.device)
+        check(lib.inferop_topk_softmax(ids.data_ptr(), weights.data_ptr(), logits.data_ptr(), tokens, experts,
+                                       topk, 1 if renormalize else 0, _stream_ptr(stream)), "topk_softmax")
+    return ids, weights
+
+
+def silu_and_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, d + i] (reference include/inferop/ops.h:54-55)."""
+    _dev_tensor(gate_up, "gate_up")
+    tokens, d2 = gate_up.shape
+    with torch.cuda.device(gate_up.device):
+        if out is None:
+            out = torch.empty((tokens, d2 // 2), dtype=gate_up.dtype, device=gate_up.device)
+        check(lib.inferop_silu_and_mul(out.data_ptr(), gate_up.data_ptr(), int(_TORCH2CODE[gate_up.dtype]),
+                                       tokens, d2 // 2, _stream_ptr(stream)), "silu_and_mul")
+    return out
+
+
+def silu_and_mul_quant(gate_up: torch.Tensor, q: torch.Tensor | None = None,
+                       scales: torch.Tensor | None = None, stream=None):
+    """silu_and_mul followed by quant_fp8_per_token_group (group 128) in one pass, bit for bit."""
+    _dev_tensor(gate_up, "gate_up")
+    tokens, d2 = gate_up.shape
+    d = d2 // 2
+    with torch.cuda.device(gate_up.device):
+        if q is None:
+            q = torch.empty((tokens, d), dtype=torch.uint8, device=gate_up.device)
+        if scales is None:
+            scales = torch.empty((tokens, d // 128), dtype=torch.float32, device=gate_up.device)
+        check(lib.inferop_silu_and_mul_quant(q.data_ptr(), scales.data_ptr(), gate_up.data_ptr(),
+                                             int(_TORCH2CODE[gate_up.dtype]), tokens, d, 128,
+                                             _stream_ptr(stream)), "silu_and_mul_quant")
+    return q, scales
+
+
+class MoeLayout:
+    """Device arrays describing the expert-sorted order of a routing (see inferop_moe_align)."""
+
+    def __init__(self, tokens: int, topk: int, experts: int, device):
+        self.tokens, self.topk, self.experts = tokens, topk, experts
+        self.pairs = tokens * topk
+        self.max_mtiles = int(lib.inferop_moe_max_mtiles(tokens, topk, experts))
+        i32 = dict(dtype=torch.int32, device=device)
+        self.counts = torch.empty(experts, **i32)
+        self.offsets = torch.empty(experts + 1, **i32)
+        self.pos = torch.empty(self.pairs, **i32)
+        self.src_token = torch.empty(self.pairs, **i32)
+        self.tile_row0 = torch.empty(self.max_mtiles, **i32)
+        self.tile_meta = torch.empty(self.max_mtiles, **i32)
+        self.num_mtiles = torch.zeros(1, **i32)
+
+
+def moe_align(topk_ids: torch.Tensor, experts: int, layout: MoeLayout | None = None, stream=None) -> MoeLayout:
+    _dev_tensor(topk_ids, "topk_ids")
+    tokens, topk = topk_ids.shape
+    with torch.cuda.device(topk_ids.device):
+        if layout is None:
+            layout = MoeLayout(tokens, topk, experts, topk_ids.device)
+        check(lib.inferop_moe_align(topk_ids.data_ptr(), tokens, topk, experts, layout.counts.data_ptr(),
+                                    layout.offsets.data_ptr(), layout.pos.data_ptr(),
+                                    layout.src_token.data_ptr(), layout.tile_row0.data_ptr(),
+                                    layout.tile_meta.data_ptr(), layout.num_mtiles.data_ptr(),
+                                    _stream_ptr(stream)), "moe_align")
+    return layout
+
+
+def moe_scatter_quant(x: torch.Tensor, layout: MoeLayout, q: torch.Tensor | None = None,
+                      scales: torch.Tensor | None = None, stream=None):
+    """Quantise every token row once and write it to its top-k expert-sorted rows."""
+    _dev_tensor(x, "x")
+    tokens, cols = x.shape
+    with torch.cuda.device(x.device):
+        if q is None:
+            q = torch.empty((layout.pairs, cols), dtype=torch.uint8, device=x.device)
+        if scales is None:
+            scales = torch.empty((layout.pairs, cols // 128), dtype=torch.float32, device=x.device)
+        check(lib.inferop_moe_scatter_quant(q.data_ptr(), scales.data_ptr(), x.data_ptr(),
+                                            int(_TORCH2CODE[x.dtype]), layout.pos.data_ptr(), tokens, cols,
+                                            layout.topk, 128, _stream_ptr(stream)), "moe_scatter_quant")
+    return q, scales
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, layout: MoeLayout, out: torch.Tensor | None = None,
+                stream=None) -> torch.Tensor:
+    """out[t] = sum_k weights[t, k] * y[pos[t, k]]."""
+    _dev_tensor(y, "y")
+    _dev_tensor(weights, "weights")
+    hidden = y.shape[1]
+    with torch.cuda.device(y.device):
+        if out is None:
+            out = torch.empty((layout.tokens, hidden), dtype=y.dtype, device=y.device)
+        check(lib.inferop_moe_combine(out.data_ptr(), y.data_ptr(), weights.data_ptr(), layout.pos.data_ptr(),
+                                      int(_TORCH2CODE[y.dtype]), layout.tokens, hidden, layout.topk,
+                                      _stream_ptr(stream)), "moe_combine")
+    return out
+
+
+def w8a8_block_fp8_gemm_grouped_tiles(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: torch.Tensor,
+                                      b_scales: torch.Tensor, layout: MoeLayout, out_dtype=torch.bfloat16,
+                                      out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """The grouped GEMM driven by the device-side tile list of a MoeLayout (no host round trip)."""
+    for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
+        _dev_tensor(t, name)
+    groups, n, k = b_q.shape
+    m_total = a_q.shape[0]
+    with torch.cuda.device(a_q.device):
+        if out is None:
+            out = torch.empty((m_total, n), dtype=out_dtype, device=a_q.device)
+        check(lib.inferop_w8a8_block_fp8_gemm_grouped_tiles(
+            out.data_ptr(), a_q.data_ptr(), a_scales.data_ptr(), b_q.data_ptr(), b_scales.data_ptr(),
+            layout.tile_row0.data_ptr(), layout.tile_meta.data_ptr(), layout.num_mtiles.data_ptr(),
+            layout.max_mtiles, m_total, groups, n, k, 128, 128, int(_TORCH2CODE[out.dtype]),
+            _stream_ptr(stream)), "w8a8_block_fp8_gemm_grouped_tiles")
+    return out
+
+
 def device_status(reset: bool = True):
     """Synchronise and return the device-side status record (code, block, aux0, aux1)."""
     rec = (C.c_uint32 * 4)()

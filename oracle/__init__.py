@@ -182,6 +182,49 @@ def topk_softmax(logits, topk: int, renormalize: bool = True):
     return ids, w
 
 
+def silu_and_mul(gate_up):
+    """gate_up fp32 [tokens, 2d] -> fp32 [tokens, d] (reference/reference.cpp:55-63)."""
+    gate_up = _f32(gate_up)
+    t, d2 = gate_up.shape
+    out = np.empty((t, d2 // 2), np.float32)
+    if _lib.orc_silu_and_mul(_ptr(out), _ptr(gate_up), _i64(t), _i64(d2 // 2)) != 0:
+        raise ValueError("bad shape")
+    return out
+
+
+def moe_align(topk_ids, experts: int, tile_rows: int = 128):
+    """Expert-sorted layout of a routing: the checker of the device kernel that has no reference
+    counterpart (the reference loops over experts on the host).  Pairs (token, k) are sorted by
+    expert with a stable sort; returns counts, offsets, pos, src_token, tile_row0, tile_meta."""
+    ids = np.ascontiguousarray(topk_ids, dtype=np.int32)
+    t, topk = ids.shape
+    flat = ids.reshape(-1)
+    order = np.argsort(flat, kind="stable")
+    pos = np.empty(t * topk, np.int32)
+    pos[order] = np.arange(t * topk, dtype=np.int32)
+    counts = np.bincount(flat, minlength=experts).astype(np.int32)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    src_token = (order // topk).astype(np.int32)
+    row0, meta = [], []
+    for e in range(experts):
+        for r in range(0, int(counts[e]), tile_rows):
+            row0.append(int(offsets[e]) + r)
+            meta.append((e << 8) | (min(tile_rows, int(counts[e]) - r) - 1))
+    return counts, offsets, pos, src_token, np.array(row0, np.int32), np.array(meta, np.int32)
+
+
+def moe_combine(y, weights, pos):
+    """out[t] = sum_k w[t,k] * y[pos[t,k]] with every product and sum rounded to fp32, in the
+    order of k (y fp32 [pairs, hidden], weights fp32 [tokens, topk], pos int [tokens*topk])."""
+    y, weights = _f32(y), _f32(weights)
+    t, topk = weights.shape
+    p = np.asarray(pos).reshape(t, topk)
+    acc = np.zeros((t, y.shape[1]), np.float32)
+    for k in range(topk):
+        acc = acc + (weights[:, k:k + 1] * y[p[:, k]]).astype(np.float32)
+    return acc
+
+
 # ---------------------------------------------------------------- the reference itself
 class _Reference:
     """The reference's unmodified CPU functions (``oracle/_ref``), same signatures as above."""
@@ -259,6 +302,13 @@ class _Reference:
             self.lib.ref_w8a8_block_fp8_gemm_mt(_ptr(out), _ptr(aq), _ptr(a_s), _ptr(bq),
                                                 _ptr(bs), _i64(m), _i64(n), _i64(k),
                                                 _int(group_size), _int(block_n), _int(threads))
+        return out
+
+    def silu_and_mul(self, gate_up):
+        gate_up = _f32(gate_up)
+        t, d2 = gate_up.shape
+        out = np.empty((t, d2 // 2), np.float32)
+        self.lib.ref_silu_and_mul(_ptr(out), _ptr(gate_up), _i64(t), _i64(d2 // 2))
         return out
 
     def topk_softmax(self, logits, topk, renormalize=True):

@@ -251,3 +251,20 @@ int orc_topk_softmax(int32_t* ids, float* weights, const float* logits, int64_t 
   free(used);
   return 0;
 }
+
+/* ---- SwiGLU (reference/reference.cpp:55-63) -----------------------------
+ * out[t, i] = (g / (1 + expf(-g))) * u with g = gate_up[t, i], u = gate_up[t, d + i], every
+ * operation in fp32. */
+int orc_silu_and_mul(float* out, const float* gate_up, int64_t tokens, int64_t d) {
+  if (tokens < 0 || d <= 0) return -1;
+  for (int64_t t = 0; t < tokens; ++t) {
+    const float* row = gate_up + t * 2 * d;
+    for (int64_t i = 0; i < d; ++i) {
+      volatile float den = 1.0f + expf(-row[i]);
+      volatile float s = row[i] / den;
+      out[t * d + i] = s * row[d + i];
+    }
+  }
+  return 0;
+}
+

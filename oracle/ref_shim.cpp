@@ -47,6 +47,10 @@ void ref_topk_softmax(int32_t* ids, float* w, const float* logits, int64_t token
   r::topk_softmax(ids, w, logits, tokens, experts, topk, renorm != 0);
 }
 
+void ref_silu_and_mul(float* out, const float* gate_up, int64_t tokens, int64_t d) {
+  r::silu_and_mul(out, gate_up, tokens, d);
+}
+
 // Row-sliced multi-thread drivers.  Rows of A (and of x for quant) are
 // independent in both operators, so slice t handles rows [t*m/T, (t+1)*m/T).
 int ref_w8a8_block_fp8_gemm_mt(float* c, const uint8_t* aq, const float* as, const uint8_t* bq,

@@ -113,7 +113,29 @@ def config1():
         json.dump(rec, f, indent=1)
 
 
+def moe():
+    """Routing and SwiGLU vectors from the reference's CPU functions (reference.cpp:152-181,
+    :55-63): the reference test's shapes (257 x 256 top-8, 3 x 8 top-2, 17 x 1024 top-16) with
+    N(0, 2) logits, one set with repeated logits (tie-breaking), and a SwiGLU block."""
+    rng = np.random.default_rng(21)
+    out = {}
+    for name, (t, e, k) in {"a": (257, 256, 8), "b": (3, 8, 2), "c": (17, 1024, 16)}.items():
+        lg = (2.0 * rng.standard_normal((t, e))).astype(np.float32)
+        for renorm in (0, 1):
+            ids, w = R.topk_softmax(lg, k, bool(renorm))
+            out[f"ids_{name}{renorm}"], out[f"w_{name}{renorm}"] = ids, w
+        out[f"logits_{name}"] = lg
+    ties = np.round(rng.standard_normal((40, 64)) * 2).astype(np.float32)   # many equal logits
+    out["logits_ties"] = ties
+    out["ids_ties"], out["w_ties"] = R.topk_softmax(ties, 6, True)
+    gu = (3.0 * rng.standard_normal((48, 512))).astype(np.float32)
+    out["gate_up"] = gu
+    out["silu"] = R.silu_and_mul(gu)
+    np.savez_compressed(os.path.join(HERE, "moe_golden.npz"), **out)
+
+
 if __name__ == "__main__":
+    moe()
     codec()
     quant()
     gemm_small()

@@ -27,7 +27,7 @@ def _build(name, tmp_path):
     return exe
 
 
-@pytest.mark.parametrize("name", ["test_fp8", "test_quant", "test_gemm"])
+@pytest.mark.parametrize("name", ["test_fp8", "test_quant", "test_gemm", "test_topk", "test_silu_mul"])
 def test_reference_test_program_builds_and_its_cpu_half_passes(name, tmp_path):
     import torch
     exe = _build(name, tmp_path)

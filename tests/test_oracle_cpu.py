@@ -167,6 +167,36 @@ def test_topk_softmax_properties():
     assert all(len(set(r)) == 8 for r in ids)
 
 
+def test_moe_golden_routing_and_swiglu():
+    g = np.load(os.path.join(GOLDEN, "moe_golden.npz"))
+    for name, k in (("a", 8), ("b", 2), ("c", 16)):
+        for renorm in (0, 1):
+            ids, w = oracle.topk_softmax(g[f"logits_{name}"], k, bool(renorm))
+            assert np.array_equal(ids, g[f"ids_{name}{renorm}"])
+            assert np.array_equal(w.view(np.uint32), g[f"w_{name}{renorm}"].view(np.uint32))
+    ids, w = oracle.topk_softmax(g["logits_ties"], 6, True)
+    assert np.array_equal(ids, g["ids_ties"]) and np.array_equal(w.view(np.uint32), g["w_ties"].view(np.uint32))
+    assert np.array_equal(oracle.silu_and_mul(g["gate_up"]).view(np.uint32), g["silu"].view(np.uint32))
+
+
+def test_moe_align_and_combine_restatements():
+    rng = np.random.default_rng(3)
+    ids, w = oracle.topk_softmax(rng.standard_normal((300, 16)).astype(np.float32), 4)
+    counts, offsets, pos, src, row0, meta = oracle.moe_align(ids, 16)
+    assert counts.sum() == 1200 and offsets[-1] == 1200 and sorted(pos.tolist()) == list(range(1200))
+    flat = ids.reshape(-1)
+    for e in range(16):          # every expert's rows: its pairs, in pair order
+        rows = pos[flat == e]
+        assert np.array_equal(rows, np.arange(offsets[e], offsets[e + 1]))
+    assert np.array_equal(src[pos], np.arange(1200) // 4)
+    assert sum((m & 0xFF) + 1 for m in meta) == 1200 and all((m >> 8) == flat[np.nonzero(pos == r)[0][0]]
+                                                             for r, m in zip(row0, meta))
+    y = rng.standard_normal((1200, 8)).astype(np.float32)
+    out = oracle.moe_combine(y, w, pos)
+    ref = np.einsum("tk,tkh->th", w.astype(np.float64), y[pos.reshape(300, 4)].astype(np.float64))
+    assert np.allclose(out, ref, rtol=1e-5, atol=1e-6)
+
+
 # ------------------------------------------------------------------ against the reference itself
 @needs_ref
 def test_encoder_identical_to_reference_on_all_2_32_inputs():
@@ -194,3 +224,5 @@ def test_operators_identical_to_reference():
     i1, w1 = R.topk_softmax(lg, 8)
     assert np.array_equal(i0, i1) and np.array_equal(w0.view(np.uint32), w1.view(np.uint32))
     assert np.array_equal(oracle.bf16_narrow(x[:4, :64] * 1.001), R.bf16_narrow(x[:4, :64] * 1.001))
+    gu = (3 * rng.standard_normal((40, 256))).astype(np.float32)
+    assert np.array_equal(oracle.silu_and_mul(gu).view(np.uint32), R.silu_and_mul(gu).view(np.uint32))
