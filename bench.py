@@ -49,6 +49,10 @@ def parse_args():
     ap.add_argument("--no-sweep", action="store_true", help="skip the decode / prefill shape sweep (N=1 only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU-baseline sample budget")
+    ap.add_argument("--moe-only", action="store_true",
+                    help="run only the MoE section (grouped GEMMs and the expert layer) and print it")
+    ap.add_argument("--moe-experts", type=int, default=256)
+    ap.add_argument("--moe-tokens", type=int, default=4096)
     return ap.parse_args()
 
 
@@ -319,7 +323,80 @@ def moe_config(peaks, experts=256, hidden=7168, inter=2048, tokens=4096, topk=8)
         out[name] = res
         del bq, bs, c, aq, a_s
         torch.cuda.empty_cache()
+    out["layer"] = moe_layer(peaks, experts, hidden, inter, tokens, topk, logits.cuda(), x)
     return out
+
+
+def moe_layer(peaks, experts, hidden, inter, tokens, topk, logits, x):
+    """The whole expert layer as seven launches with no host step (routing -> layout ->
+    scatter-quantise -> gate_up -> SwiGLU + quantise -> down -> combine): per-kernel device times
+    and, for the HBM-bound ones, achieved bandwidth against the measured copy rate."""
+    import torch
+    from inference_b200 import ops, synth
+    from inference_b200.moe import MoEFP8Layer
+
+    def weights(n, k, seed):
+        bq = torch.empty((experts, n, k), dtype=torch.uint8, device="cuda")
+        bs = torch.empty((experts, n // 128, k // 128), dtype=torch.float32, device="cuda")
+        for e0 in range(0, experts, 32):
+            q, s_ = synth.quantised_weights(32 * n, k, seed=seed + e0)
+            bq[e0:e0 + 32] = q.view(32, n, k)
+            bs[e0:e0 + 32] = s_.view(32, n // 128, k // 128)
+        return bq, bs
+
+    wgu, sgu = weights(2 * inter, hidden, 300)
+    wd, sd = weights(hidden, inter, 700)
+    layer = MoEFP8Layer(wgu, sgu, wd, sd, topk, tokens)
+    out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device="cuda")
+    pairs = tokens * topk
+    lay = layer.layout
+    steps = [
+        ("topk_softmax", lambda: ops.topk_softmax(logits, topk, True, layer.ids, layer.weights),
+         4 * tokens * experts + 8 * pairs),
+        ("moe_align", lambda: ops.moe_align(layer.ids, experts, lay), None),
+        ("moe_scatter_quant", lambda: ops.moe_scatter_quant(x, lay, layer.xq, layer.xs),
+         2 * tokens * hidden + pairs * hidden * (1 + 4 / 128)),
+        ("gate_up_gemm", lambda: ops.w8a8_block_fp8_gemm_grouped_tiles(layer.xq, layer.xs, wgu, sgu, lay,
+                                                                        out=layer.gate_up),
+         experts * 2 * inter * hidden + pairs * hidden + 2 * pairs * 2 * inter),
+        ("silu_and_mul_quant", lambda: ops.silu_and_mul_quant(layer.gate_up, layer.hq, layer.hs),
+         2 * pairs * 2 * inter + pairs * inter * (1 + 4 / 128)),
+        ("down_gemm", lambda: ops.w8a8_block_fp8_gemm_grouped_tiles(layer.hq, layer.hs, wd, sd, lay, out=layer.y),
+         experts * hidden * inter + pairs * inter + 2 * pairs * hidden),
+        ("moe_combine", lambda: ops.moe_combine(layer.y, layer.weights, lay, out),
+         2 * pairs * hidden + 2 * tokens * hidden),
+    ]
+    for _ in range(2):
+        layer.forward(x, logits, out)
+    torch.cuda.synchronize()
+    iters = 5
+    res = {"kernels": {}}
+    for name, fn, byt in steps:
+        fn()
+        e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0_.record()
+        for _ in range(iters):
+            fn()
+        e1_.record()
+        torch.cuda.synchronize()
+        us = e0_.elapsed_time(e1_) / iters * 1e3
+        rec = {"us": round(us, 1)}
+        if byt:
+            rec["gbs"] = round(byt / us / 1e3, 1)
+            rec["frac_of_measured_hbm"] = round(byt / us / 1e3 / peaks["hbm_gbs"], 3)
+        res["kernels"][name] = rec
+    e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0_.record()
+    for _ in range(iters):
+        layer.forward(x, logits, out)
+    e1_.record()
+    torch.cuda.synchronize()
+    ms = e0_.elapsed_time(e1_) / iters
+    flops = 2.0 * pairs * hidden * (2 * inter) + 2.0 * pairs * inter * hidden
+    res.update({"layer_ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1), "launches": len(steps),
+                "host_synchronisations": 0})
+    assert ops.device_status()[0] == 0
+    return res
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -528,7 +605,7 @@ def run_ours(args):
         line["sweep"] = {"what": "quant + GEMM per shape, device-timed (CUDA graph replay), bf16 out",
                          "shapes": shape_sweep(peaks)}
         torch.cuda.empty_cache()
-        line["moe"] = moe_config(peaks)
+        line["moe"] = moe_config(peaks, experts=args.moe_experts, tokens=args.moe_tokens)
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         smp = sized_cpu_sample(k, threads, args.cpu_seconds)
@@ -555,6 +632,9 @@ def main():
     try:
         if args.impl == "reference":
             run_reference(args)
+        elif args.moe_only:
+            res = moe_config(measured_peaks(), experts=args.moe_experts, tokens=args.moe_tokens)
+            print_result(json.dumps({"moe": res}))
         else:
             run_ours(args)
     finally:

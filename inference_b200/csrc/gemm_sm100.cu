@@ -365,6 +365,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       const int gm = ti.a_row + row;
       const int nbi = ti.sb_row + half;
       const bool have = gm < ti.row_end && nbi < ti.sb_rows;
+      // a warp whose 32 rows all lie beyond the tile's last row (ragged last M-tile, small expert
+      // group) keeps the barrier protocol going but neither loads nor promotes anything
+      const bool warp_has_rows = ti.a_row + quarter * 32 < ti.row_end;
       // a TMA store writes whole 128-row boxes (clipped only at the end of C): a grouped tile
       // with fewer rows must not spill into the next group's rows
       const bool tma_store = p.tma_store && (!kGrouped || ti.row_end - ti.a_row == BM);
@@ -393,6 +396,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
         }
         __syncwarp();
         tc_fence_after_sync();
+        if (!warp_has_rows) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          continue;
+        }
         const uint32_t taddr = lane_base + buf * BN;
         uint32_t v0[32], v1[32];
         tmem_ld_32x32(taddr, v0);

@@ -112,6 +112,17 @@ topk_softmax_kernel(int32_t* __restrict__ ids, float* __restrict__ weights,
 __device__ __forceinline__ float silu_mul(float g, float u) {
   return (g / (1.0f + expf(-g))) * u;
 }
+// For 16-bit outputs: exponential and division from the special-function unit (about 2 units in
+// the last place of fp32 each, a thousandth of the 16-bit rounding step), a third of the
+// instructions.  The kernel is otherwise instruction-bound.  Below g = -87 the quotient
+// underflows to zero (exact value: under 1e-36 times the up-projection).
+__device__ __forceinline__ float silu_mul_fast(float g, float u) {
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+template <typename T>
+__device__ __forceinline__ float silu_mul_as(float g, float u) {
+  return sizeof(T) == 2 ? silu_mul_fast(g, u) : silu_mul(g, u);
+}
 
 template <typename T>
 __device__ __forceinline__ float ld_f32(const T* p);
@@ -172,10 +183,10 @@ __device__ __forceinline__ uint4 silu_mul8(const uint4& g_raw, const uint4& u_ra
   unpack8<T>(g_raw, g);
   unpack8<T>(u_raw, u);
   uint4 o;
-  o.x = pack2_rn<T>(silu_mul(g[0], u[0]), silu_mul(g[1], u[1]));
-  o.y = pack2_rn<T>(silu_mul(g[2], u[2]), silu_mul(g[3], u[3]));
-  o.z = pack2_rn<T>(silu_mul(g[4], u[4]), silu_mul(g[5], u[5]));
-  o.w = pack2_rn<T>(silu_mul(g[6], u[6]), silu_mul(g[7], u[7]));
+  o.x = pack2_rn<T>(silu_mul_fast(g[0], u[0]), silu_mul_fast(g[1], u[1]));
+  o.y = pack2_rn<T>(silu_mul_fast(g[2], u[2]), silu_mul_fast(g[3], u[3]));
+  o.z = pack2_rn<T>(silu_mul_fast(g[4], u[4]), silu_mul_fast(g[5], u[5]));
+  o.w = pack2_rn<T>(silu_mul_fast(g[6], u[6]), silu_mul_fast(g[7], u[7]));
   return o;
 }
 
@@ -202,7 +213,7 @@ silu_mul_any_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int64_t 
        i += static_cast<int64_t>(gridDim.x) * kThreads) {
     const int64_t r = i / d, c = i - r * d;
     const T* row = gate_up + r * 2 * d;
-    out[i] = st_from_f32<T>(silu_mul(ld_f32(row + c), ld_f32(row + d + c)));
+    out[i] = st_from_f32<T>(silu_mul_as<T>(ld_f32(row + c), ld_f32(row + d + c)));
   }
 }
 
@@ -220,26 +231,38 @@ silu_mul_quant_kernel(uint8_t* __restrict__ q, float* __restrict__ scales,
   const int64_t hw = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 4;
   const int64_t hw_total = (static_cast<int64_t>(gridDim.x) * kThreads) >> 4;
   const int64_t warp_first = hw & ~int64_t(1);
-  for (int64_t base = 0; warp_first + base < groups; base += hw_total) {
-    const int64_t g = hw + base;
-    const bool live = g < groups;
-    uint4 h = make_uint4(0u, 0u, 0u, 0u);
-    if (live) {
-      const int64_t r = g / gpr, c = g - r * gpr;
-      const T* row = gate_up + r * 2 * d + c * 128 + sub * 8;
-      h = silu_mul8<T>(__ldg(reinterpret_cast<const uint4*>(row)), __ldg(reinterpret_cast<const uint4*>(row + d)));
-    }
-    float f[8];
-    unpack8<T>(h, f);
-    float amax = absmax8_packed<T2>(h);
+  constexpr int kUnroll = 2;
+  for (int64_t base = 0; warp_first + base < groups; base += hw_total * kUnroll) {
+    uint4 graw[kUnroll], uraw[kUnroll];
+    bool live[kUnroll];
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    const float scale = group_scale(amax);
-    if (live) {
-      const uint2 bytes = fast_div_ok(amax) ? quantise8_fast16(h, f, scale, __frcp_rn(scale))
-                                            : quantise8<false>(f, scale, 0.0f);
-      *reinterpret_cast<uint2*>(q + g * 128 + sub * 8) = bytes;
-      if (sub == 0) scales[g] = scale;
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t g = hw + base + u * hw_total;
+      live[u] = g < groups;
+      graw[u] = uraw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (live[u]) {
+        const int64_t r = g / gpr, c = g - r * gpr;
+        const T* row = gate_up + r * 2 * d + c * 128 + sub * 8;
+        graw[u] = __ldg(reinterpret_cast<const uint4*>(row));
+        uraw[u] = __ldg(reinterpret_cast<const uint4*>(row + d));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t g = hw + base + u * hw_total;
+      const uint4 h = silu_mul8<T>(graw[u], uraw[u]);   // zeros for a lane without a group
+      float f[8];
+      unpack8<T>(h, f);
+      float amax = absmax8_packed<T2>(h);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      const float scale = group_scale(amax);
+      if (live[u]) {
+        const uint2 bytes = fast_div_ok(amax) ? quantise8_fast16(h, f, scale, __frcp_rn(scale))
+                                              : quantise8<false>(f, scale, 0.0f);
+        *reinterpret_cast<uint2*>(q + g * 128 + sub * 8) = bytes;
+        if (sub == 0) scales[g] = scale;
+      }
     }
   }
 }
@@ -298,7 +321,7 @@ int launch_silu_and_mul(void* out, const void* gate_up, int32_t dt, int64_t rows
 int launch_silu_and_mul_quant(void* q, void* scales, const void* gate_up, int32_t dt, int64_t rows,
                               int64_t d, cudaStream_t stream, int sms) {
   const int64_t groups = rows * (d / 128);
-  const int grid = grid_for((groups + kThreads / 16 - 1) / (kThreads / 16), sms, 8);
+  const int grid = grid_for((groups + (kThreads / 16) * 2 - 1) / ((kThreads / 16) * 2), sms, 8);
   if (dt == 1) {
     silu_mul_quant_kernel<__half><<<grid, kThreads, 0, stream>>>(
         static_cast<uint8_t*>(q), static_cast<float*>(scales), static_cast<const __half*>(gate_up), rows, d);
@@ -344,9 +367,17 @@ moe_align_kernel(const int32_t* __restrict__ ids, int pairs, int topk, int exper
   const int chunk = ((pairs + kAlignWarps - 1) / kAlignWarps + 31) & ~31;
   const int begin = min(pairs, warp * chunk), end = min(pairs, begin + chunk);
   int32_t* my_hist = hist + warp * experts;
-  for (int i = begin + lane; i < end; i += 32) {
-    const int e = __ldg(ids + i);
-    if (e >= 0 && e < experts) atomicAdd(&my_hist[e], 1);
+  for (int i0 = begin; i0 < end; i0 += 256) {   // eight loads in flight per lane
+    int ev[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * 32 + lane;
+      ev[u] = i < end ? __ldg(ids + i) : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (ev[u] >= 0 && ev[u] < experts) atomicAdd(&my_hist[ev[u]], 1);
+    }
   }
   __syncthreads();
 
@@ -388,20 +419,37 @@ moe_align_kernel(const int32_t* __restrict__ ids, int pairs, int topk, int exper
   }
   __syncthreads();
 
-  for (int i0 = begin; i0 < end; i0 += 32) {
-    const int i = i0 + lane;
-    int e = i < end ? __ldg(ids + i) : -1;
-    if (e >= experts) e = -1;
-    // lanes without a valid expert get distinct keys so that they match nobody
-    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e >= 0 ? e : -1 - lane);
-    int row = -1;
-    if (e >= 0) row = my_hist[e] + __popc(peers & ((1u << lane) - 1u));
-    __syncwarp();
-    if (e >= 0 && lane == 31 - __clz(peers)) my_hist[e] = row + 1;   // the last of the equals
-    __syncwarp();
-    if (i < end) {
-      pos[i] = row;
-      if (row >= 0) src_token[row] = i / topk;
+  const int id_bits = 32 - __clz(max(experts - 1, 1));
+  // the ids of four steps are requested together, so their latency is paid once per four steps
+  for (int i0 = begin; i0 < end; i0 += 128) {
+    int ev[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * 32 + lane;
+      ev[u] = i < end ? __ldg(ids + i) : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * 32 + lane;
+      if (i0 + u * 32 >= end) break;                      // warp-uniform
+      int e = ev[u];
+      if (e >= experts) e = -1;
+      // lanes of this step that hold the same expert: one ballot per bit of the expert index
+      // (far cheaper than match.any when most of the 32 values differ)
+      unsigned peers = __ballot_sync(0xFFFFFFFFu, e >= 0);
+      for (int b = 0; b < id_bits; ++b) {
+        const unsigned bal = __ballot_sync(0xFFFFFFFFu, (e >> b) & 1);
+        peers &= ((e >> b) & 1) ? bal : ~bal;
+      }
+      int row = -1;
+      if (e >= 0) row = my_hist[e] + __popc(peers & ((1u << lane) - 1u));
+      __syncwarp();
+      if (e >= 0 && lane == 31 - __clz(peers)) my_hist[e] = row + 1;   // the last of the equals
+      __syncwarp();
+      if (i < end) {
+        pos[i] = row;
+        if (row >= 0) src_token[row] = i / topk;
+      }
     }
   }
 }
