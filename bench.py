@@ -44,7 +44,9 @@ def parse_args():
     ap.add_argument("--m", type=int, default=M_FULL)
     ap.add_argument("--n", type=int, default=N_FULL)
     ap.add_argument("--k", type=int, default=K_FULL)
-    ap.add_argument("--gather", action="store_true", help="also time an NCCL all-gather of C")
+    ap.add_argument("--gather", action="store_true",
+                    help="(default for N > 1) also time the all-gather of C: NCCL, and the GEMM's own epilogue")
+    ap.add_argument("--no-gather", action="store_true", help="skip the all-gather measurements")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the decode / prefill shape sweep (N=1 only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -475,7 +477,7 @@ def run_ours(args):
 
     # ---- optional all-gather of C (reported separately)
     gather = None
-    if args.gather and world > 1:
+    if world > 1 and not args.no_gather:
         c_all = torch.empty((world * m, n_loc), dtype=torch.bfloat16, device=dev)  # [G][M][N/G] rank-blocked
         for _ in range(2):
             dist.all_gather_into_tensor(c_all, c)
@@ -493,30 +495,39 @@ def run_ours(args):
         # the same step with the gather done by the GEMM's own epilogue (peer stores into every
         # rank's row-major [M, N] buffer), then a stream-ordered meeting of the ranks
         from inference_b200 import shard
-        po = shard.PeerOutput(m, n, torch.bfloat16, dev)
+        try:
+            po = shard.PeerOutput(m, n, torch.bfloat16, dev)
+            peer_error = None
+        except Exception as exc:   # no peer mapping on this box: report it, keep the NCCL figures
+            po, peer_error = None, f"{type(exc).__name__}: {exc}"
+        # every rank must take the same branch
+        flag = torch.tensor([0 if po is None else 1], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 1:
+            def fused_step():
+                ops.quant_fp8_per_token_group(x, 128, aq, a_s)
+                ops.w8a8_block_fp8_gemm_allgather(po.ptrs, rank, aq, a_s, bq, bs)
+                po.barrier()
 
-        def fused_step():
-            ops.quant_fp8_per_token_group(x, 128, aq, a_s)
-            ops.w8a8_block_fp8_gemm_allgather(po.ptrs, rank, aq, a_s, bq, bs)
-            po.barrier()
-
-        for _ in range(2):
-            fused_step()
-        sync_all()
-        g0.record(stream)
-        for _ in range(args.steps):
-            fused_step()
-        g1.record(stream)
-        torch.cuda.synchronize()
-        tf = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
-        blocked = c_all.view(world, m, n_loc)
-        same = all(torch.equal(po.local[:, r * n_loc:(r + 1) * n_loc], blocked[r]) for r in range(world))
-        gather["fused"] = {"ms_per_step": tf * 1e3, "value": flops_total / tf / 1e12,
-                           "layout": "[M][N] row-major on every rank",
-                           "equals_nccl_gather": bool(same),
-                           "link_gbs_out_per_rank": 2 * m * n_loc * (world - 1) / tf / 1e9}
-        status = ops.device_status()
-        assert status[0] == 0, f"device-side wait ran out: {status}"
+            for _ in range(2):
+                fused_step()
+            sync_all()
+            g0.record(stream)
+            for _ in range(args.steps):
+                fused_step()
+            g1.record(stream)
+            torch.cuda.synchronize()
+            tf = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
+            blocked = c_all.view(world, m, n_loc)
+            same = all(torch.equal(po.local[:, r * n_loc:(r + 1) * n_loc], blocked[r]) for r in range(world))
+            gather["fused"] = {"ms_per_step": tf * 1e3, "value": flops_total / tf / 1e12,
+                               "layout": "[M][N] row-major on every rank",
+                               "equals_nccl_gather": bool(same),
+                               "link_gbs_out_per_rank": 2 * m * n_loc * (world - 1) / tf / 1e9}
+            status = ops.device_status()
+            assert status[0] == 0, f"device-side wait ran out: {status}"
+        else:
+            gather["fused"] = {"unavailable": peer_error or "peer mapping failed on another rank"}
         del c_all, po
 
     # ---- end-to-end through the public API with host buffers

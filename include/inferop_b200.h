@@ -121,7 +121,9 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm_grouped(void* c, const void* a_q, co
  * c_peers is a HOST array of n_peers device addresses, entry d = the base of rank d's buffer as
  * mapped into this process (CUDA IPC, virtual-memory export or symmetric memory; entry `rank` is
  * the local buffer), each 16-byte aligned; it is read before the call returns.  n % 128 == 0,
- * n_peers <= 8, out_dt 1 (fp16) or 2 (bf16).  The call does not synchronise the ranks: a rank's
+ * n_peers <= 8, out_dt 1 (fp16) or 2 (bf16).  M <= 96 runs the weight-streaming kernel of the
+ * plain GEMM (plain stores to the peers, same per-stream scratch), larger M the large-tile kernel
+ * (one TMA store per destination).  The call does not synchronise the ranks: a rank's
  * buffer is complete when every rank's call has finished, so the ranks must meet (a barrier, a
  * collective, or stream-ordered signals) after the call before any of them reads its buffer, and
  * before the call overwrites a buffer that a peer may still be reading. */

@@ -315,8 +315,23 @@ int inferop_w8a8_block_fp8_gemm_allgather(void* const* c_peers, int32_t n_peers,
   int err;
   DeviceCtx* ctx = current_ctx(&err);
   if (!ctx) return err;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // a few tokens: the weight-streaming kernel, storing straight into every rank's buffer
+  if (m <= 96 && (n + 127) / 128 <= kDecodeMaxTiles && options().gemm_path != 1) {
+    float* ws;
+    int* counters;
+    if (decode_scratch(ctx, s, &ws, &counters)) {
+      void* dst[8];
+      for (int i = 0; i < n_peers; ++i) dst[i] = c_peers[(rank + 1 + i) % n_peers];   // own buffer last
+      for (int i = 0; i < n_peers; ++i) {
+        if (!dst[i] || (reinterpret_cast<uintptr_t>(dst[i]) & 15u)) return INFEROP_ERR_POINTER;
+      }
+      return launch_gemm_decode_to(ctx, ws, counters, dst, n_peers, n * n_peers, rank * n, a_q, a_scales,
+                                   b_q, b_scales, m, n, k, out_dt, s);
+    }
+  }
   return launch_gemm_allgather(ctx, c_peers, n_peers, rank, a_q, a_scales, b_q, b_scales, m, n, k,
-                               out_dt, static_cast<cudaStream_t>(stream));
+                               out_dt, s);
 }
 
 int inferop_topk_softmax(int32_t* topk_ids, void* topk_weights, const void* logits, int32_t tokens,

@@ -64,7 +64,11 @@ struct DecodeParams {
   const float* a_scales;   // [M, KB]
   const void* a_src;       // fused prologue only: unquantised activations [M, K] (bf16 / fp16)
   const float* b_scales;   // [ceil(N/128), KB]
-  void* c;                 // [M, N]
+  // Output: the [M, N] result goes to columns [col0, col0 + N) of n_dst row-major buffers with
+  // row pitch ldc elements.  A plain call has one destination (c, ldc = N, col0 = 0); the
+  // all-gather form lists every rank's buffer (peer-mapped addresses, plain stores).
+  void* dst[8];
+  int n_dst, ldc, col0;
   float* workspace;        // [gridDim.x][MP][128] fp32 partials
   int splits;              // K parts per tile (1 = whole tiles, CTAs take runs of tiles)
   int* counters;           // [n_tiles], zero between launches
@@ -86,12 +90,20 @@ enum : uint32_t {
 
 template <typename OutT>
 __device__ __forceinline__ OutT cvt_out(float v);
+
 template <>
 __device__ __forceinline__ float cvt_out<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __half cvt_out<__half>(float v) { return __float2half_rn(v); }
 template <>
 __device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename OutT>
+__device__ __forceinline__ void store_out(const DecodeParams& p, int m, int gn, float v) {
+  const OutT o = cvt_out<OutT>(v);
+  const int64_t at = static_cast<int64_t>(m) * p.ldc + p.col0 + gn;
+  for (int d = 0; d < p.n_dst; ++d) static_cast<OutT*>(p.dst[d])[at] = o;
+}
 
 template <int N>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]);
@@ -457,7 +469,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           if (gn < p.n) {
 #pragma unroll
             for (int m = 0; m < MP; ++m)
-              if (m < p.m) static_cast<OutT*>(p.c)[static_cast<int64_t>(m) * p.n + gn] = cvt_out<OutT>(acc[m]);
+              if (m < p.m) store_out<OutT>(p, m, gn, acc[m]);
           }
         } else {
           // one K part of a split tile: this CTA's slot of the workspace
@@ -484,7 +496,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (gn < p.n) {
 #pragma unroll
               for (int m = 0; m < MP; ++m)
-                if (m < p.m) static_cast<OutT*>(p.c)[static_cast<int64_t>(m) * p.n + gn] = cvt_out<OutT>(sum[m]);
+                if (m < p.m) store_out<OutT>(p, m, gn, sum[m]);
             }
             if (ct == 0) p.counters[t] = 0;   // ready for the next launch
           }
@@ -577,7 +589,10 @@ int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, vo
   p.a_scales = nullptr;
   p.a_src = a;
   p.b_scales = static_cast<const float*>(b_scales);
-  p.c = c;
+  p.dst[0] = c;
+  p.n_dst = 1;
+  p.ldc = static_cast<int>(n);
+  p.col0 = 0;
   p.workspace = workspace;
   p.counters = counters;
   p.m = static_cast<int>(m);
@@ -610,12 +625,25 @@ int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, vo
 int launch_gemm_decode(DeviceCtx* ctx, float* workspace, int* counters, void* c, const void* a_q,
                        const void* a_scales, const void* b_q, const void* b_scales, int64_t m,
                        int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream) {
+  void* const dst[1] = {c};
+  return launch_gemm_decode_to(ctx, workspace, counters, dst, 1, n, 0, a_q, a_scales, b_q, b_scales, m, n,
+                               k, out_dt, stream);
+}
+
+int launch_gemm_decode_to(DeviceCtx* ctx, float* workspace, int* counters, void* const* dst, int n_dst,
+                          int64_t ldc, int64_t col0, const void* a_q, const void* a_scales,
+                          const void* b_q, const void* b_scales, int64_t m, int64_t n, int64_t k,
+                          int32_t out_dt, cudaStream_t stream) {
   const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
   DecodeParams p;
   p.a_src = nullptr;
   p.a_scales = static_cast<const float*>(a_scales);
   p.b_scales = static_cast<const float*>(b_scales);
-  p.c = c;
+  if (n_dst < 1 || n_dst > 8) return INFEROP_ERR_SHAPE;
+  for (int d = 0; d < 8; ++d) p.dst[d] = dst[d < n_dst ? d : 0];
+  p.n_dst = n_dst;
+  p.ldc = static_cast<int>(ldc);
+  p.col0 = static_cast<int>(col0);
   p.workspace = workspace;
   p.counters = counters;
   p.m = static_cast<int>(m);

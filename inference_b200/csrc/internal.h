@@ -106,6 +106,13 @@ int launch_gemm_decode(DeviceCtx* ctx, float* workspace, int* counters, void* c,
                        const void* a_scales, const void* b_q, const void* b_scales, int64_t m,
                        int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream);
 
+// The same with the [m, n] result written to columns [col0, col0 + n) of n_dst (<= 8) row-major
+// buffers of row pitch ldc elements (host array `dst`; peer-mapped addresses allowed).
+int launch_gemm_decode_to(DeviceCtx* ctx, float* workspace, int* counters, void* const* dst, int n_dst,
+                          int64_t ldc, int64_t col0, const void* a_q, const void* a_scales,
+                          const void* b_q, const void* b_scales, int64_t m, int64_t n, int64_t k,
+                          int32_t out_dt, cudaStream_t stream);
+
 // Fused prologue: `a` holds unquantised activations (a_dt 1 = fp16, 2 = bf16), M <= kFusedMaxM.
 constexpr int kFusedMaxM = 32;
 int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, void* c, const void* a,

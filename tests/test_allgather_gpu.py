@@ -65,6 +65,32 @@ def test_emulated_ranks_fill_every_buffer_with_the_full_result(ops, world, m, n_
     assert row <= GEMM_ROW_TOL and fro <= GEMM_FRO_TOL_BF16 * (4 if dt == torch.float16 else 1)
 
 
+@pytest.mark.parametrize("m", [1, 16, 50, 96])
+def test_few_tokens_take_the_weight_streaming_kernel_and_fill_every_buffer(ops, m):
+    from inference_b200 import shard
+    world, n_shard, k = 4, 384, 1024
+    aq, a_s, bq, bs = case(m, n_shard * world, k, seed=40 + m)
+    d_aq, d_as, d_bq, d_bs = cuda(aq), cuda(a_s), cuda(bq), cuda(bs)
+    ops.set_option("gemm_path", 0)
+    try:
+        want = ops.w8a8_block_fp8_gemm(d_aq, d_as, d_bq, d_bs)        # same kernel, unsharded
+        bufs = [torch.full((m + 2, n_shard * world), -7.0, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+        for rank in range(world):
+            wq, ws = shard.shard_weights(d_bq, d_bs, world, rank)
+            ops.w8a8_block_fp8_gemm_allgather([b[1:].data_ptr() for b in bufs], rank, d_aq, d_as, wq, ws)
+        assert ops.device_status()[0] == 0
+    finally:
+        ops.set_option("gemm_path", 1)
+    golden = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs)
+    for b in bufs:
+        assert bool((b[0] == -7.0).all()) and bool((b[m + 1] == -7.0).all())
+        row, fro = gemm_errors(b[1:m + 1].float().cpu().numpy(), golden)
+        assert row <= GEMM_ROW_TOL and fro <= GEMM_FRO_TOL_BF16
+        # split tiles add their K parts in a fixed order, but the parts depend on the shard's tile
+        # count: equal to the unsharded call up to the rounding of the output type
+        assert torch.allclose(b[1:m + 1].float(), want.float(), rtol=2e-2, atol=1e-3)
+
+
 def test_only_the_ranks_own_columns_are_written(ops):
     from inference_b200 import shard
     world, m, n_shard, k = 4, 130, 128, 256

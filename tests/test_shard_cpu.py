@@ -46,10 +46,19 @@ def _worker(rank, world, port, m, n, k, out_dir):
     c_l = torch.from_numpy(oracle.w8a8_block_fp8_gemm(aq, a_s, bq_l.numpy(), bs_l.numpy()))
     blocked = shard.gather_outputs(c_l)
     full = shard.blocked_to_row_major(blocked)
+    # the layout contract of the all-gather GEMM: rank r's result occupies columns
+    # peer_columns(N/G, r) of every rank's row-major [M, N] buffer (gloo moves the data here)
+    parts = [torch.empty_like(c_l) for _ in range(world)]
+    dist.all_gather(parts, c_l)
+    peer_full = torch.full((m, n), float("nan"))
+    for r in range(world):
+        lo, hi = shard.peer_columns(n // world, r)
+        peer_full[:, lo:hi] = parts[r]
     if rank == 0:
         want = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs)
         np.save(os.path.join(out_dir, "ok.npy"),
-                np.array([np.array_equal(full.numpy(), want), blocked.shape == (world, m, n // world)]))
+                np.array([np.array_equal(full.numpy(), want), blocked.shape == (world, m, n // world),
+                          np.array_equal(peer_full.numpy(), want)]))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -59,3 +68,11 @@ def test_two_rank_sharded_gemm_and_gather_equals_unsharded(tmp_path):
     mp.spawn(_worker, args=(world, _free_port(), m, n, k, str(tmp_path)), nprocs=world, join=True)
     ok = np.load(tmp_path / "ok.npy")
     assert ok.all()
+
+
+def test_peer_output_without_a_process_group_is_one_local_buffer():
+    out = shard.PeerOutput(4, 256, torch.float16, device="cpu")
+    assert out.world == 1 and out.rank == 0 and out.ptrs == [out.local.data_ptr()]
+    assert out.local.shape == (4, 256)
+    out.barrier()   # nothing to meet
+    assert shard.peer_columns(128, 3) == (384, 512)
