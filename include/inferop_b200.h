@@ -133,6 +133,27 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm_allgather(void* const* c_peers, int3
                                           int32_t group_size, int32_t block_n, int32_t out_dt,
                                           void* stream);
 
+/* ---- blockwise-FP8 GEMM of one K shard, reduce-scattered (row-parallel sharding)
+ * The partner of the column-parallel form (reference include/inferop/ops.h:81-84 on a K shard of
+ * both operands; the reference is single-GPU and has no collective): rank `rank` of `n_peers`
+ * holds columns of the activations a_q [M, k] / a_scales [M, k/128] and of the weights
+ * b_q [N, k] / b_scales [ceil(N/128), k/128] for its K range, so its product is a partial sum of
+ * the whole [M, N] result.  Rank d owns rows [d * M/n_peers, (d + 1) * M/n_peers) of the final
+ * result and keeps, for them, one fp32 slot per source rank: slots [n_peers][M/n_peers][N].
+ * inferop_w8a8_block_fp8_gemm_scatter stores this rank's partial tiles straight from the GEMM's
+ * epilogue into slot `rank` of each owner (TMA stores over NVLink; slot_peers is a HOST array,
+ * entry d = base of rank d's slots as mapped in this process, 16-byte aligned).  After the ranks
+ * have met, each owner calls inferop_reduce_slots, which adds its slots in rank order and rounds
+ * once to out_dt: out [M/n_peers, N].  The sum is fp32 over K blocks within a rank (as in the plain
+ * GEMM) and fp32 over the ranks, so it equals the unsharded GEMM up to fp32 reassociation, and it
+ * is reproducible.  M % (128 * n_peers) == 0, N % 4 == 0, n_peers <= 8. */
+INFEROP_API int inferop_w8a8_block_fp8_gemm_scatter(void* const* slot_peers, int32_t n_peers, int32_t rank,
+                                        const void* a_q, const void* a_scales, const void* b_q,
+                                        const void* b_scales, int64_t m, int64_t n, int64_t k,
+                                        int32_t group_size, int32_t block_n, void* stream);
+INFEROP_API int inferop_reduce_slots(void* out, int32_t out_dt, const void* slots, int32_t n_peers, int64_t rows,
+                         int64_t n, void* stream);
+
 /* ---- mixture-of-experts layer around the grouped GEMM
  * Every step stays on the device: the experts' row counts are never copied to the host, the
  * grouped GEMM reads the M-tile list that inferop_moe_align wrote.  The steps of a layer:

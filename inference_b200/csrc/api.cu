@@ -334,6 +334,39 @@ int inferop_w8a8_block_fp8_gemm_allgather(void* const* c_peers, int32_t n_peers,
                                out_dt, s);
 }
 
+int inferop_w8a8_block_fp8_gemm_scatter(void* const* slot_peers, int32_t n_peers, int32_t rank,
+                                        const void* a_q, const void* a_scales, const void* b_q,
+                                        const void* b_scales, int64_t m, int64_t n, int64_t k,
+                                        int32_t group_size, int32_t block_n, void* stream) {
+  if (group_size != 128 || block_n != 128 || k <= 0 || k % 128 != 0 || m <= 0 || n <= 0 || n % 4 != 0 ||
+      n_peers < 1 || n_peers > 8 || rank < 0 || rank >= n_peers || m % (128 * n_peers) != 0) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (m > 0x7FFFFF00LL || n > 0x7FFFFF00LL || k > 0x7FFFFF00LL) return INFEROP_ERR_LIMIT;
+  if (!slot_peers || !a_q || !a_scales || !b_q || !b_scales) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(a_q) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_gemm_scatter(ctx, slot_peers, n_peers, rank, a_q, a_scales, b_q, b_scales, m, n, k,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int inferop_reduce_slots(void* out, int32_t out_dt, const void* slots, int32_t n_peers, int64_t rows,
+                         int64_t n, void* stream) {
+  if (n_peers < 1 || n_peers > 8 || rows <= 0 || n <= 0 || n % 4 != 0) return INFEROP_ERR_SHAPE;
+  if (out_dt < 0 || out_dt > 2) return INFEROP_ERR_DTYPE;
+  if (!out || !slots) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(slots) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) return INFEROP_ERR_POINTER;
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_reduce_slots(out, out_dt, slots, n_peers, rows * n, static_cast<cudaStream_t>(stream),
+                             ctx->sm_count);
+}
+
 int inferop_topk_softmax(int32_t* topk_ids, void* topk_weights, const void* logits, int32_t tokens,
                          int32_t num_experts, int32_t topk, int32_t renormalize, void* stream) {
   if (tokens <= 0 || num_experts <= 0 || num_experts > 1024 || topk <= 0 || topk > num_experts) {

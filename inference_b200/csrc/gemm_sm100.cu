@@ -108,9 +108,19 @@ struct PeerMaps {
   CUtensorMap map[kMaxPeers];  // [M, n * ranks] two-byte row-major, box 128 rows x 64 columns
   int count;
   int col_offset;              // rank * n
+  // scatter launches only (below)
+  int rows_per_owner;
+  int rank;
 };
 
-enum : int { kModePlain = 0, kModeGrouped = 1, kModeGather = 2 };
+// Scatter launches (row-parallel sharding, the first half of a reduce-scatter): this rank holds a
+// K shard of both operands, so its result is a PARTIAL sum over K of the whole [M, N] output.  It
+// stays in fp32 and goes, tile by tile, to the rank that owns those rows of the final result:
+// rows [d * M/G, (d + 1) * M/G) belong to rank d, which keeps one [M/G, N] fp32 slot per source
+// rank; map[d] describes rank d's slots as one [G * M/G, N] fp32 tensor (box 128 rows x 32
+// columns) and this rank writes slot `rank` of it.  The owner adds its slots in rank order
+// afterwards (reduce_slots), so the sum does not depend on arrival order.
+enum : int { kModePlain = 0, kModeGrouped = 1, kModeGather = 2, kModeScatter = 3 };
 
 struct TileInfo {
   int a_row;     // first row of the tile in A / a_scales / C
@@ -220,6 +230,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
                                           const int* num_mtiles_dev) {
   constexpr bool kGrouped = kMode == kModeGrouped;
   constexpr bool kGather = kMode == kModeGather;
+  constexpr bool kScatter = kMode == kModeScatter;
   // a device-built tile list comes with its length in device memory (at most p.tiles_m entries)
   const int num_tiles =
       (kGrouped && num_mtiles_dev != nullptr) ? min(__ldg(num_mtiles_dev), p.tiles_m) * p.tiles_n
@@ -253,7 +264,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
     mbar_init_fence();
     tma_prefetch_desc(map_a);
     tma_prefetch_desc(map_b);
-    if constexpr (kGather) {
+    if constexpr (kGather || kScatter) {
       for (int d = 0; d < peers->count; ++d) tma_prefetch_desc(&peers->map[d]);
     } else {
       if (p.tma_store) tma_prefetch_desc(map_c);
@@ -367,7 +378,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       const bool have = gm < ti.row_end && nbi < ti.sb_rows;
       // a warp whose 32 rows all lie beyond the tile's last row (ragged last M-tile, small expert
       // group) keeps the barrier protocol going but neither loads nor promotes anything
+#ifdef IB200_ABLATE_PROMOTION   // measurement builds only: no tensor-memory reads, no promotion
+      const bool warp_has_rows = false;
+#else
       const bool warp_has_rows = ti.a_row + quarter * 32 < ti.row_end;
+#endif
       // a TMA store writes whole 128-row boxes (clipped only at the end of C): a grouped tile
       // with fewer rows must not spill into the next group's rows
       const bool tma_store = p.tma_store && (!kGrouped || ti.row_end - ti.a_row == BM);
@@ -423,6 +438,31 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       if (!ok) break;
 
       // ---- epilogue: this thread holds C[gm, col .. col + 128) in fp32
+      if constexpr (kScatter) {
+        // fp32 partial sums to slot `rank` of the rows' owner, 32 columns (128 bytes) per store
+        const int owner = ti.a_row / peers->rows_per_owner;
+        const int slot_row = peers->rank * peers->rows_per_owner + (ti.a_row - owner * peers->rows_per_owner);
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const float* accf = reinterpret_cast<const float*>(acc) + ch * 32;
+          const int col0 = ti.col + half * BH + ch * 32;
+          if (issuer) tma_store_wait_read0();
+          named_bar_sync(1 + half, 128);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 w = make_uint4(__float_as_uint(accf[j * 4]), __float_as_uint(accf[j * 4 + 1]),
+                                       __float_as_uint(accf[j * 4 + 2]), __float_as_uint(accf[j * 4 + 3]));
+            *reinterpret_cast<uint4*>(my_buf + row * 128 + ((j ^ (row & 7)) << 4)) = w;
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1 + half, 128);
+          if (issuer && col0 < p.n) {
+            tma_store_2d(&peers->map[owner], my_buf, col0, slot_row);
+            tma_store_commit();
+          }
+        }
+        continue;
+      }
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         const float* accf = reinterpret_cast<const float*>(acc) + ch * 64;
@@ -531,6 +571,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 w8a8_gather_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const GemmParams p, const __grid_constant__ PeerMaps peers) {
   gemm_body<OutT, kModeGather>(&map_a, &map_b, nullptr, p, TileList{nullptr, nullptr}, &peers, nullptr);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_scatter_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmParams p, const __grid_constant__ PeerMaps peers) {
+  gemm_body<float, kModeScatter>(&map_a, &map_b, nullptr, p, TileList{nullptr, nullptr}, &peers, nullptr);
 }
 
 template <typename OutT>
@@ -805,6 +851,64 @@ int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void
     case 2: return launch_grouped_dev_t<__nv_bfloat16>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
     default: return INFEROP_ERR_DTYPE;
   }
+}
+
+int launch_gemm_scatter(DeviceCtx* ctx, void* const* slot_peers, int32_t n_peers, int32_t rank,
+                        const void* a_q, const void* a_scales, const void* b_q, const void* b_scales,
+                        int64_t m, int64_t n, int64_t k, cudaStream_t stream) {
+  const Options& opt = options();
+  if (n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return INFEROP_ERR_SHAPE;
+  // a tile's 128 rows must belong to one owner; a row of fp32 must be a whole number of 16 bytes
+  if (m % (static_cast<int64_t>(BM) * n_peers) != 0 || n % 4 != 0) return INFEROP_ERR_SHAPE;
+  for (int d = 0; d < n_peers; ++d) {
+    if (slot_peers[d] == nullptr || reinterpret_cast<uintptr_t>(slot_peers[d]) % 16 != 0) return INFEROP_ERR_POINTER;
+  }
+  GemmParams p;
+  p.a_scales = static_cast<const float*>(a_scales);
+  p.b_scales = static_cast<const float*>(b_scales);
+  p.c = nullptr;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.kb = static_cast<int>(k / 128);
+  p.nb = static_cast<int>((n + 127) / 128);
+  p.tiles_m = static_cast<int>(m / BM);
+  p.tiles_n = static_cast<int>((n + BN - 1) / BN);
+  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  if (tiles > 0x7FFFFFFF || tiles * p.kb > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
+  p.num_tiles = static_cast<int>(tiles);
+  p.tma_store = 1;
+  p.group_m = opt.gemm_group_m > 0 ? opt.gemm_group_m : 32;
+  p.status = ctx->status;
+
+  CUtensorMap ma, mb;
+  int rc = make_tensor_map_2d(&ma, a_q, 1, m, k, k, BM, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  rc = make_tensor_map_2d(&mb, b_q, 1, n, k, k, BN, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  static thread_local PeerMaps peers;
+  peers.count = n_peers;
+  peers.col_offset = 0;
+  peers.rows_per_owner = static_cast<int>(m / n_peers);
+  peers.rank = rank;
+  for (int d = 0; d < n_peers; ++d) {
+    rc = make_tensor_map_2d(&peers.map[d], slot_peers[d], 4, m, n, n * 4, 128, 32, true);
+    if (rc != INFEROP_OK) return rc;
+  }
+  for (int i = n_peers; i < kMaxPeers; ++i) peers.map[i] = peers.map[0];
+  int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
+  if (ctas > p.num_tiles) ctas = p.num_tiles;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(w8a8_scatter_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_done[dev] = true;
+  }
+  w8a8_scatter_gemm_kernel<<<ctas, kThreads, kSmemBytes, stream>>>(ma, mb, p, peers);
+  return check_launch();
 }
 
 }  // namespace ib200

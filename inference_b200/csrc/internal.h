@@ -79,6 +79,16 @@ int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void
                             int64_t m_total, int64_t groups, int64_t n, int64_t k, int32_t out_dt,
                             cudaStream_t stream);
 
+// Scatter launch (row-parallel sharding): fp32 partial results of this rank's K shard, stored
+// tile by tile into slot `rank` of the rank that owns the rows; slot_peers[d] (host array) is the
+// base of rank d's [n_peers][m / n_peers][n] fp32 slots as mapped in this process.
+int launch_gemm_scatter(DeviceCtx* ctx, void* const* slot_peers, int32_t n_peers, int32_t rank,
+                        const void* a_q, const void* a_scales, const void* b_q, const void* b_scales,
+                        int64_t m, int64_t n, int64_t k, cudaStream_t stream);
+// reduce.cu : out[i] = sum over ranks (in order) of slots[r][i], rounded once
+int launch_reduce_slots(void* out, int32_t out_dt, const void* slots, int32_t ranks, int64_t elems,
+                        cudaStream_t stream, int sms);
+
 // moe.cu
 int launch_topk_softmax(int32_t* ids, float* weights, const float* logits, int32_t tokens,
                         int32_t experts, int32_t topk, int32_t renorm, cudaStream_t stream);

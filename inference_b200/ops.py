@@ -188,6 +188,35 @@ def w8a8_block_fp8_gemm_allgather(peer_ptrs, rank: int, a_q: torch.Tensor, a_sca
               "w8a8_block_fp8_gemm_allgather")
 
 
+def w8a8_block_fp8_gemm_scatter(slot_ptrs, rank: int, a_q: torch.Tensor, a_scales: torch.Tensor,
+                                b_q: torch.Tensor, b_scales: torch.Tensor, stream=None) -> None:
+    """GEMM of this rank's K shard; the fp32 partial result goes, tile by tile, into slot `rank`
+    of the rank that owns the rows (slot_ptrs[d] = base of rank d's [G][M/G][N] fp32 slots)."""
+    for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
+        _dev_tensor(t, name)
+    m, k = a_q.shape
+    n = b_q.shape[0]
+    ptrs = (C.c_void_p * len(slot_ptrs))(*[int(p) for p in slot_ptrs])
+    with torch.cuda.device(a_q.device):
+        check(lib.inferop_w8a8_block_fp8_gemm_scatter(ptrs, len(slot_ptrs), int(rank), a_q.data_ptr(),
+                                                      a_scales.data_ptr(), b_q.data_ptr(), b_scales.data_ptr(),
+                                                      m, n, k, 128, 128, _stream_ptr(stream)),
+              "w8a8_block_fp8_gemm_scatter")
+
+
+def reduce_slots(slots: torch.Tensor, out_dtype=torch.bfloat16, out: torch.Tensor | None = None,
+                 stream=None) -> torch.Tensor:
+    """slots fp32 [G, rows, N] -> out [rows, N]: the sum over G in order, rounded once."""
+    _dev_tensor(slots, "slots")
+    g, rows, n = slots.shape
+    with torch.cuda.device(slots.device):
+        if out is None:
+            out = torch.empty((rows, n), dtype=out_dtype, device=slots.device)
+        check(lib.inferop_reduce_slots(out.data_ptr(), int(_TORCH2CODE[out.dtype]), slots.data_ptr(), g, rows, n,
+                                       _stream_ptr(stream)), "reduce_slots")
+    return out
+
+
 # --------------------------------------------------------------------------- mixture of experts
 def topk_softmax(logits: torch.Tensor, topk: int, renormalize: bool = True, ids: torch.Tensor | None = None,
                  weights: torch.Tensor | None = None, stream=None):

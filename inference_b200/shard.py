@@ -91,3 +91,58 @@ class PeerOutput:
         only when every rank's GEMM (and with it every store into this rank's buffer) has."""
         if self._flag is not None:
             dist.all_reduce(self._flag, group=self.group)
+
+
+# ----------------------------------------------------------------------------- row-parallel (K shards)
+def k_shard_bounds(k: int, world: int, rank: int) -> tuple[int, int]:
+    """Columns [lo, hi) of A_q / B_q owned by `rank` when K is split; whole 128-wide scale groups."""
+    if k % (BLOCK * world) != 0:
+        raise ValueError(f"K={k} does not split into {world} shards of whole {BLOCK}-column groups")
+    per = k // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_k(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: torch.Tensor, b_scales: torch.Tensor,
+            world: int, rank: int):
+    """This rank's K range of a full (a_q [M, K], a_scales [M, K/128], b_q [N, K], b_scales
+    [N/128, K/128]) set, each made contiguous."""
+    lo, hi = k_shard_bounds(a_q.shape[1], world, rank)
+    return (a_q[:, lo:hi].contiguous(), a_scales[:, lo // BLOCK:hi // BLOCK].contiguous(),
+            b_q[:, lo:hi].contiguous(), b_scales[:, lo // BLOCK:hi // BLOCK].contiguous())
+
+
+def owner_rows(m: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [lo, hi) of the reduce-scattered result that `rank` owns."""
+    if m % (BLOCK * world) != 0:
+        raise ValueError(f"M={m} does not split into {world} blocks of whole {BLOCK}-row tiles")
+    per = m // world
+    return rank * per, (rank + 1) * per
+
+
+class PeerSlots:
+    """This rank's fp32 slots [G][M/G][N] for the partial results of its rows, mapped into every
+    rank, and the other ranks' slots mapped into this one (`ptrs[d]` = rank d's slots here): the
+    destinations of the scatter GEMM.  Same mapping mechanism and degradation as PeerOutput."""
+
+    def __init__(self, m: int, n: int, device=None, group=None):
+        import os
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+            self.group = group if group is not None else dist.group.WORLD
+            self.world = dist.get_world_size(self.group)
+            self.rank = dist.get_rank(self.group)
+            rows = owner_rows(m, self.world, self.rank)
+            self.local = symm.empty((self.world, rows[1] - rows[0], n), dtype=torch.float32, device=device)
+            self._handle = symm.rendezvous(self.local, self.group)
+            self.ptrs = [int(p) for p in self._handle.buffer_ptrs]
+            self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        else:
+            self.group, self.world, self.rank = None, 1, 0
+            self.local = torch.empty((1, m, n), dtype=torch.float32, device=device)
+            self.ptrs = [self.local.data_ptr()]
+            self._flag = None
+
+    def barrier(self) -> None:
+        if self._flag is not None:
+            dist.all_reduce(self._flag, group=self.group)

@@ -76,3 +76,51 @@ def test_peer_output_without_a_process_group_is_one_local_buffer():
     assert out.local.shape == (4, 256)
     out.barrier()   # nothing to meet
     assert shard.peer_columns(128, 3) == (384, 512)
+
+
+def _k_worker(rank, world, port, m, n, k, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = (0.02 * rng.standard_normal((n, k))).astype(np.float32)
+    aq, a_s = oracle.quant_fp8_per_token_group(a)
+    bq, bs = oracle.block_quant_weights(w)
+    t = [torch.from_numpy(x) for x in (aq, a_s, bq, bs)]
+    mine = [x.numpy() for x in shard.shard_k(*t, world, rank)]
+    part = torch.from_numpy(oracle.w8a8_block_fp8_gemm(*mine))          # this rank's partial [M, N]
+    # the contract of the scatter GEMM: owner d receives rows owner_rows(d) of every rank's partial
+    # in slot [source rank]; gloo gathers move the row blocks here
+    rows = [shard.owner_rows(m, world, d) for d in range(world)]
+    send = [part[lo:hi].contiguous() for lo, hi in rows]
+    recv = []
+    for d in range(world):                  # gloo has no all-to-all: one gather per owner
+        got = [torch.empty_like(send[d]) for _ in range(world)] if rank == d else None
+        dist.gather(send[d], got, dst=d)
+        if rank == d:
+            recv = got
+    acc = recv[0].clone()
+    for r in range(1, world):
+        acc = acc + recv[r]
+    lo, hi = rows[rank]
+    want = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs)[lo:hi]
+    ok = np.allclose(acc.numpy(), want, rtol=1e-5, atol=1e-6)
+    np.save(os.path.join(out_dir, f"ok{rank}.npy"), np.array([ok]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_k_sharded_gemm_scatter_and_sum_equals_unsharded(tmp_path):
+    world, m, n, k = 2, 256, 96, 512
+    mp.spawn(_k_worker, args=(world, _free_port(), m, n, k, str(tmp_path)), nprocs=world, join=True)
+    assert all(np.load(tmp_path / f"ok{r}.npy").all() for r in range(world))
+
+
+def test_k_shard_and_owner_bounds():
+    assert shard.k_shard_bounds(1024, 4, 1) == (256, 512)
+    assert shard.owner_rows(512, 2, 1) == (256, 512)
+    with pytest.raises(ValueError):
+        shard.k_shard_bounds(384, 2, 0)
+    with pytest.raises(ValueError):
+        shard.owner_rows(384, 2, 0)
