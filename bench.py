@@ -401,6 +401,80 @@ def moe_layer(peaks, experts, hidden, inter, tokens, topk, logits, x):
     return res
 
 
+def row_parallel_bench(args, world, rank, dev, max_over_ranks, sync_all, m=M_FULL, n=7168, k=18432):
+    """The layer that follows a column-parallel one: activations and weights sharded over K, so
+    every rank's GEMM yields a partial [M, N] sum and the ranks reduce-scatter it over the rows.
+    Times (a) GEMM with fp32 output + NCCL reduce_scatter and (b) the GEMM whose epilogue stores
+    its fp32 partial tiles into the row owners' slots + an ordered sum on the owner."""
+    import torch
+    import torch.distributed as dist
+    from inference_b200 import ops, shard, synth
+    if m % (128 * world) or k % (128 * world):
+        return {"unavailable": "shape does not split over the ranks"}
+    k_loc = k // world
+    x = synth.activations(m, k_loc, seed=20 + rank, outliers=True, device=dev)     # this rank's K range
+    bq, bs = synth.quantised_weights(n, k_loc, seed=40 + rank, device=dev)
+    aq, a_s = ops.quant_fp8_per_token_group(x)
+    part = torch.empty((m, n), dtype=torch.float32, device=dev)
+    rs_out = torch.empty((m // world, n), dtype=torch.float32, device=dev)
+    stream = torch.cuda.current_stream()
+    flops = 2.0 * m * n * k
+    res = {"m": m, "n": n, "k": k, "k_per_gpu": k_loc,
+           "bytes_sent_per_rank": 4 * (m // world) * n * (world - 1)}
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return max_over_ranks(e0.elapsed_time(e1) * 1e-3 / args.steps)
+
+    def gemm_only():
+        ops.quant_fp8_per_token_group(x, 128, aq, a_s)
+        ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, out=part)
+
+    def nccl():
+        gemm_only()
+        dist.reduce_scatter_tensor(rs_out, part)
+
+    t0 = timed(gemm_only)
+    res["gemm_only"] = {"ms_per_step": t0 * 1e3, "value": flops / t0 / 1e12}
+    t1 = timed(nccl)
+    res["nccl_reduce_scatter"] = {"ms_per_step": t1 * 1e3, "value": flops / t1 / 1e12, "sum": "fp32, NCCL's order"}
+    try:
+        slots = shard.PeerSlots(m, n, dev)
+        err = None
+    except Exception as exc:
+        slots, err = None, f"{type(exc).__name__}: {exc}"
+    flag = torch.tensor([0 if slots is None else 1], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag.item()) == 0:
+        res["fused"] = {"unavailable": err or "peer mapping failed on another rank"}
+        return res
+    out = torch.empty((m // world, n), dtype=torch.bfloat16, device=dev)
+
+    def fused():
+        ops.quant_fp8_per_token_group(x, 128, aq, a_s)
+        ops.w8a8_block_fp8_gemm_scatter(slots.ptrs, rank, aq, a_s, bq, bs)
+        slots.barrier()
+        ops.reduce_slots(slots.local, out=out)
+        slots.barrier()      # nobody overwrites slots that their owner is still adding
+
+    t2 = timed(fused)
+    close = torch.allclose(out.float(), rs_out, rtol=2e-2, atol=1e-2)
+    res["fused"] = {"ms_per_step": t2 * 1e3, "value": flops / t2 / 1e12, "sum": "fp32, rank order",
+                    "agrees_with_nccl_within_bf16_rounding": bool(close),
+                    "link_gbs_out_per_rank": res["bytes_sent_per_rank"] / t2 / 1e9}
+    status = ops.device_status()
+    assert status[0] == 0, f"device-side wait ran out: {status}"
+    return res
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def run_ours(args):
     import torch
@@ -530,6 +604,11 @@ def run_ours(args):
             gather["fused"] = {"unavailable": peer_error or "peer mapping failed on another rank"}
         del c_all, po
 
+    # ---- the row-parallel partner layer (K sharded), reduce-scattered: reported separately
+    row_parallel = None
+    if world > 1 and not args.no_gather:
+        row_parallel = row_parallel_bench(args, world, rank, dev, max_over_ranks, sync_all)
+
     # ---- end-to-end through the public API with host buffers
     e2e = None
     if not args.no_e2e:
@@ -610,6 +689,8 @@ def run_ours(args):
         line["e2e"] = e2e
     if gather:
         line["gather"] = gather
+    if row_parallel:
+        line["row_parallel"] = row_parallel
     if world == 1 and not args.no_sweep:
         del x, bq, bs, aq, a_s, c
         torch.cuda.empty_cache()
