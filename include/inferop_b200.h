@@ -272,8 +272,9 @@ INFEROP_API int inferop_selftest_quant_div(int32_t dt, uint64_t* out3);
 /* Tuning knobs for experiments and tests (process-wide, not thread-safe).
  * key: "gemm_tma_store" (-1 auto, 0, 1), "gemm_ctas" (0 = one per SM), "gemm_path" (0 auto,
  *      1 always the large-tile kernel, 2 the small-M kernel whenever M <= 128), "gemm_block_n"
- *      (accepted and ignored: the kernel has one tile shape).  Returns INFEROP_ERR_SHAPE for
- *      an unknown key/value. */
+ *      (0 auto, 128 or 256: tile width of the large-tile kernel; results do not depend on it),
+ *      "gemm_group_m", "decode_splits", "decode_pdl".  Returns INFEROP_ERR_SHAPE for an unknown
+ *      key/value. */
 INFEROP_API int inferop_set_option(const char* key, int64_t value);
 
 #ifdef __cplusplus
