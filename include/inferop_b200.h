@@ -77,7 +77,8 @@ INFEROP_API int inferop_dequant_fp8_per_token_group(void* x, int32_t dt, const v
  * Contract as in the reference: group_size == 128, block_n == 128, K % 128 == 0,
  * M > 0, N > 0 (else INFEROP_ERR_SHAPE).  a_q and b_q must be 16-byte aligned
  * (INFEROP_ERR_POINTER otherwise); c may have any alignment and N any value.
- * Calls with M <= 96 take a weight-streaming kernel that keeps a library-owned scratch
+ * Calls with few tokens (M <= 32, and M <= 64 when ceil(N/128) is below 3/4 of the SM count)
+ * take a weight-streaming kernel that keeps a library-owned scratch
  * buffer (about 10 MB) per stream; it is allocated by the first such call on a stream, so
  * make that call before capturing the stream into a CUDA graph. */
 INFEROP_API int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, const void* b_q,
@@ -121,7 +122,7 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm_grouped(void* c, const void* a_q, co
  * c_peers is a HOST array of n_peers device addresses, entry d = the base of rank d's buffer as
  * mapped into this process (CUDA IPC, virtual-memory export or symmetric memory; entry `rank` is
  * the local buffer), each 16-byte aligned; it is read before the call returns.  n % 128 == 0,
- * n_peers <= 8, out_dt 1 (fp16) or 2 (bf16).  M <= 96 runs the weight-streaming kernel of the
+ * n_peers <= 8, out_dt 1 (fp16) or 2 (bf16).  Few tokens (the rule of the plain GEMM) run the weight-streaming kernel of the
  * plain GEMM (plain stores to the peers, same per-stream scratch), larger M the large-tile kernel
  * (one TMA store per destination).  The call does not synchronise the ranks: a rank's
  * buffer is complete when every rank's call has finished, so the ranks must meet (a barrier, a

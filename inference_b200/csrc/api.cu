@@ -208,6 +208,20 @@ int inferop_dequant_fp8_per_token_group(void* x, int32_t dt, const void* q, cons
                         static_cast<cudaStream_t>(stream), ctx->sm_count);
 }
 
+// Which kernel serves a plain GEMM call.  Measured on B200 (N x K = 18432 x 7168, 7168 x 18432,
+// 24576 x 1536, 4096 x 7168, 36864 x 7168): up to 32 tokens the weight-streaming kernel is never
+// slower; from 65 tokens on the large-tile kernel with 128-column tiles is 1.5-2.5 times faster;
+// in between the large-tile kernel wins once there is about one 128-row weight tile per SM, and
+// the weight-streaming kernel (which splits K over the idle SMs) wins below that.
+static bool small_m_kernel(const DeviceCtx* ctx, int64_t m, int64_t n) {
+  const int path = options().gemm_path;
+  const int64_t tiles = (n + 127) / 128;
+  if (path == 1 || m > kDecodeMaxM || tiles > kDecodeMaxTiles) return false;
+  if (path == 2 || m <= 32) return true;
+  if (m <= 64) return tiles * 4 < static_cast<int64_t>(ctx->sm_count) * 3;
+  return false;
+}
+
 int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, const void* b_q,
                                 const void* b_scales, int64_t m, int64_t n, int64_t k,
                                 int32_t group_size, int32_t block_n, int32_t out_dt,
@@ -234,9 +248,7 @@ int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, 
   // scratch is created on the first such call of each stream (a cudaMalloc: make that call
   // before any stream capture); with more than DeviceCtx::kMaxStreams streams, or when the
   // allocation fails, the large-tile kernel serves the call instead.
-  const int path = options().gemm_path;
-  const int64_t tiles = (n + 127) / 128;
-  if (path != 1 && m <= kDecodeMaxM && tiles <= kDecodeMaxTiles && (path == 2 || m <= 96)) {
+  if (small_m_kernel(ctx, m, n)) {
     float* ws = nullptr;
     int* counters = nullptr;
     if (decode_scratch(ctx, s, &ws, &counters)) {
@@ -317,7 +329,7 @@ int inferop_w8a8_block_fp8_gemm_allgather(void* const* c_peers, int32_t n_peers,
   if (!ctx) return err;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // a few tokens: the weight-streaming kernel, storing straight into every rank's buffer
-  if (m <= 96 && (n + 127) / 128 <= kDecodeMaxTiles && options().gemm_path != 1) {
+  if (small_m_kernel(ctx, m, n)) {
     float* ws;
     int* counters;
     if (decode_scratch(ctx, s, &ws, &counters)) {
@@ -519,7 +531,7 @@ int inferop_set_option(const char* key, int64_t value) {
   if (!key) return INFEROP_ERR_SHAPE;
   Options& o = options();
   if (!strcmp(key, "gemm_block_n")) {
-    if (value != 0 && value != 128 && value != 256) return INFEROP_ERR_SHAPE;  // kept for callers; one tile shape now
+    if (value != 0 && value != 128 && value != 256) return INFEROP_ERR_SHAPE;
     o.gemm_block_n = static_cast<int>(value);
   } else if (!strcmp(key, "gemm_tma_store")) {
     if (value < -1 || value > 1) return INFEROP_ERR_SHAPE;

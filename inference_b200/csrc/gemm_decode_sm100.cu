@@ -98,11 +98,17 @@ __device__ __forceinline__ __half cvt_out<__half>(float v) { return __float2half
 template <>
 __device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-template <typename OutT>
-__device__ __forceinline__ void store_out(const DecodeParams& p, int m, int gn, float v) {
-  const OutT o = cvt_out<OutT>(v);
-  const int64_t at = static_cast<int64_t>(m) * p.ldc + p.col0 + gn;
-  for (int d = 0; d < p.n_dst; ++d) static_cast<OutT*>(p.dst[d])[at] = o;
+// Column gn of the result (MP values, one per token, in registers) to every destination.  The
+// destination loop is the outer one so that the token loop stays fully unrolled over registers;
+// with the usual single destination it runs once.
+template <int MP, typename OutT>
+__device__ __forceinline__ void store_column(const DecodeParams& p, int gn, const float (&v)[MP]) {
+  for (int d = 0; d < p.n_dst; ++d) {
+    OutT* col = static_cast<OutT*>(p.dst[d]) + p.col0 + gn;
+#pragma unroll
+    for (int m = 0; m < MP; ++m)
+      if (m < p.m) col[static_cast<int64_t>(m) * p.ldc] = cvt_out<OutT>(v[m]);
+  }
 }
 
 template <int N>
@@ -466,11 +472,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int gn = t * TN + row;
         const bool whole = (seg_kb0 == 0 && kb == p.kb - 1);
         if (whole) {
-          if (gn < p.n) {
-#pragma unroll
-            for (int m = 0; m < MP; ++m)
-              if (m < p.m) store_out<OutT>(p, m, gn, acc[m]);
-          }
+          if (gn < p.n) store_column<MP, OutT>(p, gn, acc);
         } else {
           // one K part of a split tile: this CTA's slot of the workspace
           float* wp = p.workspace + static_cast<int64_t>(blockIdx.x) * (MP * TN);
@@ -493,11 +495,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
               for (int m = 0; m < MP; ++m) sum[m] += __ldcg(rp + m * TN + row);
             }
-            if (gn < p.n) {
-#pragma unroll
-              for (int m = 0; m < MP; ++m)
-                if (m < p.m) store_out<OutT>(p, m, gn, sum[m]);
-            }
+            if (gn < p.n) store_column<MP, OutT>(p, gn, sum);
             if (ct == 0) p.counters[t] = 0;   // ready for the next launch
           }
           named_bar_sync(1, 128);   // last_flag may be rewritten only after everyone has read it

@@ -509,6 +509,36 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
             }
             tma_store_commit();
           }
+        } else if (kGrouped && sizeof(OutT) == 2 && p.tma_store) {
+          // A group's ragged tile: a TMA store would write all 128 rows and run into the next
+          // group, so the block is staged the same way and copied out by the 128 threads of this
+          // column half with row-guarded 16-byte stores, 8 lanes per 128-byte row segment
+          // (coalesced; the per-thread-row stores below touch 32 rows per instruction).
+          if (issuer) tma_store_wait_read0();
+          named_bar_sync(1 + half, 128);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 w;
+            const float* a8 = accf + j * 8;
+            w.x = pack2<OutT>(a8[0], a8[1]);
+            w.y = pack2<OutT>(a8[2], a8[3]);
+            w.z = pack2<OutT>(a8[4], a8[5]);
+            w.w = pack2<OutT>(a8[6], a8[7]);
+            *reinterpret_cast<uint4*>(my_buf + row * 128 + ((j ^ (row & 7)) << 4)) = w;
+          }
+          named_bar_sync(1 + half, 128);
+          if (col0 < p.n) {
+            const int chunk = row & 7;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = (row >> 3) + 16 * i;
+              if (ti.a_row + r < ti.row_end) {
+                const uint4 w = *reinterpret_cast<const uint4*>(my_buf + r * 128 + ((chunk ^ (r & 7)) << 4));
+                OutT* dst = static_cast<OutT*>(p.c) + static_cast<int64_t>(ti.a_row + r) * p.n + col0 + chunk * 8;
+                *reinterpret_cast<uint4*>(dst) = w;
+              }
+            }
+          }
         } else if (gm < ti.row_end) {
           OutT* crow = static_cast<OutT*>(p.c) + static_cast<int64_t>(gm) * p.n;
           constexpr int kVec = 16 / sizeof(OutT);
