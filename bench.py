@@ -35,6 +35,30 @@ NOMINAL_HBM_GBS = 8000.0
 print_result = print
 
 
+_REAL_STDOUT_FD = None
+
+
+def emit_now(text: str) -> None:
+    """Write a result line straight to the process's real stdout (used when the run is cut short)."""
+    fd = _REAL_STDOUT_FD if _REAL_STDOUT_FD is not None else 1
+    os.write(fd, (text + "\n").encode())
+
+
+def run_with_deadline(fn, seconds, on_timeout):
+    import threading
+    done = threading.Event()
+
+    def watch():
+        if not done.wait(seconds):
+            on_timeout()
+
+    threading.Thread(target=watch, daemon=True).start()
+    try:
+        return fn()
+    finally:
+        done.set()
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -47,6 +71,8 @@ def parse_args():
     ap.add_argument("--gather", action="store_true",
                     help="(default for N > 1) also time the all-gather of C: NCCL, and the GEMM's own epilogue")
     ap.add_argument("--no-gather", action="store_true", help="skip the all-gather measurements")
+    ap.add_argument("--collective-seconds", type=int, default=180,
+                    help="deadline for the collective sections (N > 1); the main result is printed without them after it")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the decode / prefill shape sweep (N=1 only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -549,66 +575,6 @@ def run_ours(args):
     t_step = t_region / args.steps
     value = flops_total / t_step / 1e12
 
-    # ---- optional all-gather of C (reported separately)
-    gather = None
-    if world > 1 and not args.no_gather:
-        c_all = torch.empty((world * m, n_loc), dtype=torch.bfloat16, device=dev)  # [G][M][N/G] rank-blocked
-        for _ in range(2):
-            dist.all_gather_into_tensor(c_all, c)
-        sync_all()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record(stream)
-        for _ in range(args.steps):
-            step()
-            dist.all_gather_into_tensor(c_all, c)
-        g1.record(stream)
-        torch.cuda.synchronize()
-        tg = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
-        gather = {"ms_per_step_with_gather": tg * 1e3, "value_with_gather": flops_total / tg / 1e12,
-                  "bytes_received_per_rank": 2 * m * n_loc * (world - 1), "layout": "[G][M][N/G] rank-blocked"}
-        # the same step with the gather done by the GEMM's own epilogue (peer stores into every
-        # rank's row-major [M, N] buffer), then a stream-ordered meeting of the ranks
-        from inference_b200 import shard
-        try:
-            po = shard.PeerOutput(m, n, torch.bfloat16, dev)
-            peer_error = None
-        except Exception as exc:   # no peer mapping on this box: report it, keep the NCCL figures
-            po, peer_error = None, f"{type(exc).__name__}: {exc}"
-        # every rank must take the same branch
-        flag = torch.tensor([0 if po is None else 1], device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 1:
-            def fused_step():
-                ops.quant_fp8_per_token_group(x, 128, aq, a_s)
-                ops.w8a8_block_fp8_gemm_allgather(po.ptrs, rank, aq, a_s, bq, bs)
-                po.barrier()
-
-            for _ in range(2):
-                fused_step()
-            sync_all()
-            g0.record(stream)
-            for _ in range(args.steps):
-                fused_step()
-            g1.record(stream)
-            torch.cuda.synchronize()
-            tf = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
-            blocked = c_all.view(world, m, n_loc)
-            same = all(torch.equal(po.local[:, r * n_loc:(r + 1) * n_loc], blocked[r]) for r in range(world))
-            gather["fused"] = {"ms_per_step": tf * 1e3, "value": flops_total / tf / 1e12,
-                               "layout": "[M][N] row-major on every rank",
-                               "equals_nccl_gather": bool(same),
-                               "link_gbs_out_per_rank": 2 * m * n_loc * (world - 1) / tf / 1e9}
-            status = ops.device_status()
-            assert status[0] == 0, f"device-side wait ran out: {status}"
-        else:
-            gather["fused"] = {"unavailable": peer_error or "peer mapping failed on another rank"}
-        del c_all, po
-
-    # ---- the row-parallel partner layer (K sharded), reduce-scattered: reported separately
-    row_parallel = None
-    if world > 1 and not args.no_gather:
-        row_parallel = row_parallel_bench(args, world, rank, dev, max_over_ranks, sync_all)
-
     # ---- end-to-end through the public API with host buffers
     e2e = None
     if not args.no_e2e:
@@ -673,6 +639,71 @@ def run_ours(args):
     roofline["traffic"] = model * ratio
     roofline["traffic_note"] = "model bands*N*K + M*K + 2*M*N, checked against ncu at M=4096 and M=8192"
 
+    # ---- the collective forms (all-gather of C, row-parallel partner): measured after the main
+    # figures are complete and under a deadline, so that a box on which the peer mapping or a
+    # collective stalls still yields the main result
+    def collective_sections():
+        # ---- optional all-gather of C (reported separately)
+        gather = None
+        if world > 1 and not args.no_gather:
+            c_all = torch.empty((world * m, n_loc), dtype=torch.bfloat16, device=dev)  # [G][M][N/G] rank-blocked
+            for _ in range(2):
+                dist.all_gather_into_tensor(c_all, c)
+            sync_all()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record(stream)
+            for _ in range(args.steps):
+                step()
+                dist.all_gather_into_tensor(c_all, c)
+            g1.record(stream)
+            torch.cuda.synchronize()
+            tg = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
+            gather = {"ms_per_step_with_gather": tg * 1e3, "value_with_gather": flops_total / tg / 1e12,
+                      "bytes_received_per_rank": 2 * m * n_loc * (world - 1), "layout": "[G][M][N/G] rank-blocked"}
+            # the same step with the gather done by the GEMM's own epilogue (peer stores into every
+            # rank's row-major [M, N] buffer), then a stream-ordered meeting of the ranks
+            from inference_b200 import shard
+            try:
+                po = shard.PeerOutput(m, n, torch.bfloat16, dev)
+                peer_error = None
+            except Exception as exc:   # no peer mapping on this box: report it, keep the NCCL figures
+                po, peer_error = None, f"{type(exc).__name__}: {exc}"
+            # every rank must take the same branch
+            flag = torch.tensor([0 if po is None else 1], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 1:
+                def fused_step():
+                    ops.quant_fp8_per_token_group(x, 128, aq, a_s)
+                    ops.w8a8_block_fp8_gemm_allgather(po.ptrs, rank, aq, a_s, bq, bs)
+                    po.barrier()
+
+                for _ in range(2):
+                    fused_step()
+                sync_all()
+                g0.record(stream)
+                for _ in range(args.steps):
+                    fused_step()
+                g1.record(stream)
+                torch.cuda.synchronize()
+                tf = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
+                blocked = c_all.view(world, m, n_loc)
+                same = all(torch.equal(po.local[:, r * n_loc:(r + 1) * n_loc], blocked[r]) for r in range(world))
+                gather["fused"] = {"ms_per_step": tf * 1e3, "value": flops_total / tf / 1e12,
+                                   "layout": "[M][N] row-major on every rank",
+                                   "equals_nccl_gather": bool(same),
+                                   "link_gbs_out_per_rank": 2 * m * n_loc * (world - 1) / tf / 1e9}
+                status = ops.device_status()
+                assert status[0] == 0, f"device-side wait ran out: {status}"
+            else:
+                gather["fused"] = {"unavailable": peer_error or "peer mapping failed on another rank"}
+            del c_all, po
+
+        # ---- the row-parallel partner layer (K sharded), reduce-scattered: reported separately
+        row_parallel = None
+        if world > 1 and not args.no_gather:
+            row_parallel = row_parallel_bench(args, world, rank, dev, max_over_ranks, sync_all)
+        return gather, row_parallel
+
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": t_step * 1e3, "higher_is_better": True,
@@ -687,10 +718,17 @@ def run_ours(args):
     }
     if e2e:
         line["e2e"] = e2e
-    if gather:
-        line["gather"] = gather
-    if row_parallel:
-        line["row_parallel"] = row_parallel
+    if world > 1 and not args.no_gather:
+        def give_up():
+            if rank == 0:
+                line["gather"] = {"unavailable": f"the collective sections did not finish within {args.collective_seconds} s"}
+                emit_now(json.dumps(line))
+            os._exit(0)
+        gather, row_parallel = run_with_deadline(collective_sections, args.collective_seconds, give_up)
+        if gather:
+            line["gather"] = gather
+        if row_parallel:
+            line["row_parallel"] = row_parallel
     if world == 1 and not args.no_sweep:
         del x, bq, bs, aq, a_s, c
         torch.cuda.empty_cache()
@@ -717,6 +755,8 @@ def main():
     # and the result line is written to the saved descriptor.
     sys.stdout.flush()
     real_stdout = os.dup(1)
+    global _REAL_STDOUT_FD
+    _REAL_STDOUT_FD = real_stdout
     os.dup2(2, 1)
     captured = []
     global print_result
