@@ -44,6 +44,11 @@ def emit_now(text: str) -> None:
     os.write(fd, (text + "\n").encode())
 
 
+def progress(msg: str) -> None:
+    """One line on stderr: where a multi-GPU run is (stdout carries only the result line)."""
+    print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 def run_with_deadline(fn, seconds, on_timeout):
     import threading
     done = threading.Event()
@@ -468,10 +473,13 @@ def row_parallel_bench(args, world, rank, dev, max_over_ranks, sync_all, m=M_FUL
         gemm_only()
         dist.reduce_scatter_tensor(rs_out, part)
 
+    progress("row-parallel: GEMM alone")
     t0 = timed(gemm_only)
     res["gemm_only"] = {"ms_per_step": t0 * 1e3, "value": flops / t0 / 1e12}
+    progress("row-parallel: NCCL reduce_scatter")
     t1 = timed(nccl)
     res["nccl_reduce_scatter"] = {"ms_per_step": t1 * 1e3, "value": flops / t1 / 1e12, "sum": "fp32, NCCL's order"}
+    progress("row-parallel: mapping the peers' slots")
     try:
         slots = shard.PeerSlots(m, n, dev)
         err = None
@@ -491,6 +499,7 @@ def row_parallel_bench(args, world, rank, dev, max_over_ranks, sync_all, m=M_FUL
         ops.reduce_slots(slots.local, out=out)
         slots.barrier()      # nobody overwrites slots that their owner is still adding
 
+    progress("row-parallel: scatter epilogue + ordered sum")
     t2 = timed(fused)
     close = torch.allclose(out.float(), rs_out, rtol=2e-2, atol=1e-2)
     res["fused"] = {"ms_per_step": t2 * 1e3, "value": flops / t2 / 1e12, "sum": "fp32, rank order",
@@ -599,11 +608,6 @@ def run_ours(args):
                "api": "inference_b200.host.HostLinearFP8: 2048-row panels, copy-in / quant+GEMM / copy-out on three streams"}
         del x_host, c_host, lin
 
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
     peaks = measured_peaks()
     fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
     gemm_flops = 2.0 * m * n_loc * k
@@ -646,6 +650,7 @@ def run_ours(args):
         # ---- optional all-gather of C (reported separately)
         gather = None
         if world > 1 and not args.no_gather:
+            progress("all-gather by NCCL")
             c_all = torch.empty((world * m, n_loc), dtype=torch.bfloat16, device=dev)  # [G][M][N/G] rank-blocked
             for _ in range(2):
                 dist.all_gather_into_tensor(c_all, c)
@@ -663,6 +668,7 @@ def run_ours(args):
             # the same step with the gather done by the GEMM's own epilogue (peer stores into every
             # rank's row-major [M, N] buffer), then a stream-ordered meeting of the ranks
             from inference_b200 import shard
+            progress("mapping the peers' output buffers")
             try:
                 po = shard.PeerOutput(m, n, torch.bfloat16, dev)
                 peer_error = None
@@ -672,6 +678,8 @@ def run_ours(args):
             flag = torch.tensor([0 if po is None else 1], device=dev)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
             if int(flag.item()) == 1:
+                progress("all-gather by the GEMM epilogue")
+
                 def fused_step():
                     ops.quant_fp8_per_token_group(x, 128, aq, a_s)
                     ops.w8a8_block_fp8_gemm_allgather(po.ptrs, rank, aq, a_s, bq, bs)
@@ -701,8 +709,17 @@ def run_ours(args):
         # ---- the row-parallel partner layer (K sharded), reduce-scattered: reported separately
         row_parallel = None
         if world > 1 and not args.no_gather:
+            progress("row-parallel partner")
             row_parallel = row_parallel_bench(args, world, rank, dev, max_over_ranks, sync_all)
+            progress("collective sections done")
         return gather, row_parallel
+
+    if rank != 0:
+        # the other ranks take part in the collective sections and print nothing
+        if not args.no_gather:
+            run_with_deadline(collective_sections, args.collective_seconds, lambda: os._exit(0))
+        dist.destroy_process_group()
+        return
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
