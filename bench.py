@@ -665,6 +665,42 @@ def run_ours(args):
             tg = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
             gather = {"ms_per_step_with_gather": tg * 1e3, "value_with_gather": flops_total / tg / 1e12,
                       "bytes_received_per_rank": 2 * m * n_loc * (world - 1), "layout": "[G][M][N/G] rank-blocked"}
+            # the same with the GEMM cut into row panels and each panel's all-gather issued on a
+            # second stream as soon as the panel is done, so that NCCL moves panel p while the
+            # tensor cores work on panel p + 1 (layout [P][G][M/P][N/G])
+            progress("all-gather by NCCL, panel-pipelined")
+            panels = 8 if m % (8 * 128) == 0 else 1
+            rows_p = m // panels
+            side = torch.cuda.Stream(device=dev)
+            c_pan = torch.empty((panels, world * rows_p, n_loc), dtype=torch.bfloat16, device=dev)
+            evs = [torch.cuda.Event() for _ in range(panels)]
+
+            def panel_step():
+                ops.quant_fp8_per_token_group(x, 128, aq, a_s)
+                for pi in range(panels):
+                    r0, r1 = pi * rows_p, (pi + 1) * rows_p
+                    ops.w8a8_block_fp8_gemm(aq[r0:r1], a_s[r0:r1], bq, bs, out=c[r0:r1])
+                    evs[pi].record(stream)
+                    with torch.cuda.stream(side):
+                        side.wait_event(evs[pi])
+                        dist.all_gather_into_tensor(c_pan[pi], c[r0:r1])
+                stream.wait_stream(side)
+
+            for _ in range(2):
+                panel_step()
+            sync_all()
+            g0.record(stream)
+            for _ in range(args.steps):
+                panel_step()
+            g1.record(stream)
+            torch.cuda.synchronize()
+            tp = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
+            same_p = all(torch.equal(c_pan[pi].view(world, rows_p, n_loc)[r],
+                                     c_all.view(world, m, n_loc)[r, pi * rows_p:(pi + 1) * rows_p])
+                         for pi in range(panels) for r in range(world))
+            gather["panel_pipelined"] = {"ms_per_step": tp * 1e3, "value": flops_total / tp / 1e12, "panels": panels,
+                                         "layout": "[P][G][M/P][N/G]", "equals_nccl_gather": bool(same_p)}
+            del c_pan
             # the same step with the gather done by the GEMM's own epilogue (peer stores into every
             # rank's row-major [M, N] buffer), then a stream-ordered meeting of the ranks
             from inference_b200 import shard
