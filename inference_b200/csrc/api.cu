@@ -112,6 +112,15 @@ DeviceCtx* current_ctx(int* err) {
   return c;
 }
 
+DeviceCtx* peek_ctx() {
+  DeviceTable& t = table();
+  int dev = -1;
+  if (t.count <= 0 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  DeviceCtx* c = &t.ctx[dev];
+  std::lock_guard<std::mutex> lock(t.ctx_mutex);
+  return c->ordinal < 0 ? nullptr : c;
+}
+
 // Scratch set of `stream` on this device, created on first use.  False when none can be had.
 bool decode_scratch(DeviceCtx* ctx, cudaStream_t stream, float** ws, int** counters) {
   static std::mutex m;
@@ -255,6 +264,7 @@ int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, 
       return launch_gemm_decode(ctx, ws, counters, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
     }
   }
+  if (use_pair_kernel(m)) return launch_gemm_pair(ctx, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
   return launch_gemm(ctx, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
 }
 
@@ -277,7 +287,7 @@ int inferop_w8a8_block_fp8_gemm_fused_quant(void* c, const void* a, int32_t a_dt
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* ws = nullptr;
   int* counters = nullptr;
-  if (!decode_scratch(ctx, s, &ws, &counters)) return INFEROP_ERR_CUDA;
+  if (!decode_scratch(ctx, s, &ws, &counters)) return INFEROP_ERR_LIMIT;   // no scratch set left for this stream
   return launch_gemm_decode_fused(ctx, ws, counters, c, a, a_dt, b_q, b_scales, m, n, k, out_dt, s);
 }
 
@@ -495,19 +505,27 @@ int inferop_w8a8_block_fp8_gemm_grouped_tiles(void* c, const void* a_q, const vo
 }
 
 int inferop_device_status(uint32_t* out4, int reset) {
-  int err;
-  DeviceCtx* ctx = current_ctx(&err);
-  if (!ctx) return err;
+  // Allocates nothing: reads the record of the library-owned context if one exists on this
+  // device, and the record inside the fixed scratch array if the allocation-free entry point
+  // has run here.  The first non-zero record is reported.
+  if (table().count <= 0) return INFEROP_ERR_NO_DEVICE;
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return note_cuda_error(e);
-  DeviceStatus host;
-  e = cudaMemcpy(&host, ctx->status, sizeof(host), cudaMemcpyDeviceToHost);
-  if (e != cudaSuccess) return note_cuda_error(e);
-  if (out4) memcpy(out4, &host, sizeof(host));
-  if (reset) {
-    e = cudaMemset(ctx->status, 0, sizeof(DeviceStatus));
+  DeviceStatus host = {0, 0, 0, 0};
+  if (DeviceCtx* ctx = peek_ctx()) {
+    e = cudaMemcpy(&host, ctx->status, sizeof(host), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return note_cuda_error(e);
+    if (reset) {
+      e = cudaMemset(ctx->status, 0, sizeof(DeviceStatus));
+      if (e != cudaSuccess) return note_cuda_error(e);
+    }
   }
+  DeviceStatus fixed = {0, 0, 0, 0};
+  bool used = false;
+  const int rc = fixed_scratch_status(&fixed, reset != 0, &used);
+  if (rc != INFEROP_OK) return rc;
+  if (host.code == 0 && used && fixed.code != 0) host = fixed;
+  if (out4) memcpy(out4, &host, sizeof(host));
   return host.code == 0 ? INFEROP_OK : INFEROP_ERR_DEVICE_WAIT;
 }
 
@@ -547,6 +565,11 @@ int inferop_set_option(const char* key, int64_t value) {
   } else if (!strcmp(key, "gemm_path")) {
     if (value < 0 || value > 2) return INFEROP_ERR_SHAPE;
     o.gemm_path = static_cast<int>(value);
+  } else if (!strcmp(key, "gemm_pair")) {
+    if (value < -1 || value > 1) return INFEROP_ERR_SHAPE;
+    o.gemm_pair = static_cast<int>(value);
+  } else if (!strcmp(key, "gemm_pdl")) {
+    o.gemm_pdl = value != 0;
   } else if (!strcmp(key, "gemm_ctas")) {
     if (value < 0 || value > 1024) return INFEROP_ERR_SHAPE;
     o.gemm_ctas = static_cast<int>(value);

@@ -622,16 +622,16 @@ int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, vo
 
 int launch_gemm_decode(DeviceCtx* ctx, float* workspace, int* counters, void* c, const void* a_q,
                        const void* a_scales, const void* b_q, const void* b_scales, int64_t m,
-                       int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream) {
+                       int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream, int clear_counters) {
   void* const dst[1] = {c};
   return launch_gemm_decode_to(ctx, workspace, counters, dst, 1, n, 0, a_q, a_scales, b_q, b_scales, m, n,
-                               k, out_dt, stream);
+                               k, out_dt, stream, clear_counters);
 }
 
 int launch_gemm_decode_to(DeviceCtx* ctx, float* workspace, int* counters, void* const* dst, int n_dst,
                           int64_t ldc, int64_t col0, const void* a_q, const void* a_scales,
                           const void* b_q, const void* b_scales, int64_t m, int64_t n, int64_t k,
-                          int32_t out_dt, cudaStream_t stream) {
+                          int32_t out_dt, cudaStream_t stream, int clear_counters) {
   const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
   DecodeParams p;
   p.a_src = nullptr;
@@ -656,6 +656,12 @@ int launch_gemm_decode_to(DeviceCtx* ctx, float* workspace, int* counters, void*
   if (rc != INFEROP_OK) return rc;
   rc = make_tensor_map_2d(&ma, a_q, 1, m, k, k, mp, BK, true);
   if (rc != INFEROP_OK) return rc;
+  if (out_dt < 0 || out_dt > 2) return INFEROP_ERR_DTYPE;
+  if (clear_counters > 0) {
+    // everything that can reject the call has been checked: nothing is left on the stream by a rejected call
+    const cudaError_t e = cudaMemsetAsync(counters, 0, static_cast<size_t>(clear_counters) * sizeof(int), stream);
+    if (e != cudaSuccess) return note_cuda_error(e);
+  }
   const Options& opt = options();
   int max_ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
   if (max_ctas > ctx->sm_count) max_ctas = ctx->sm_count;   // the workspace is sized for one CTA per SM
@@ -714,10 +720,18 @@ struct FixedScratchPtr {
   int sm_version = 0;
 };
 
+FixedScratchPtr g_fixed_cache[64];
+std::mutex g_fixed_mutex;
+
+FixedScratch* fixed_scratch_cached(int dev) {
+  std::lock_guard<std::mutex> lock(g_fixed_mutex);
+  return g_fixed_cache[dev].ptr;
+}
+
 // Device address of the scratch on the current device, resolved once per device.
 int fixed_scratch_for_current_device(FixedScratchPtr* out) {
-  static FixedScratchPtr cache[64];
-  static std::mutex m;
+  FixedScratchPtr* cache = g_fixed_cache;
+  std::mutex& m = g_fixed_mutex;
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return note_cuda_error(e);
@@ -749,12 +763,18 @@ extern "C" int inferop_w8a8_block_fp8_gemm_fixed_scratch(void* c, const void* a_
                                                          int64_t n, int64_t k, int32_t group_size,
                                                          int32_t block_n, int32_t out_dt, void* stream) {
   using namespace ib200;
-  if (group_size != 128 || block_n != 128 || k <= 0 || k % 128 != 0 || m <= 0 || n <= 0) {
+  if (group_size != 128 || block_n != 128 || k < 0 || k % 128 != 0 || m <= 0 || n <= 0) {
     return INFEROP_ERR_SHAPE;
   }
   if (out_dt < 0 || out_dt > 2) return INFEROP_ERR_DTYPE;
   if (m > kFixedMaxM || (n + TN - 1) / TN > kFixedMaxTiles || k > 0x7FFFFF00LL) return INFEROP_ERR_LIMIT;
-  if (!c || !a_q || !a_scales || !b_q || !b_scales) return INFEROP_ERR_POINTER;
+  if (!c) return INFEROP_ERR_POINTER;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (k == 0) {  // empty sum: zeros, as the regular entry point (and the reference's kernel) stores
+    const cudaError_t e = cudaMemsetAsync(c, 0, static_cast<size_t>(m) * n * (out_dt == 0 ? 4 : 2), s);
+    return e == cudaSuccess ? INFEROP_OK : note_cuda_error(e);
+  }
+  if (!a_q || !a_scales || !b_q || !b_scales) return INFEROP_ERR_POINTER;
   if ((reinterpret_cast<uintptr_t>(a_q) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u)) {
     return INFEROP_ERR_POINTER;
   }
@@ -763,16 +783,35 @@ extern "C" int inferop_w8a8_block_fp8_gemm_fixed_scratch(void* c, const void* a_
   if (rc != INFEROP_OK) return rc;
   if (fs.sm_version != 100) return INFEROP_ERR_ARCH;
   if (fs.sm_count > kFixedMaxCtas) return INFEROP_ERR_LIMIT;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // the array keeps whatever the last call left: the arrival counters must start at zero
-  const int64_t tiles = (n + TN - 1) / TN;
-  const cudaError_t e = cudaMemsetAsync(fs.ptr->counters, 0, static_cast<size_t>(tiles) * sizeof(int), s);
-  if (e != cudaSuccess) return note_cuda_error(e);
   DeviceCtx local;  // carries the SM count and the status slot to the launcher; owns nothing
   local.ordinal = 0;
   local.sm_version = fs.sm_version;
   local.sm_count = fs.sm_count;
   local.status = &fs.ptr->status;
+  // the array keeps whatever the last call left: the launcher zeroes the arrival counters of this
+  // call's tiles on the stream, after its last check and before the kernel
+  const int tiles = static_cast<int>((n + TN - 1) / TN);
   return launch_gemm_decode(&local, fs.ptr->partials, fs.ptr->counters, c, a_q, a_scales, b_q, b_scales,
-                            m, n, k, out_dt, s);
+                            m, n, k, out_dt, s, tiles);
+}
+
+// The bounded-wait record of the fixed-scratch entry point on the current device, for
+// inferop_device_status: nothing is read (and *used = false) when that entry point has not
+// run on this device yet.  Allocates nothing.
+int ib200::fixed_scratch_status(DeviceStatus* out, bool reset, bool* used) {
+  *used = false;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  if (dev < 0 || dev >= 64) return INFEROP_OK;
+  FixedScratch* ptr = fixed_scratch_cached(dev);
+  if (!ptr) return INFEROP_OK;
+  e = cudaMemcpy(out, &ptr->status, sizeof(DeviceStatus), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  if (reset) {
+    e = cudaMemset(&ptr->status, 0, sizeof(DeviceStatus));
+    if (e != cudaSuccess) return note_cuda_error(e);
+  }
+  *used = true;
+  return INFEROP_OK;
 }

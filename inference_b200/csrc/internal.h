@@ -22,7 +22,7 @@ struct DeviceCtx {
   DeviceStatus* status = nullptr;  // device memory, zero-initialised
   // Scratch of the small-M GEMM path, one set per stream that has used it (launches on one
   // stream run in order and may share a set; launches on different streams may overlap).
-  static constexpr int kMaxStreams = 16;
+  static constexpr int kMaxStreams = 64;
   int n_scratch = 0;
   cudaStream_t scratch_stream[kMaxStreams] = {};
   float* scratch_ws[kMaxStreams] = {};
@@ -39,6 +39,8 @@ struct Options {
   int decode_pdl = 1;      // small-M kernel: launch with programmatic stream serialisation
   int decode_splits = 0;   // 0 auto, else K parts per tile of the small-M kernel (capped by SMs / tiles)
   int gemm_path = 0;       // 0 auto, 1 always the large-tile kernel, 2 small-M kernel whenever M <= 128
+  int gemm_pair = -1;      // large-tile GEMM on CTA pairs (256 x 256 tiles): -1 auto, 0 never, 1 always
+  int gemm_pdl = 1;        // pair kernel: launch with programmatic stream serialisation
 };
 Options& options();
 bool decode_scratch(DeviceCtx* ctx, cudaStream_t stream, float** ws, int** counters);
@@ -56,6 +58,12 @@ int run_div_selftest(int is_bf16, uint64_t* out3, int sms);
 int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, const void* b_q,
                 const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
                 cudaStream_t stream);
+
+// gemm_pair_sm100.cu : the same GEMM on CTA pairs (tcgen05.mma.cta_group::2, 256 x 256 tiles)
+bool use_pair_kernel(int64_t m);
+int launch_gemm_pair(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, const void* b_q,
+                     const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
+                     cudaStream_t stream);
 
 // Grouped launch: group g has m_per_group[g] (host array) rows of A / C, stacked in group
 // order; b_q is [groups][n][k], b_scales [groups][n/128][k/128].
@@ -112,16 +120,21 @@ int launch_moe_combine(void* out, const void* y, const float* w, const int32_t* 
 constexpr int kDecodeMaxM = 128;
 constexpr int kDecodeMaxTiles = 1 << 16;
 size_t decode_workspace_bytes(int ctas);
+// clear_counters > 0: that many counters are zeroed on the stream after the call's last check.
 int launch_gemm_decode(DeviceCtx* ctx, float* workspace, int* counters, void* c, const void* a_q,
                        const void* a_scales, const void* b_q, const void* b_scales, int64_t m,
-                       int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream);
+                       int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream, int clear_counters = 0);
+// Bounded-wait record of the allocation-free entry point on the current device (if it has run).
+int fixed_scratch_status(DeviceStatus* out, bool reset, bool* used);
+// Context of the current device if one has been created already; never allocates.
+DeviceCtx* peek_ctx();
 
 // The same with the [m, n] result written to columns [col0, col0 + n) of n_dst (<= 8) row-major
 // buffers of row pitch ldc elements (host array `dst`; peer-mapped addresses allowed).
 int launch_gemm_decode_to(DeviceCtx* ctx, float* workspace, int* counters, void* const* dst, int n_dst,
                           int64_t ldc, int64_t col0, const void* a_q, const void* a_scales,
                           const void* b_q, const void* b_scales, int64_t m, int64_t n, int64_t k,
-                          int32_t out_dt, cudaStream_t stream);
+                          int32_t out_dt, cudaStream_t stream, int clear_counters = 0);
 
 // Fused prologue: `a` holds unquantised activations (a_dt 1 = fp16, 2 = bf16), M <= kFusedMaxM.
 constexpr int kFusedMaxM = 32;

@@ -101,14 +101,26 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // Each probe may park the thread for at most kProbeNs, so the clock and the
 // abort flag need reading only every few probes.
 constexpr unsigned int kProbeNs = 4000;
+#ifndef IB200_WAIT_MODE
+#define IB200_WAIT_MODE 0   // 0: parking probe with a time hint; 1: parking probe, default limit; 2: non-blocking probe
+#endif
+__device__ __forceinline__ bool mbar_probe(uint64_t* bar, uint32_t parity) {
+#if IB200_WAIT_MODE == 0
+  return mbar_try_wait_hint(bar, parity, kProbeNs);
+#elif IB200_WAIT_MODE == 1
+  return mbar_try_wait(bar, parity);
+#else
+  return mbar_test_wait(bar, parity);
+#endif
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile uint32_t* abort_flag, DeviceStatus* status,
                                           uint32_t site) {
-  if (mbar_try_wait_hint(bar, parity, kProbeNs)) return true;
+  if (mbar_probe(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t polls = 0;
   while (true) {
-    if (mbar_try_wait_hint(bar, parity, kProbeNs)) return true;
+    if (mbar_probe(bar, parity)) return true;
     if ((++polls & 15u) != 0u) continue;
     if (*abort_flag != 0u) return false;
     if (clock64() - t0 > kWaitBudgetCycles) {
@@ -292,6 +304,93 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
                : "memory");
+}
+
+// ------------------------------ CTA pairs (cta_group::2) -------------------
+// Two CTAs of one cluster (ranks 0 and 1) run one tcgen05.mma together: each supplies its
+// own half of the A rows and half of the B rows from its own shared memory and receives its
+// half of the accumulator rows in its own tensor memory.  Rank 0 (the leader) issues.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Every thread of every CTA of the cluster arrives and waits (release / acquire).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// Arrive on an mbarrier of any CTA of the cluster (address from mapa_shared).  Default
+// semantics (release at CTA scope): a cluster-scope release would first wait for every earlier
+// memory operation of the thread to become visible cluster-wide, which costs about a
+// microsecond per arrival; what the arrival orders here (tensor-memory reads) is fenced by
+// tcgen05.fence::before_thread_sync.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose byte count is credited to an mbarrier that
+// may live in the other CTA of the pair (bar_cluster_addr from mapa_shared).  No multicast:
+// every CTA fetches its own tile.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster_addr, int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+// Tensor-memory allocation for the pair: the same warp of both CTAs executes it, each with
+// its own shared-memory slot.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_slot)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B over the pair (M = 256: 128 rows per CTA); leader thread issues.
+__device__ __forceinline__ void umma_f8_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The barrier at this shared-memory offset in every CTA named by cta_mask gets one arrival
+// once all tcgen05.mma issued so far by this thread have finished.  (A commit is an mbarrier
+// arrival, not a load: nothing is fetched from any other CTA or GPU.)
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(cta_mask)
+      : "memory");
+}
+// barrier among `threads` threads that also ORs a predicate over them
+__device__ __forceinline__ bool named_bar_or(uint32_t id, uint32_t threads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %3, 0;\n\t"
+      "barrier.cta.red.or.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(threads), "r"(pred ? 1u : 0u)
+      : "memory");
+  return out != 0;
 }
 
 template <int N>

@@ -226,3 +226,31 @@ def test_operators_identical_to_reference():
     assert np.array_equal(oracle.bf16_narrow(x[:4, :64] * 1.001), R.bf16_narrow(x[:4, :64] * 1.001))
     gu = (3 * rng.standard_normal((40, 256))).astype(np.float32)
     assert np.array_equal(oracle.silu_and_mul(gu).view(np.uint32), R.silu_and_mul(gu).view(np.uint32))
+
+
+def test_sampled_checker_equals_the_full_oracle_on_the_sampled_entries():
+    """oracle/sampled.py gathers the sampled operand rows and calls the oracle with one scale row
+    per sampled column (block_n = 1): the same numbers as indexing the full golden result."""
+    import torch
+    from oracle import sampled
+    rng = np.random.default_rng(3)
+    m, n, k = 40, 700, 512
+    a = oracle.bf16_widen(oracle.bf16_narrow(rng.standard_normal((m, k)).astype(np.float32)))
+    w = oracle.bf16_widen(oracle.bf16_narrow((0.02 * rng.standard_normal((n, k))).astype(np.float32)))
+    aq, a_s = oracle.quant_fp8_per_token_group(a)
+    bq, bs = oracle.block_quant_weights(w)
+    full = oracle.w8a8_block_fp8_gemm(aq, a_s, bq, bs)
+    rows = sampled.band_rows(m, 6, seed=1, band=16)
+    cols = sampled.stratified(n, 37, seed=2)
+    assert rows[0] == 0 and rows[-1] == m - 1 and len(np.unique(cols)) == len(cols) and cols.max() < n
+    t = torch.from_numpy
+    row, fro = sampled.gemm_sample(t(aq), t(a_s), t(bq), t(bs), t(full), rows, cols, threads=2)
+    assert row == 0.0 and fro == 0.0
+    noisy = full.copy()
+    noisy[rows[1], cols[3]] *= 1.5
+    assert sampled.gemm_sample(t(aq), t(a_s), t(bq), t(bs), t(noisy), rows, cols)[0] > 0
+    x16 = t(oracle.bf16_narrow(a).view(np.int16)).view(torch.bfloat16)
+    assert sampled.quant_rows_exact(x16, t(aq), t(a_s), rows)
+    bad = aq.copy()
+    bad[rows[2], 7] ^= 1
+    assert not sampled.quant_rows_exact(x16, t(bad), t(a_s), rows)
