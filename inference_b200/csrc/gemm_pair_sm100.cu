@@ -32,31 +32,8 @@
 
 #include "internal.h"
 
-#ifndef IB200_PAIR_ABLATE
-#define IB200_PAIR_ABLATE 0   // experiments only: 1 no FMAs, 2 no tensor-memory loads either, 4 no TMA after the first ring
-#endif
-
-#ifndef IB200_TRACE
-#define IB200_TRACE 0
-#endif
-#if IB200_TRACE
-// experiments only: time stamps of pair 0's roles over its first K blocks
-__device__ unsigned long long g_trace[2][4][64][4][2];
-__device__ __forceinline__ void trace_at(uint32_t rank, int role, uint32_t it, int ev) {
-  if (it < 64u) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_trace[rank][role][it][ev][0] = t;
-    g_trace[rank][role][it][ev][1] = static_cast<unsigned long long>(clock64());
-  }
-}
-#define TRACE(cond, role, it, ev) do { if (cond) trace_at(rank, role, it, ev); } while (0)
-extern "C" __attribute__((visibility("default"))) int ib200_trace_read(void* host, size_t bytes) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, bytes < sizeof(g_trace) ? bytes : sizeof(g_trace)));
-}
-#else
-#define TRACE(cond, role, it, ev) do { } while (0)
-#endif
+#define IB200_TRACE_TAG pair
+#include "trace.cuh"
 
 namespace ib200 {
 namespace {
@@ -219,22 +196,12 @@ w8a8_pair_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             ok = false;
             break;
           }
-          TRACE(pair == 0, 0, static_cast<uint32_t>((t - pair) / num_pairs * p.kb + kb), 0);
+          TRACE(rank, pair == 0, 0, static_cast<uint32_t>((t - pair) / num_pairs * p.kb + kb), 0);
           uint8_t* sa = smem + stage * kStageBytes;
           const uint32_t leader_full = mapa_shared(smem_u32(&full[stage]), 0u);
           if (rank == 0) mbar_arrive_expect_tx(&full[stage], 2 * kStageBytes);
-#if (IB200_PAIR_ABLATE & 4)
-          if (t != pair || kb >= kStages) {
-            // stand-in for the loads: credit the bytes without moving them
-            asm volatile("mbarrier.complete_tx.relaxed.cluster.shared::cluster.b64 [%0], %1;" ::"r"(leader_full),
-                         "r"(kStageBytes)
-                         : "memory");
-          } else
-#endif
-          {
-            tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, a_row);
-            tma_load_2d_pair(sa + kBytesA, &map_b, leader_full, kb * BK, b_row);
-          }
+          tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, a_row);
+          tma_load_2d_pair(sa + kBytesA, &map_b, leader_full, kb * BK, b_row);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -266,9 +233,9 @@ w8a8_pair_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
         const uint32_t d_tmem = tmem_base + buf * PN;
         if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kSitePMmaFull)) break;
-        TRACE(pair == 0 && lane == 0, 1, it, 0);
+        TRACE(rank, pair == 0 && lane == 0, 1, it, 0);
         if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, kSitePMmaTmemEmpty)) break;
-        TRACE(pair == 0 && lane == 0, 1, it, 1);
+        TRACE(rank, pair == 0 && lane == 0, 1, it, 1);
         __syncwarp();
         tc_fence_after_sync();
         const uint32_t a_addr = smem_base + stage * kStageBytes;
@@ -283,7 +250,7 @@ w8a8_pair_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           umma_commit_pair(&empty[stage], 3);
         }
         __syncwarp();
-        TRACE(pair == 0 && lane == 0, 1, it, 2);
+        TRACE(rank, pair == 0 && lane == 0, 1, it, 2);
       }
     }
   } else {
@@ -327,33 +294,16 @@ w8a8_pair_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           ok = false;
           break;
         }
-        TRACE(pair == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 0);
+        TRACE(rank, pair == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 0);
         __syncwarp();
         tc_fence_after_sync();
         const uint32_t taddr = lane_base + buf * PN;
-#if (IB200_PAIR_ABLATE & 2)
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(leader_tmem_empty + buf * 8u);
-        acc[0].x += s;
-#else
         uint32_t v0[32], v1[32];
         tmem_ld_32x32(taddr, v0);
         tmem_ld_32x32(taddr + 32, v1);
         tmem_ld_wait_pin(v0);
         tmem_ld_wait_pin(v1);
-#if (IB200_PAIR_ABLATE & 1)
-        acc[0].x += __uint_as_float(v0[0]) * s + __uint_as_float(v1[0]);
-        tmem_ld_32x32(taddr + 64, v0);
-        tmem_ld_32x32(taddr + 96, v1);
-        tmem_ld_wait_pin(v0);
-        tmem_ld_wait_pin(v1);
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(leader_tmem_empty + buf * 8u);
-        acc[1].x += __uint_as_float(v0[0]) * s + __uint_as_float(v1[0]);
-#else
-        TRACE(pair == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 1);
+        TRACE(rank, pair == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 1);
         promote32(acc, v0, s);
         tmem_ld_32x32(taddr + 64, v0);
         promote32(acc + 16, v1, s);
@@ -363,12 +313,10 @@ w8a8_pair_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(leader_tmem_empty + buf * 8u);
-        TRACE(pair == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 2);
+        TRACE(rank, pair == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 2);
         promote32(acc + 32, v0, s);
         promote32(acc + 48, v1, s);
-        TRACE(pair == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 3);
-#endif
-#endif
+        TRACE(rank, pair == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 3);
       }
       // the four warps of a column half leave together or not at all
       if (named_bar_or(1 + half, 128, !ok)) break;

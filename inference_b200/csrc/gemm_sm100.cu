@@ -47,6 +47,9 @@
 
 #include "internal.h"
 
+#define IB200_TRACE_TAG single
+#include "trace.cuh"
+
 namespace ib200 {
 namespace {
 
@@ -361,7 +364,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
         const uint32_t d_tmem = tmem_base + buf * BN;
         // operands first (normally long there), then the accumulator buffer (the late one)
         if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kSiteMmaFull)) break;
+        TRACE(0, blockIdx.x == 0 && lane == 0, 1, it, 0);
         if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, kSiteMmaTmemEmpty)) break;
+        TRACE(0, blockIdx.x == 0 && lane == 0, 1, it, 1);
         __syncwarp();
         tc_fence_after_sync();
         const uint32_t a_addr = smem_base + stage * kStageBytes;
@@ -377,6 +382,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           umma_commit(&empty[stage]);
         }
         __syncwarp();
+        TRACE(0, blockIdx.x == 0 && lane == 0, 1, it, 2);
       }
     }
   } else {
@@ -390,8 +396,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
     uint8_t* my_buf = store_buf + half * kStoreBufBytes;
     const bool issuer = (quarter == 0 && lane == 0);
     uint32_t kiter = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      bool ok = true;
       const TileInfo ti = tile_info<kGrouped, BN>(t, p, tab);
       const int gm = ti.a_row + row;
       const int nbi = ti.sb_row + (half * CT) / 128;
@@ -422,6 +428,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           ok = false;
           break;
         }
+        TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 0);
         __syncwarp();
         tc_fence_after_sync();
         const uint32_t taddr = lane_base + buf * BN;
@@ -431,6 +438,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
         tmem_ld_wait_pin(v0);
         tmem_ld_wait_pin(v1);
         if constexpr (CT == 128) {
+          TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 1);
           promote32(acc, v0, s);
           tmem_ld_32x32(taddr + 64, v0);
           promote32(acc + 16, v1, s);
@@ -440,8 +448,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 2);
           promote32(acc + 32, v0, s);
           promote32(acc + 48, v1, s);
+          TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 3);
         } else {
           // 64 columns per thread: one round of loads, the buffer is free before the FMAs
           tc_fence_before_sync();
@@ -451,7 +461,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           promote32(acc + 16, v1, s);
         }
       }
-      if (!ok) break;
+      // A warp whose wait ran out must not leave its siblings alone at the named barriers of the
+      // epilogue: the four warps of a column half agree here, through a reducing barrier, whether
+      // the tile is abandoned, and leave together.
+      if (named_bar_or(1 + half, 128, !ok)) break;
 
       // ---- epilogue: this thread holds C[gm, col .. col + 128) in fp32
       if constexpr (kScatter) {
