@@ -85,6 +85,9 @@ def parse_args():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU-baseline sample budget")
     ap.add_argument("--moe-only", action="store_true",
                     help="run only the MoE section (grouped GEMMs and the expert layer) and print it")
+    ap.add_argument("--sweep-only", action="store_true", help="run only the decode / prefill shape sweep and print it")
+    ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE",
+                    help="library tuning option (inferop_set_option), e.g. --set gemm_pair=0; may be repeated")
     ap.add_argument("--moe-experts", type=int, default=256)
     ap.add_argument("--moe-tokens", type=int, default=4096)
     return ap.parse_args()
@@ -561,6 +564,9 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     assert ops.has_cuda() and ops.device_sm_version(local) == 100, "needs B200 (sm_100); no fallback"
+    for kv in args.set:
+        key, val = kv.split("=")
+        ops.set_option(key, int(val))
 
     m, n, k = args.m, args.n, args.k
     assert n % (128 * world) == 0, "N must split into 128-row blocks per rank"
@@ -875,9 +881,16 @@ def main():
     try:
         if args.impl == "reference":
             run_reference(args)
-        elif args.moe_only:
-            res = moe_config(measured_peaks(), experts=args.moe_experts, tokens=args.moe_tokens)
-            print_result(json.dumps({"moe": res}))
+        elif args.moe_only or args.sweep_only:
+            from inference_b200 import ops
+            for kv in args.set:
+                key, val = kv.split("=")
+                ops.set_option(key, int(val))
+            if args.moe_only:
+                res = moe_config(measured_peaks(), experts=args.moe_experts, tokens=args.moe_tokens)
+                print_result(json.dumps({"moe": res}))
+            else:
+                print_result(json.dumps({"sweep": shape_sweep(measured_peaks()), "options": args.set}))
         else:
             run_ours(args)
     finally:

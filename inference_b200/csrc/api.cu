@@ -511,21 +511,21 @@ int inferop_device_status(uint32_t* out4, int reset) {
   if (table().count <= 0) return INFEROP_ERR_NO_DEVICE;
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return note_cuda_error(e);
-  DeviceStatus host = {0, 0, 0, 0};
+  DeviceStatus host = {0, 0, 0, 0, 0};
   if (DeviceCtx* ctx = peek_ctx()) {
-    e = cudaMemcpy(&host, ctx->status, sizeof(host), cudaMemcpyDeviceToHost);
+    e = cudaMemcpy(&host, ctx->status, kStatusRecordBytes, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return note_cuda_error(e);
     if (reset) {
-      e = cudaMemset(ctx->status, 0, sizeof(DeviceStatus));
+      e = cudaMemset(ctx->status, 0, kStatusRecordBytes);   // the wait budget behind the record stays
       if (e != cudaSuccess) return note_cuda_error(e);
     }
   }
-  DeviceStatus fixed = {0, 0, 0, 0};
+  DeviceStatus fixed = {0, 0, 0, 0, 0};
   bool used = false;
   const int rc = fixed_scratch_status(&fixed, reset != 0, &used);
   if (rc != INFEROP_OK) return rc;
   if (host.code == 0 && used && fixed.code != 0) host = fixed;
-  if (out4) memcpy(out4, &host, sizeof(host));
+  if (out4) memcpy(out4, &host, kStatusRecordBytes);
   return host.code == 0 ? INFEROP_OK : INFEROP_ERR_DEVICE_WAIT;
 }
 
@@ -559,12 +559,27 @@ int inferop_set_option(const char* key, int64_t value) {
     o.gemm_group_m = static_cast<int>(value);
   } else if (!strcmp(key, "decode_pdl")) {
     o.decode_pdl = value != 0;
+  } else if (!strcmp(key, "decode_deal")) {
+    if (value < 0 || value > 1) return INFEROP_ERR_SHAPE;
+    o.decode_deal = static_cast<int>(value);
   } else if (!strcmp(key, "decode_splits")) {
     if (value < 0 || value > 1024) return INFEROP_ERR_SHAPE;
     o.decode_splits = static_cast<int>(value);
   } else if (!strcmp(key, "gemm_path")) {
     if (value < 0 || value > 2) return INFEROP_ERR_SHAPE;
     o.gemm_path = static_cast<int>(value);
+  } else if (!strcmp(key, "debug_no_loads")) {
+    o.debug_no_loads = value != 0;
+  } else if (!strcmp(key, "wait_budget_us")) {
+    // how long a wait inside a kernel may last before it gives up (0 = the default, about a second);
+    // stored beside the status record of the current device
+    if (value < 0 || value > 10000000) return INFEROP_ERR_SHAPE;
+    int err;
+    DeviceCtx* ctx = current_ctx(&err);
+    if (!ctx) return err;
+    const unsigned long long cycles = static_cast<unsigned long long>(value) * 2000ull;   // at about 2 GHz
+    const cudaError_t e = cudaMemcpy(&ctx->status->budget_cycles, &cycles, sizeof(cycles), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return note_cuda_error(e);
   } else if (!strcmp(key, "gemm_pair")) {
     if (value < -1 || value > 1) return INFEROP_ERR_SHAPE;
     o.gemm_pair = static_cast<int>(value);

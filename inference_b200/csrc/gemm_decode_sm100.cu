@@ -69,11 +69,12 @@ struct DecodeParams {
   // all-gather form lists every rank's buffer (peer-mapped addresses, plain stores).
   void* dst[8];
   int n_dst, ldc, col0;
-  float* workspace;        // [gridDim.x][MP][128] fp32 partials
-  int splits;              // K parts per tile (1 = whole tiles, CTAs take runs of tiles)
+  float* workspace;        // [gridDim.x][2][MP][128] fp32 partials (slot 0: the CTA's first tile, slot 1: its last)
+  int splits;              // 0: units dealt evenly (below); else K parts per tile (1 = runs of whole tiles)
   int* counters;           // [n_tiles], zero between launches
   int m, n, kb, n_tiles;
   long long units;         // n_tiles * kb
+  int no_loads;            // test hook: the producer issues no load
   DeviceStatus* status;
 };
 
@@ -204,10 +205,20 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_slot, 0);
 
-  // this CTA's piece: tiles [t_first, ...) from K block kb_first, `count` units in all
+  // This CTA's piece: tiles [t_first, ...) from K block kb_first, `count` units in all.  A unit
+  // is one (weight tile, K block) pair = 16 KiB of weights.  Default: the n_tiles * kb units are
+  // dealt evenly, CTA c takes units [c U / G, (c + 1) U / G), so every SM streams the same number
+  // of bytes whatever the tile count; a piece may start and end inside a tile, and the K parts of
+  // a tile are then added in CTA order by the last CTA to finish (deterministic).
   int t_first, kb_first;
   uint32_t count;
-  if (p.splits == 1) {
+  if (p.splits == 0) {
+    const long long g = gridDim.x, c = blockIdx.x;
+    const long long u0 = c * p.units / g, u1 = (c + 1) * p.units / g;
+    t_first = static_cast<int>(u0 / p.kb);
+    kb_first = static_cast<int>(u0 - static_cast<long long>(t_first) * p.kb);
+    count = static_cast<uint32_t>(u1 - u0);
+  } else if (p.splits == 1) {
     const long long g = gridDim.x, c = blockIdx.x;
     t_first = static_cast<int>(c * p.n_tiles / g);
     kb_first = 0;
@@ -229,7 +240,9 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     uint32_t armed = 0;
     bool ok = true;
     const uint32_t head = count < static_cast<uint32_t>(C::kStages) ? count : static_cast<uint32_t>(C::kStages);
-    if (!kFused) {
+    if (p.no_loads) {
+      // test hook: nothing is ever loaded, so every other role's wait runs out
+    } else if (!kFused) {
       int th = t, kh = kb;
       for (uint32_t i = 0; i < head; ++i) {
         uint8_t* dst = smem + i * C::kStageBytes;
@@ -257,7 +270,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     } else {
       pdl_wait();
     }
-    for (uint32_t i = (kFused ? 0u : head); i < count; ++i) {
+    for (uint32_t i = (kFused ? 0u : head); i < count && !p.no_loads; ++i) {
       const uint32_t stage = i % C::kStages;
       const uint32_t phase = (i / C::kStages) & 1u;
       if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteDProducerEmpty)) {
@@ -425,64 +438,80 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     pdl_wait();   // the output, workspace and counters may still be in use by the preceding kernel
     int t = t_first, kb = kb_first, seg_kb0 = kb_first;
     bool ok = true;
-    for (uint32_t i = 0; ok && i < count; ++i) {
+    for (uint32_t i = 0; i < count; ++i) {
       const uint32_t buf = i % C::kBufs;
       const uint32_t par = (i / C::kBufs) & 1u;
-      if (!mbar_wait(&tmem_full[buf], par, abort_flag, p.status, kSiteDPromoFull) ||
-          !mbar_wait(&sv_full[buf], par, abort_flag, p.status, kSiteDPromoScale)) {
+      // a warp whose wait ran out skips the work of the remaining units of its segment (without
+      // waiting) and meets its siblings at the segment's end, where the four warps agree to leave
+      if (ok && (!mbar_wait(&tmem_full[buf], par, abort_flag, p.status, kSiteDPromoFull) ||
+                 !mbar_wait(&sv_full[buf], par, abort_flag, p.status, kSiteDPromoScale))) {
         ok = false;
-        break;
       }
-      __syncwarp();
-      tc_fence_after_sync();
-      const float4* svb = reinterpret_cast<const float4*>(sv + buf * MP);
-      // all loads of up to 64 columns are issued before the single wait, so that their
-      // latencies overlap; 128 columns go in two such halves (register budget)
-      constexpr int HALF = (MP < 64) ? MP : 64;
+      if (ok) {
+        __syncwarp();
+        tc_fence_after_sync();
+        const float4* svb = reinterpret_cast<const float4*>(sv + buf * MP);
+        // all loads of up to 64 columns are issued before the single wait, so that their
+        // latencies overlap; 128 columns go in two such halves (register budget)
+        constexpr int HALF = (MP < 64) ? MP : 64;
 #pragma unroll
-      for (int h0 = 0; h0 < MP; h0 += HALF) {
-        uint32_t v[HALF / CH][CH];
+        for (int h0 = 0; h0 < MP; h0 += HALF) {
+          uint32_t v[HALF / CH][CH];
 #pragma unroll
-        for (int q = 0; q < HALF / CH; ++q) tmem_ld_cols<CH>(lane_base + buf * MP + h0 + q * CH, v[q]);
-        tmem_ld_wait();
+          for (int q = 0; q < HALF / CH; ++q) tmem_ld_cols<CH>(lane_base + buf * MP + h0 + q * CH, v[q]);
+          tmem_ld_wait();
 #pragma unroll
-        for (int q = 0; q < HALF / CH; ++q) {
+          for (int q = 0; q < HALF / CH; ++q) {
 #pragma unroll
-          for (int j = 0; j < CH; ++j) asm volatile("" : "+r"(v[q][j])::"memory");
-        }
+            for (int j = 0; j < CH; ++j) asm volatile("" : "+r"(v[q][j])::"memory");
+          }
 #pragma unroll
-        for (int q = 0; q < HALF / CH; ++q) {
+          for (int q = 0; q < HALF / CH; ++q) {
 #pragma unroll
-          for (int j = 0; j < CH; j += 4) {
-            const int c = h0 + q * CH + j;
-            const float4 s4 = svb[c >> 2];
-            acc[c + 0] = fmaf(__uint_as_float(v[q][j + 0]), s4.x, acc[c + 0]);
-            acc[c + 1] = fmaf(__uint_as_float(v[q][j + 1]), s4.y, acc[c + 1]);
-            acc[c + 2] = fmaf(__uint_as_float(v[q][j + 2]), s4.z, acc[c + 2]);
-            acc[c + 3] = fmaf(__uint_as_float(v[q][j + 3]), s4.w, acc[c + 3]);
+            for (int j = 0; j < CH; j += 4) {
+              const int c = h0 + q * CH + j;
+              const float4 s4 = svb[c >> 2];
+              acc[c + 0] = fmaf(__uint_as_float(v[q][j + 0]), s4.x, acc[c + 0]);
+              acc[c + 1] = fmaf(__uint_as_float(v[q][j + 1]), s4.y, acc[c + 1]);
+              acc[c + 2] = fmaf(__uint_as_float(v[q][j + 2]), s4.z, acc[c + 2]);
+              acc[c + 3] = fmaf(__uint_as_float(v[q][j + 3]), s4.w, acc[c + 3]);
+            }
           }
         }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
 
       const bool seg_end = (kb == p.kb - 1) || (i + 1 == count);
       if (seg_end) {
+        if (named_bar_or(2, 128, !ok)) break;   // agreed: the piece is abandoned, nobody waits at the barriers below
         const int gn = t * TN + row;
         const bool whole = (seg_kb0 == 0 && kb == p.kb - 1);
         if (whole) {
           if (gn < p.n) store_column<MP, OutT>(p, gn, acc);
         } else {
-          // one K part of a split tile: this CTA's slot of the workspace
-          float* wp = p.workspace + static_cast<int64_t>(blockIdx.x) * (MP * TN);
+          // one K part of a split tile: a slot of this CTA in the workspace (slot 0 for the tile
+          // the piece starts in, slot 1 for the tile it ends in)
+          const int64_t my_slot = p.splits == 0 ? static_cast<int64_t>(blockIdx.x) * 2 + (t == t_first ? 0 : 1)
+                                                : static_cast<int64_t>(blockIdx.x);
+          float* wp = p.workspace + my_slot * (MP * TN);
 #pragma unroll
           for (int m = 0; m < MP; ++m) __stcg(wp + m * TN + row, acc[m]);
           __threadfence();
+          // which CTAs hold parts of tile t: with even dealing, the CTA that owns unit u is
+          // ceil((u + 1) G / U) - 1
+          int c_lo = 0, c_hi = 0;
+          if (p.splits == 0) {
+            const long long g = gridDim.x;
+            c_lo = static_cast<int>(((static_cast<long long>(t) * p.kb + 1) * g + p.units - 1) / p.units) - 1;
+            c_hi = static_cast<int>(((static_cast<long long>(t + 1) * p.kb) * g + p.units - 1) / p.units) - 1;
+          }
+          const int parts = p.splits == 0 ? c_hi - c_lo + 1 : p.splits;
           named_bar_sync(1, 128);
           if (ct == 0) {
             const int prev = atomicAdd(p.counters + t, 1);
-            *last_flag = (prev == p.splits - 1) ? 1u : 0u;
+            *last_flag = (prev == parts - 1) ? 1u : 0u;
           }
           named_bar_sync(1, 128);
           if (*last_flag != 0u) {
@@ -490,8 +519,16 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             float sum[MP];
 #pragma unroll
             for (int m = 0; m < MP; ++m) sum[m] = 0.0f;
-            for (int part = 0; part < p.splits; ++part) {   // fixed order: the result does not depend on arrival order
-              const float* rp = p.workspace + (static_cast<int64_t>(t) * p.splits + part) * (MP * TN);
+            for (int part = 0; part < parts; ++part) {   // fixed order: the result does not depend on arrival order
+              int64_t slot;
+              if (p.splits == 0) {
+                const long long c2 = c_lo + part;
+                const int tf = static_cast<int>((c2 * p.units / gridDim.x) / p.kb);   // the tile CTA c2 starts in
+                slot = c2 * 2 + (tf == t ? 0 : 1);
+              } else {
+                slot = static_cast<int64_t>(t) * p.splits + part;
+              }
+              const float* rp = p.workspace + slot * (MP * TN);
 #pragma unroll
               for (int m = 0; m < MP; ++m) sum[m] += __ldcg(rp + m * TN + row);
             }
@@ -577,7 +614,7 @@ int launch_decode_mp(int mp, const CUtensorMap& mw, const CUtensorMap& ma, const
 
 }  // namespace
 
-size_t decode_workspace_bytes(int ctas) { return static_cast<size_t>(ctas) * kDecodeMaxM * TN * 4; }
+size_t decode_workspace_bytes(int ctas) { return static_cast<size_t>(ctas) * 2 * kDecodeMaxM * TN * 4; }
 
 int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, void* c, const void* a,
                              int32_t a_dt, const void* b_q, const void* b_scales, int64_t m, int64_t n,
@@ -598,6 +635,7 @@ int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, vo
   p.kb = static_cast<int>(k / 128);
   p.n_tiles = static_cast<int>((n + TN - 1) / TN);
   p.units = static_cast<long long>(p.n_tiles) * p.kb;
+  p.no_loads = options().debug_no_loads;
   p.status = ctx->status;
   CUtensorMap mw;
   const int rc = make_tensor_map_2d(&mw, b_q, 1, n, k, k, TN, BK, true);
@@ -606,7 +644,11 @@ int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, vo
   int max_ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
   if (max_ctas > ctx->sm_count) max_ctas = ctx->sm_count;
   int ctas;
-  if (p.n_tiles >= max_ctas) {
+  if (opt.decode_deal == 0) {
+    // every (tile, K block) unit dealt evenly over one CTA per SM
+    p.splits = 0;
+    ctas = p.units < max_ctas ? static_cast<int>(p.units) : max_ctas;
+  } else if (p.n_tiles >= max_ctas) {
     p.splits = 1;
     ctas = max_ctas;
   } else {
@@ -649,6 +691,7 @@ int launch_gemm_decode_to(DeviceCtx* ctx, float* workspace, int* counters, void*
   p.kb = static_cast<int>(k / 128);
   p.n_tiles = static_cast<int>((n + TN - 1) / TN);
   p.units = static_cast<long long>(p.n_tiles) * p.kb;
+  p.no_loads = options().debug_no_loads;
   p.status = ctx->status;
 
   CUtensorMap mw, ma;
@@ -666,7 +709,11 @@ int launch_gemm_decode_to(DeviceCtx* ctx, float* workspace, int* counters, void*
   int max_ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
   if (max_ctas > ctx->sm_count) max_ctas = ctx->sm_count;   // the workspace is sized for one CTA per SM
   int ctas;
-  if (p.n_tiles >= max_ctas) {
+  if (opt.decode_deal == 0) {
+    // every (tile, K block) unit dealt evenly over one CTA per SM
+    p.splits = 0;
+    ctas = p.units < max_ctas ? static_cast<int>(p.units) : max_ctas;
+  } else if (p.n_tiles >= max_ctas) {
     p.splits = 1;
     ctas = max_ctas;
   } else {
@@ -693,7 +740,7 @@ int launch_gemm_decode_to(DeviceCtx* ctx, float* workspace, int* counters, void*
 // left for the driver to give out, and a latency-critical loop cannot afford an allocation
 // call that may take driver locks or synchronise the device.  For them the split-tile scratch
 // of the small-M kernel lives in a fixed array inside the library image instead of in memory
-// obtained at run time.  Every GPU that loads the library carries the array (about 2.6 MB)
+// obtained at run time.  Every GPU that loads the library carries the array (about 5.3 MB)
 // until the process exits, which is why it is kept small: M <= 32 tokens, at most 4096 weight
 // tiles (N <= 524288) and at most 160 SMs.
 // ---------------------------------------------------------------------------
@@ -705,7 +752,7 @@ constexpr int kFixedMaxCtas = 160;
 constexpr int kFixedMaxTiles = 4096;
 
 struct FixedScratch {
-  float partials[kFixedMaxCtas * kFixedMaxM * TN];  // one K part of a split tile per CTA
+  float partials[kFixedMaxCtas * 2 * kFixedMaxM * TN];  // two K parts of split tiles per CTA
   int counters[kFixedMaxTiles];                     // arrivals per tile; zero between launches
   DeviceStatus status;                              // bounded-wait record of this entry point
 };
@@ -806,10 +853,10 @@ int ib200::fixed_scratch_status(DeviceStatus* out, bool reset, bool* used) {
   if (dev < 0 || dev >= 64) return INFEROP_OK;
   FixedScratch* ptr = fixed_scratch_cached(dev);
   if (!ptr) return INFEROP_OK;
-  e = cudaMemcpy(out, &ptr->status, sizeof(DeviceStatus), cudaMemcpyDeviceToHost);
+  e = cudaMemcpy(out, &ptr->status, kStatusRecordBytes, cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) return note_cuda_error(e);
   if (reset) {
-    e = cudaMemset(&ptr->status, 0, sizeof(DeviceStatus));
+    e = cudaMemset(&ptr->status, 0, kStatusRecordBytes);
     if (e != cudaSuccess) return note_cuda_error(e);
   }
   *used = true;

@@ -63,6 +63,7 @@ struct PairParams {
   int tiles_m, tiles_n, num_tiles;   // tiles of 256 x 256
   int group_m;                       // M-tiles per rasterisation band
   int tma_store;
+  int no_loads;   // test hook: the producers issue no load
   DeviceStatus* status;
 };
 
@@ -186,7 +187,7 @@ w8a8_pair_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; ok && t < p.num_tiles; t += num_pairs) {
+      for (int t = pair; ok && !p.no_loads && t < p.num_tiles; t += num_pairs) {
         int row0, col0;
         tile_origin(t, p, row0, col0);
         const int a_row = row0 + static_cast<int>(rank) * PM;
@@ -439,6 +440,7 @@ int launch_gemm_pair(DeviceCtx* ctx, void* c, const void* a_q, const void* a_sca
   p.tma_store = tma_store ? 1 : 0;
   // bands of 4096 rows like the single-CTA kernel (option gemm_group_m counts 128-row tiles)
   p.group_m = opt.gemm_group_m > 0 ? (opt.gemm_group_m + 1) / 2 : 16;
+  p.no_loads = opt.debug_no_loads;
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;

@@ -90,6 +90,7 @@ struct GemmParams {
   int tiles_m, tiles_n, num_tiles;
   int group_m;   // M-tiles per rasterisation band: a band's A panel stays in L2 while W streams past once
   int tma_store; // 1: epilogue goes through shared memory + TMA store
+  int no_loads;  // test hook: the producer issues no load
   DeviceStatus* status;
 };
 
@@ -305,7 +306,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       uint32_t phase = 0;
       uint32_t armed = 0, armed_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+      for (int t = blockIdx.x; ok && !p.no_loads && t < num_tiles; t += gridDim.x) {
         const TileInfo ti = tile_info<kGrouped, BN>(t, p, tab);
         for (int kb = 0; kb < p.kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty)) {
@@ -331,7 +332,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           const uint32_t par = (armed_phase >> s) & 1u;
           const long long t0 = clock64();
           while (!mbar_test_wait(&full[s], par)) {
-            if (clock64() - t0 > kWaitBudgetCycles) {
+            if (clock64() - t0 > wait_budget(p.status)) {
               atomicCAS(&p.status->code, 0u, kSiteProducerDrain);
               break;
             }
@@ -726,6 +727,7 @@ int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, 
   p.num_tiles = static_cast<int>(tiles);
   p.tma_store = tma_store ? 1 : 0;
   p.group_m = opt.gemm_group_m > 0 ? opt.gemm_group_m : 32;
+  p.no_loads = opt.debug_no_loads;
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;
@@ -780,6 +782,7 @@ int launch_gemm_grouped(DeviceCtx* ctx, void* c, const void* a_q, const void* a_
   p.tiles_n = static_cast<int>((n + BN - 1) / BN);
   p.tma_store = tma_store ? 1 : 0;
   p.group_m = 32;
+  p.no_loads = opt.debug_no_loads;
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;
@@ -862,6 +865,7 @@ int launch_gemm_allgather(DeviceCtx* ctx, void* const* c_peers, int32_t n_peers,
   p.num_tiles = static_cast<int>(tiles);
   p.tma_store = 1;
   p.group_m = opt.gemm_group_m > 0 ? opt.gemm_group_m : 32;
+  p.no_loads = opt.debug_no_loads;
   p.status = ctx->status;
 
   CUtensorMap ma, mb;
@@ -911,6 +915,7 @@ int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void
   p.num_tiles = static_cast<int>(tiles);
   p.tma_store = tma_store ? 1 : 0;
   p.group_m = 32;
+  p.no_loads = opt.debug_no_loads;
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;
@@ -964,6 +969,7 @@ int launch_gemm_scatter(DeviceCtx* ctx, void* const* slot_peers, int32_t n_peers
   p.num_tiles = static_cast<int>(tiles);
   p.tma_store = 1;
   p.group_m = opt.gemm_group_m > 0 ? opt.gemm_group_m : 32;
+  p.no_loads = opt.debug_no_loads;
   p.status = ctx->status;
 
   CUtensorMap ma, mb;

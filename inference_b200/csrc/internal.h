@@ -37,10 +37,12 @@ struct Options {
   int gemm_ctas = 0;       // 0 = one per SM
   int gemm_group_m = 0;    // M-tiles per rasterisation band of the large-tile kernel (0 = default 32)
   int decode_pdl = 1;      // small-M kernel: launch with programmatic stream serialisation
-  int decode_splits = 0;   // 0 auto, else K parts per tile of the small-M kernel (capped by SMs / tiles)
+  int decode_deal = 1;     // small-M kernel: 1 whole tiles / equal K parts per CTA (default); 0 (tile, K block) units dealt evenly
+  int decode_splits = 0;   // with decode_deal 1: 0 auto, else K parts per tile (capped by SMs / tiles)
   int gemm_path = 0;       // 0 auto, 1 always the large-tile kernel, 2 small-M kernel whenever M <= 128
   int gemm_pair = -1;      // large-tile GEMM on CTA pairs (256 x 256 tiles): -1 auto, 0 never, 1 always
   int gemm_pdl = 1;        // pair kernel: launch with programmatic stream serialisation
+  int debug_no_loads = 0;  // test hook: the TMA producers of the GEMM kernels issue no load (every wait runs out)
 };
 Options& options();
 bool decode_scratch(DeviceCtx* ctx, cudaStream_t stream, float** ws, int** counters);

@@ -19,9 +19,18 @@ struct DeviceStatus {
   unsigned int block;  // blockIdx.x of the first CTA that gave up
   unsigned int aux0;
   unsigned int aux1;
+  // set by the host (option wait_budget_us): cycles a wait may last before it gives up; 0 = default
+  unsigned long long budget_cycles;
 };
 
+constexpr int kStatusRecordBytes = 16;   // code, block, aux0, aux1: what inferop_device_status reports and resets
 constexpr long long kWaitBudgetCycles = 1LL << 31;  // about a second at the SM's top clock
+
+// the budget of a wait: read only on the slow path, after the first probes have failed
+__device__ __forceinline__ long long wait_budget(const DeviceStatus* status) {
+  const unsigned long long b = *reinterpret_cast<const volatile unsigned long long*>(&status->budget_cycles);
+  return b != 0ull ? static_cast<long long>(b) : kWaitBudgetCycles;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -116,7 +125,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     if (mbar_probe(bar, parity)) return true;
     if ((++polls & 15u) != 0u) continue;
     if (*abort_flag != 0u) return false;
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    if (clock64() - t0 > wait_budget(status)) {
       *abort_flag = 1u;
       if (atomicCAS(&status->code, 0u, site) == 0u) {
         status->block = blockIdx.x;
