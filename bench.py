@@ -639,7 +639,8 @@ def run_ours(args):
         from inference_b200.host import HostLinearFP8
         x_host = x.cpu().pin_memory()
         c_host = torch.empty((m, n_loc), dtype=torch.bfloat16).pin_memory()
-        lin = HostLinearFP8(bq, bs, max_rows=m, panel_rows=2048)   # the public host-buffer call
+        lin = HostLinearFP8(bq, bs, max_rows=m, panel_rows=2048,   # the public host-buffer call
+                            group=dist.group.WORLD if world > 1 else None)
 
         for _ in range(2):
             lin(x_host, c_host)
@@ -652,9 +653,14 @@ def run_ours(args):
         h1.record(stream)
         torch.cuda.synchronize()
         te = max_over_ranks(h0.elapsed_time(h1) * 1e-3 / n_e2e)
-        e2e = {"value": flops_total / te / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2,
-               "d2h_bytes_per_step": c_host.numel() * 2, "ms_per_step": te * 1e3, "steps": n_e2e,
-               "api": "inference_b200.host.HostLinearFP8: 2048-row panels, copy-in / quant+GEMM / copy-out on three streams"}
+        # parity of the end-to-end result (host buffer) on this rank's shard
+        e2e_par = parity_gate(None, aq, a_s, bq, bs, c_host.to(dev), seed=23 + rank, rows_per_band=4, n_cols=128)
+        e2e = {"value": flops_total / te / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": x_host.numel() * 2 // world, "d2h_bytes_per_step": c_host.numel() * 2,
+               "bytes_are": "per rank (every rank uploads 1/G of the activation rows and reads back its [M, N/G] result)",
+               "ms_per_step": te * 1e3, "steps": n_e2e, "parity": {"row": e2e_par["row"], "fro": e2e_par["fro"], "ok": True},
+               "api": "inference_b200.host.HostLinearFP8: 2048-row panels, copy-in / quant (+ all-gather of the FP8 rows "
+                      "at N > 1) + GEMM / copy-out on three streams"}
         del x_host, c_host, lin
 
     peaks = measured_peaks()

@@ -124,3 +124,37 @@ def test_k_shard_and_owner_bounds():
         shard.k_shard_bounds(384, 2, 0)
     with pytest.raises(ValueError):
         shard.owner_rows(384, 2, 0)
+
+
+# ------------------------------------------------------------------ row-split upload of the host front end
+def _rows_worker(rank, world, port, rows, k, out_dir):
+    """What inference_b200.host.HostLinearFP8 does with a panel at N > 1: every rank quantises its
+    rank_rows chunk, the ranks all-gather bytes and scales; the result must equal quantising the
+    whole panel in one place."""
+    from inference_b200 import host
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rng = np.random.default_rng(7)                       # the same host activations on every rank
+    x = oracle.bf16_widen(oracle.bf16_narrow(rng.standard_normal((rows, k)).astype(np.float32)))
+    lo, hi = host.rank_rows(rows, world, rank)
+    q_part, s_part = (torch.from_numpy(t) for t in oracle.quant_fp8_per_token_group(x[lo:hi]))
+    q = torch.empty((rows, k), dtype=torch.uint8)
+    s = torch.empty((rows, k // 128), dtype=torch.float32)
+    dist.all_gather_into_tensor(q, q_part)
+    dist.all_gather_into_tensor(s, s_part)
+    want_q, want_s = oracle.quant_fp8_per_token_group(x)
+    np.save(os.path.join(out_dir, f"rows{rank}.npy"),
+            np.array([np.array_equal(q.numpy(), want_q), np.array_equal(s.numpy(), want_s)]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_row_split_quantisation_all_gathers_to_the_whole_panel(tmp_path):
+    from inference_b200 import host
+    assert host.rank_rows(2048, 8, 3) == (768, 1024)
+    with pytest.raises(ValueError):
+        host.rank_rows(100, 8, 0)
+    world, rows, k = 2, 64, 512
+    mp.spawn(_rows_worker, args=(world, _free_port(), rows, k, str(tmp_path)), nprocs=world, join=True)
+    assert all(np.load(tmp_path / f"rows{r}.npy").all() for r in range(world))
