@@ -402,8 +402,9 @@ def moe_config(peaks, experts=256, hidden=7168, inter=2048, tokens=4096, topk=8)
 
 
 def moe_layer(peaks, experts, hidden, inter, tokens, topk, logits, x):
-    """The whole expert layer as seven launches with no host step (routing -> layout ->
-    scatter-quantise -> gate_up -> SwiGLU + quantise -> down -> combine): per-kernel device times
+    """The whole expert layer as six launches with no host step (routing -> layout ->
+    scatter-quantise -> gate_up with SwiGLU + quantisation in its epilogue -> down -> combine),
+    beside the seven-launch form with a separate SwiGLU kernel: per-kernel device times
     and, for the HBM-bound ones, achieved bandwidth against the measured copy rate."""
     import torch
     from inference_b200 import ops, synth
@@ -430,11 +431,9 @@ def moe_layer(peaks, experts, hidden, inter, tokens, topk, logits, x):
         ("moe_align", lambda: ops.moe_align(layer.ids, experts, lay), None),
         ("moe_scatter_quant", lambda: ops.moe_scatter_quant(x, lay, layer.xq, layer.xs),
          2 * tokens * hidden + pairs * hidden * (1 + 4 / 128)),
-        ("gate_up_gemm", lambda: ops.w8a8_block_fp8_gemm_grouped_tiles(layer.xq, layer.xs, wgu, sgu, lay,
-                                                                        out=layer.gate_up),
-         experts * 2 * inter * hidden + pairs * hidden + 2 * pairs * 2 * inter),
-        ("silu_and_mul_quant", lambda: ops.silu_and_mul_quant(layer.gate_up, layer.hq, layer.hs),
-         2 * pairs * 2 * inter + pairs * inter * (1 + 4 / 128)),
+        ("gate_up_gemm_swiglu_quant", lambda: ops.w8a8_block_fp8_gemm_grouped_tiles_swiglu(
+            layer.xq, layer.xs, wgu, sgu, lay, torch.bfloat16, layer.hq, layer.hs),
+         experts * 2 * inter * hidden + pairs * hidden + pairs * inter * (1 + 4 / 128)),
         ("down_gemm", lambda: ops.w8a8_block_fp8_gemm_grouped_tiles(layer.hq, layer.hs, wd, sd, lay, out=layer.y),
          experts * hidden * inter + pairs * inter + 2 * pairs * hidden),
         ("moe_combine", lambda: ops.moe_combine(layer.y, layer.weights, lay, out),
@@ -469,6 +468,17 @@ def moe_layer(peaks, experts, hidden, inter, tokens, topk, logits, x):
     flops = 2.0 * pairs * hidden * (2 * inter) + 2.0 * pairs * inter * hidden
     res.update({"layer_ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1), "launches": len(steps),
                 "host_synchronisations": 0})
+    # the same layer with the separate SwiGLU + quantisation kernel (bit-identical output)
+    out7 = torch.empty_like(out)
+    layer7 = MoEFP8Layer(wgu, sgu, wd, sd, topk, tokens, fused_swiglu=False)
+    for _ in range(2):
+        layer7.forward(x, logits, out7)
+    e0_.record()
+    for _ in range(iters):
+        layer7.forward(x, logits, out7)
+    e1_.record()
+    torch.cuda.synchronize()
+    res["seven_launch_form"] = {"layer_ms": round(e0_.elapsed_time(e1_) / iters, 3), "same_bits": bool(torch.equal(out, out7))}
     assert ops.device_status()[0] == 0
     return res
 

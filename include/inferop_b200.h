@@ -230,6 +230,25 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm_grouped_tiles(void* c, const void* a
                                               int32_t group_size, int32_t block_n, int32_t out_dt,
                                               void* stream);
 
+/* The gate_up projection of an expert layer with SwiGLU and the 1x128 re-quantisation done in the
+ * GEMM's epilogue: replaces inferop_w8a8_block_fp8_gemm_grouped_tiles (gate_up) followed by
+ * inferop_silu_and_mul_quant, i.e. the reference's w8a8_block_fp8_gemm + silu_and_mul +
+ * quant_fp8_per_token_group chain (include/inferop/ops.h:81-84, :54-55, :64-65;
+ * kernels/silu_mul.cu:16-28), and produces the same bytes and scales bit for bit.
+ *   b_q [groups][2 * inter][k] with the gate rows first and the up rows second (the layout
+ *   silu_and_mul expects of the GEMM's output columns), b_scales [groups][2 * inter / 128][k / 128];
+ *   q [m_total, inter] E4M3, q_scales [m_total, inter / 128] fp32;
+ *   mid_dt (1 fp16 / 2 bf16): the 16-bit type the two-kernel chain would have stored gate_up in
+ *   (both the GEMM result and the SwiGLU result are rounded to it before the quantisation).
+ * inter % 128 == 0; q 16-byte aligned.  The 16-bit gate_up matrix is never written. */
+INFEROP_API int inferop_w8a8_block_fp8_gemm_grouped_tiles_swiglu(void* q, void* q_scales, const void* a_q,
+                                                     const void* a_scales, const void* b_q,
+                                                     const void* b_scales, const int32_t* tile_row0,
+                                                     const int32_t* tile_meta, const int32_t* num_mtiles,
+                                                     int64_t max_mtiles, int64_t m_total, int64_t groups,
+                                                     int64_t inter, int64_t k, int32_t group_size,
+                                                     int32_t block_n, int32_t mid_dt, void* stream);
+
 /* ---- blockwise-FP8 GEMM for a few tokens, with no allocation
  * No counterpart in the reference: added for callers that must not trigger a device
  * allocation, such as a server that gave all device memory to its own pool at start-up, or a

@@ -44,6 +44,8 @@ SIGNATURES = {
     "inferop_moe_combine": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i64, _i64, _i32, _vp]),
     "inferop_w8a8_block_fp8_gemm_grouped_tiles": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                                             _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
+    "inferop_w8a8_block_fp8_gemm_grouped_tiles_swiglu": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                                                                   _i64, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "inferop_w8a8_block_fp8_gemm_fixed_scratch": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
                                                             _i32, _i32, _i32, _vp]),
     "inferop_device_status": (C.c_int, [C.POINTER(C.c_uint32), C.c_int]),

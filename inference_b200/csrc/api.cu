@@ -504,6 +504,36 @@ int inferop_w8a8_block_fp8_gemm_grouped_tiles(void* c, const void* a_q, const vo
                                  max_mtiles, m_total, groups, n, k, out_dt, static_cast<cudaStream_t>(stream));
 }
 
+int inferop_w8a8_block_fp8_gemm_grouped_tiles_swiglu(void* q, void* q_scales, const void* a_q,
+                                                     const void* a_scales, const void* b_q,
+                                                     const void* b_scales, const int32_t* tile_row0,
+                                                     const int32_t* tile_meta, const int32_t* num_mtiles,
+                                                     int64_t max_mtiles, int64_t m_total, int64_t groups,
+                                                     int64_t inter, int64_t k, int32_t group_size,
+                                                     int32_t block_n, int32_t mid_dt, void* stream) {
+  if (group_size != 128 || block_n != 128 || k <= 0 || k % 128 != 0 || inter <= 0 || inter % 128 != 0 ||
+      groups <= 0 || m_total <= 0 || max_mtiles <= 0) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (mid_dt != 1 && mid_dt != 2) return INFEROP_ERR_DTYPE;
+  if (m_total > 0x7FFFFF00LL || groups * 2 * inter > 0x7FFFFF00LL || k > 0x7FFFFF00LL || groups >= (1 << 22)) {
+    return INFEROP_ERR_LIMIT;
+  }
+  if (!q || !q_scales || !a_q || !a_scales || !b_q || !b_scales || !tile_row0 || !tile_meta || !num_mtiles) {
+    return INFEROP_ERR_POINTER;
+  }
+  if ((reinterpret_cast<uintptr_t>(a_q) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u) ||
+      (reinterpret_cast<uintptr_t>(q) & 15u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_gemm_swiglu(ctx, q, static_cast<float*>(q_scales), a_q, a_scales, b_q, b_scales, tile_row0,
+                            tile_meta, num_mtiles, max_mtiles, m_total, groups, inter, k, mid_dt,
+                            static_cast<cudaStream_t>(stream));
+}
+
 int inferop_device_status(uint32_t* out4, int reset) {
   // Allocates nothing: reads the record of the library-owned context if one exists on this
   // device, and the record inside the fixed scratch array if the allocation-free entry point

@@ -45,7 +45,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "internal.h"
+#include "quant_math.cuh"
+#include "swiglu_math.cuh"
 
 #define IB200_TRACE_TAG single
 #include "trace.cuh"
@@ -91,6 +95,8 @@ struct GemmParams {
   int group_m;   // M-tiles per rasterisation band: a band's A panel stays in L2 while W streams past once
   int tma_store; // 1: epilogue goes through shared memory + TMA store
   int no_loads;  // test hook: the producer issues no load
+  // SwiGLU launches only: c receives E4M3 bytes [rows, n / 2], c_scales one fp32 per 128 of them
+  float* c_scales;
   DeviceStatus* status;
 };
 
@@ -134,13 +140,22 @@ struct PeerMaps {
 // rank; map[d] describes rank d's slots as one [G * M/G, N] fp32 tensor (box 128 rows x 32
 // columns) and this rank writes slot `rank` of it.  The owner adds its slots in rank order
 // afterwards (reduce_slots), so the sum does not depend on arrival order.
-enum : int { kModePlain = 0, kModeGrouped = 1, kModeGather = 2, kModeScatter = 3 };
+// SwiGLU launches (the gate_up projection of an expert layer): a grouped launch whose weights are
+// [groups][2 I][K] with the gate rows first and the up rows second (the reference's layout,
+// kernels/silu_mul.cu:16-28).  Tile tn takes gate rows [128 tn, 128 tn + 128) as its left 128
+// columns and up rows [I + 128 tn, ...) as its right 128, so one tile holds everything one
+// 128-wide output group needs: the epilogue rounds both halves to the 16-bit type, applies
+// silu(gate) * up, quantises the 128 results of each row (one scale per row and tile) and writes
+// E4M3 bytes + scales, bit for bit what silu_and_mul_quant makes of the GEMM's 16-bit output.
+enum : int { kModePlain = 0, kModeGrouped = 1, kModeGather = 2, kModeScatter = 3, kModeSwiglu = 4 };
 
 struct TileInfo {
   int a_row;     // first row of the tile in A / a_scales / C
   int row_end;   // rows at and beyond this index are not this tile's
   int b_row;     // first row of the tile in the (stacked) weight matrix
+  int b_row_hi;  // SwiGLU launches: first weight row of the right column half (the up rows)
   int sb_row;    // row of b_scales for the tile's left half
+  int sb_step;   // rows of b_scales between the left and the right column half
   int sb_rows;   // one past the last valid b_scales row for this tile's group
   int col;       // first output column
 };
@@ -162,10 +177,26 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / band_m;
 }
 
-template <bool kGrouped, int BN>
+template <bool kGrouped, int BN, bool kSwiglu = false>
 __device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p, const TileList& tab) {
   TileInfo ti;
-  if (kGrouped) {
+  ti.sb_step = (BN / 2) / 128;
+  ti.b_row_hi = 0;
+  if (kSwiglu) {
+    // p.n = 2 I weight rows per group, p.tiles_n = I / 128 tiles, 128 output columns per tile
+    const int mt = t / p.tiles_n, tn = t - mt * p.tiles_n;
+    const int meta = tab.meta[mt];
+    const int group = meta >> 8;
+    const int inter = p.n >> 1;
+    ti.a_row = tab.row0[mt];
+    ti.row_end = ti.a_row + (meta & 0xFF) + 1;
+    ti.b_row = group * p.n + tn * 128;
+    ti.b_row_hi = ti.b_row + inter;
+    ti.sb_row = group * p.nb + tn;
+    ti.sb_step = inter >> 7;
+    ti.sb_rows = (group + 1) * p.nb;
+    ti.col = tn * 128;
+  } else if (kGrouped) {
     const int mt = t / p.tiles_n, tn = t - mt * p.tiles_n;
     const int meta = tab.meta[mt];
     const int group = meta >> 8;
@@ -242,7 +273,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
                                           const CUtensorMap* map_c, const GemmParams& p,
                                           const TileList tab, const PeerMaps* peers,
                                           const int* num_mtiles_dev) {
-  constexpr bool kGrouped = kMode == kModeGrouped;
+  constexpr bool kSwiglu = kMode == kModeSwiglu;
+  constexpr bool kGrouped = kMode == kModeGrouped || kSwiglu;
   constexpr bool kGather = kMode == kModeGather;
   constexpr bool kScatter = kMode == kModeScatter;
   using TL = Tile<TBN>;
@@ -307,7 +339,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       uint32_t armed = 0, armed_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && !p.no_loads && t < num_tiles; t += gridDim.x) {
-        const TileInfo ti = tile_info<kGrouped, BN>(t, p, tab);
+        const TileInfo ti = tile_info<kGrouped, BN, kSwiglu>(t, p, tab);
         for (int kb = 0; kb < p.kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty)) {
             ok = false;
@@ -316,7 +348,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           uint8_t* sa = smem + stage * kStageBytes;
           mbar_arrive_expect_tx(&full[stage], kStageBytes);
           tma_load_2d(sa, map_a, &full[stage], kb * BK, ti.a_row);
-          tma_load_2d(sa + kBytesA, map_b, &full[stage], kb * BK, ti.b_row);
+          if constexpr (kSwiglu) {
+            // two 128-row boxes of the weights: the gate rows, then the up rows of the same block
+            tma_load_2d(sa + kBytesA, map_b, &full[stage], kb * BK, ti.b_row);
+            tma_load_2d(sa + kBytesA + 128 * BK, map_b, &full[stage], kb * BK, ti.b_row_hi);
+          } else {
+            tma_load_2d(sa + kBytesA, map_b, &full[stage], kb * BK, ti.b_row);
+          }
           armed |= 1u << stage;
           armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
           if (++stage == kStages) {
@@ -399,9 +437,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
     uint32_t kiter = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       bool ok = true;
-      const TileInfo ti = tile_info<kGrouped, BN>(t, p, tab);
+      const TileInfo ti = tile_info<kGrouped, BN, kSwiglu>(t, p, tab);
       const int gm = ti.a_row + row;
-      const int nbi = ti.sb_row + (half * CT) / 128;
+      const int nbi = ti.sb_row + half * ti.sb_step;
       const bool have = gm < ti.row_end && nbi < ti.sb_rows;
       // a TMA store writes whole 128-row boxes (clipped only at the end of C): a grouped tile
       // with fewer rows must not spill into the next group's rows
@@ -465,9 +503,65 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       // A warp whose wait ran out must not leave its siblings alone at the named barriers of the
       // epilogue: the four warps of a column half agree here, through a reducing barrier, whether
       // the tile is abandoned, and leave together.
-      if (named_bar_or(1 + half, 128, !ok)) break;
+      if (named_bar_or(kSwiglu ? 3 : 1 + half, kSwiglu ? 256 : 128, !ok)) break;
 
       // ---- epilogue: this thread holds C[gm, col .. col + 128) in fp32
+      if constexpr (kSwiglu) {
+        // The right column half (up) parks its 128 values per row, rounded to the 16-bit type, in
+        // the staging memory: row r = 256 bytes, 16-byte chunk j at position j ^ (r & 15), which
+        // keeps both the row-per-thread writes and reads free of bank conflicts.  The left half
+        // (gate) then owns one whole 128-wide output group per thread.
+        named_bar_sync(3, 256);   // the previous tile's readers are done with the staging memory
+        const float* accf = reinterpret_cast<const float*>(acc);
+        uint8_t* ex = store_buf + row * 256;
+        if (half == 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            uint4 w;
+            const float* a8 = accf + j * 8;
+            w.x = pack2<OutT>(a8[0], a8[1]);
+            w.y = pack2<OutT>(a8[2], a8[3]);
+            w.z = pack2<OutT>(a8[4], a8[5]);
+            w.w = pack2<OutT>(a8[6], a8[7]);
+            *reinterpret_cast<uint4*>(ex + ((j ^ (row & 15)) << 4)) = w;
+          }
+        }
+        named_bar_sync(3, 256);
+        if (half == 0) {
+          using T2 = typename std::conditional<std::is_same<OutT, __half>::value, __half2, __nv_bfloat162>::type;
+          uint4 h[16];
+          float amax = 0.0f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            uint4 g;
+            const float* a8 = accf + j * 8;
+            g.x = pack2<OutT>(a8[0], a8[1]);
+            g.y = pack2<OutT>(a8[2], a8[3]);
+            g.z = pack2<OutT>(a8[4], a8[5]);
+            g.w = pack2<OutT>(a8[6], a8[7]);
+            const uint4 u = *reinterpret_cast<const uint4*>(ex + ((j ^ (row & 15)) << 4));
+            h[j] = swiglu::silu_mul8<OutT>(g, u);
+            amax = fmaxf(amax, absmax8_packed<T2>(h[j]));
+          }
+          const float scale = group_scale(amax);
+          if (gm < ti.row_end) {
+            const bool fast = fast_div_ok(amax);
+            const float rcp = __frcp_rn(scale);
+            uint8_t* qrow = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(gm) * (p.n >> 1) + ti.col;
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              float f0[8], f1[8];
+              swiglu::unpack8<OutT>(h[j], f0);
+              swiglu::unpack8<OutT>(h[j + 1], f1);
+              const uint2 b0 = fast ? quantise8_fast16(h[j], f0, scale, rcp) : quantise8<false>(f0, scale, 0.0f);
+              const uint2 b1 = fast ? quantise8_fast16(h[j + 1], f1, scale, rcp) : quantise8<false>(f1, scale, 0.0f);
+              *reinterpret_cast<uint4*>(qrow + j * 8) = make_uint4(b0.x, b0.y, b1.x, b1.y);
+            }
+            p.c_scales[static_cast<int64_t>(gm) * (p.n >> 8) + (ti.col >> 7)] = scale;
+          }
+        }
+        continue;
+      }
       if constexpr (kScatter) {
         // fp32 partial sums to slot `rank` of the rows' owner, 32 columns (128 bytes) per store
         const int owner = ti.a_row / peers->rows_per_owner;
@@ -608,6 +702,31 @@ w8a8_grouped_dev_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __
   gemm_body<OutT, kModeGrouped, TBN>(&map_a, &map_b, &map_c, p, TileList{row0, meta}, nullptr, num_mtiles);
 }
 
+// SwiGLU launch: grouped tile list from device memory, output = E4M3 bytes + scales
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_swiglu_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const GemmParams p, const int* __restrict__ row0, const int* __restrict__ meta,
+                        const int* __restrict__ num_mtiles) {
+  gemm_body<T, kModeSwiglu, 256>(&map_a, &map_b, nullptr, p, TileList{row0, meta}, nullptr, num_mtiles);
+}
+
+template <typename T>
+int launch_swiglu_t(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, const int* row0,
+                    const int* meta, const int* num_mtiles, int ctas, cudaStream_t stream) {
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(w8a8_swiglu_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_done[dev] = true;
+  }
+  w8a8_swiglu_gemm_kernel<T><<<ctas, kThreads, kSmemBytes, stream>>>(ma, mb, p, row0, meta, num_mtiles);
+  return check_launch();
+}
+
 template <typename OutT, int TBN>
 int launch_grouped_dev_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
                          const GemmParams& p, const int* row0, const int* meta, const int* num_mtiles,
@@ -728,6 +847,7 @@ int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, 
   p.tma_store = tma_store ? 1 : 0;
   p.group_m = opt.gemm_group_m > 0 ? opt.gemm_group_m : 32;
   p.no_loads = opt.debug_no_loads;
+  p.c_scales = nullptr;
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;
@@ -783,6 +903,7 @@ int launch_gemm_grouped(DeviceCtx* ctx, void* c, const void* a_q, const void* a_
   p.tma_store = tma_store ? 1 : 0;
   p.group_m = 32;
   p.no_loads = opt.debug_no_loads;
+  p.c_scales = nullptr;
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;
@@ -866,6 +987,7 @@ int launch_gemm_allgather(DeviceCtx* ctx, void* const* c_peers, int32_t n_peers,
   p.tma_store = 1;
   p.group_m = opt.gemm_group_m > 0 ? opt.gemm_group_m : 32;
   p.no_loads = opt.debug_no_loads;
+  p.c_scales = nullptr;
   p.status = ctx->status;
 
   CUtensorMap ma, mb;
@@ -916,6 +1038,7 @@ int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void
   p.tma_store = tma_store ? 1 : 0;
   p.group_m = 32;
   p.no_loads = opt.debug_no_loads;
+  p.c_scales = nullptr;
   p.status = ctx->status;
 
   CUtensorMap ma, mb, mc;
@@ -940,6 +1063,42 @@ int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void
                              : launch_grouped_dev_t<__nv_bfloat16, 256>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
     default: return INFEROP_ERR_DTYPE;
   }
+}
+
+int launch_gemm_swiglu(DeviceCtx* ctx, void* q, float* q_scales, const void* a_q, const void* a_scales,
+                       const void* b_q, const void* b_scales, const int32_t* tile_row0,
+                       const int32_t* tile_meta, const int32_t* num_mtiles, int64_t max_mtiles,
+                       int64_t m_total, int64_t groups, int64_t inter, int64_t k, int32_t mid_dt,
+                       cudaStream_t stream) {
+  const Options& opt = options();
+  GemmParams p;
+  p.a_scales = static_cast<const float*>(a_scales);
+  p.b_scales = static_cast<const float*>(b_scales);
+  p.c = q;
+  p.c_scales = q_scales;
+  p.m = static_cast<int>(m_total);
+  p.n = static_cast<int>(2 * inter);          // weight rows per group: gate rows, then up rows
+  p.k = static_cast<int>(k);
+  p.kb = static_cast<int>(k / 128);
+  p.nb = static_cast<int>(2 * inter / 128);
+  p.tiles_n = static_cast<int>(inter / 128);
+  p.tiles_m = static_cast<int>(max_mtiles);
+  const int64_t tiles = max_mtiles * p.tiles_n;
+  if (tiles > 0x7FFFFFFF || tiles * p.kb > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
+  p.num_tiles = static_cast<int>(tiles);
+  p.tma_store = 0;
+  p.group_m = 32;
+  p.no_loads = opt.debug_no_loads;
+  p.status = ctx->status;
+  CUtensorMap ma, mb;
+  int rc = make_tensor_map_2d(&ma, a_q, 1, m_total, k, k, BM, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  rc = make_tensor_map_2d(&mb, b_q, 1, groups * 2 * inter, k, k, 128, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
+  if (ctas > p.num_tiles) ctas = p.num_tiles;
+  return mid_dt == 1 ? launch_swiglu_t<__half>(ma, mb, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
+                     : launch_swiglu_t<__nv_bfloat16>(ma, mb, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
 }
 
 int launch_gemm_scatter(DeviceCtx* ctx, void* const* slot_peers, int32_t n_peers, int32_t rank,
@@ -970,6 +1129,7 @@ int launch_gemm_scatter(DeviceCtx* ctx, void* const* slot_peers, int32_t n_peers
   p.tma_store = 1;
   p.group_m = opt.gemm_group_m > 0 ? opt.gemm_group_m : 32;
   p.no_loads = opt.debug_no_loads;
+  p.c_scales = nullptr;
   p.status = ctx->status;
 
   CUtensorMap ma, mb;

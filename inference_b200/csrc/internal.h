@@ -89,6 +89,15 @@ int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void
                             int64_t m_total, int64_t groups, int64_t n, int64_t k, int32_t out_dt,
                             cudaStream_t stream);
 
+// Grouped launch of a gate_up projection whose epilogue applies SwiGLU and quantises the result
+// per 1 x 128 group: q [m_total, inter] E4M3 + q_scales [m_total, inter / 128]; b_q is
+// [groups][2 * inter][k], gate rows first.
+int launch_gemm_swiglu(DeviceCtx* ctx, void* q, float* q_scales, const void* a_q, const void* a_scales,
+                       const void* b_q, const void* b_scales, const int32_t* tile_row0,
+                       const int32_t* tile_meta, const int32_t* num_mtiles, int64_t max_mtiles,
+                       int64_t m_total, int64_t groups, int64_t inter, int64_t k, int32_t mid_dt,
+                       cudaStream_t stream);
+
 // Scatter launch (row-parallel sharding): fp32 partial results of this rank's K shard, stored
 // tile by tile into slot `rank` of the rank that owns the rows; slot_peers[d] (host array) is the
 // base of rank d's [n_peers][m / n_peers][n] fp32 slots as mapped in this process.

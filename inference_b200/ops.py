@@ -346,6 +346,33 @@ def w8a8_block_fp8_gemm_grouped_tiles(a_q: torch.Tensor, a_scales: torch.Tensor,
     return out
 
 
+def w8a8_block_fp8_gemm_grouped_tiles_swiglu(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: torch.Tensor,
+                                             b_scales: torch.Tensor, layout: MoeLayout, mid_dtype=torch.bfloat16,
+                                             q: torch.Tensor | None = None, scales: torch.Tensor | None = None,
+                                             stream=None):
+    """gate_up projection + SwiGLU + 1x128 quantisation in one launch: the same (q, scales) as
+    w8a8_block_fp8_gemm_grouped_tiles(out dtype mid_dtype) followed by silu_and_mul_quant.
+    b_q [G, 2 * inter, K] (gate rows first), b_scales [G, 2 * inter / 128, K / 128]."""
+    for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
+        _dev_tensor(t, name)
+    if mid_dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("mid_dtype must be fp16 or bf16")
+    groups, n2, k = b_q.shape
+    inter = n2 // 2
+    m_total = a_q.shape[0]
+    with torch.cuda.device(a_q.device):
+        if q is None:
+            q = torch.empty((m_total, inter), dtype=torch.uint8, device=a_q.device)
+        if scales is None:
+            scales = torch.empty((m_total, inter // 128), dtype=torch.float32, device=a_q.device)
+        check(lib.inferop_w8a8_block_fp8_gemm_grouped_tiles_swiglu(
+            q.data_ptr(), scales.data_ptr(), a_q.data_ptr(), a_scales.data_ptr(), b_q.data_ptr(), b_scales.data_ptr(),
+            layout.tile_row0.data_ptr(), layout.tile_meta.data_ptr(), layout.num_mtiles.data_ptr(),
+            layout.max_mtiles, m_total, groups, inter, k, 128, 128, int(_TORCH2CODE[mid_dtype]),
+            _stream_ptr(stream)), "w8a8_block_fp8_gemm_grouped_tiles_swiglu")
+    return q, scales
+
+
 def device_status(reset: bool = True):
     """Synchronise and return the device-side status record (code, block, aux0, aux1)."""
     rec = (C.c_uint32 * 4)()

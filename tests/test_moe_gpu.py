@@ -189,9 +189,53 @@ def test_grouped_gemm_from_device_tiles_equals_the_host_count_form(ops):
     assert torch.equal(got, want)
 
 
+# ------------------------------------------------ SwiGLU + re-quantisation in the gate_up epilogue
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("tokens,experts,topk,inter,k", [(700, 12, 3, 384, 512), (64, 4, 2, 128, 256),
+                                                          (4096, 64, 8, 2048, 1024)])
+def test_swiglu_epilogue_equals_gemm_then_silu_and_mul_quant(ops, dt, tokens, experts, topk, inter, k):
+    """One launch against the two it replaces (grouped GEMM with 16-bit output, then
+    silu_and_mul_quant): bytes and scales must be identical; and against the oracle's chain
+    (fp64 golden GEMM -> rounding -> SwiGLU -> quantisation) on one expert, where a 16-bit
+    rounding of the GEMM result may differ by one unit in the last place."""
+    from inference_b200 import synth
+    rng = np.random.default_rng(tokens + inter)
+    logits = rng.standard_normal((tokens, experts)).astype(np.float32)
+    if experts > 4:
+        logits[:, 1] = -60.0      # an empty expert
+    ids, _ = oracle.topk_softmax(logits, topk)
+    lay = ops.moe_align(cuda(ids), experts)
+    x = synth.activations(tokens, k, seed=2).to(dt)
+    aq, a_s = ops.moe_scatter_quant(x, lay)
+    bq, bs = synth.quantised_weights(experts * 2 * inter, k, seed=3)
+    bq, bs = bq.view(experts, 2 * inter, k), bs.view(experts, 2 * inter // 128, k // 128)
+    pairs = tokens * topk
+    gu = ops.w8a8_block_fp8_gemm_grouped_tiles(aq, a_s, bq, bs, lay, dt)
+    q2, s2 = ops.silu_and_mul_quant(gu)
+    canary = torch.full((pairs * inter + 4096,), 0xA5, dtype=torch.uint8, device="cuda")
+    q1 = canary[:pairs * inter].view(pairs, inter)
+    s1 = torch.full((pairs, inter // 128), -1.0, dtype=torch.float32, device="cuda")
+    ops.w8a8_block_fp8_gemm_grouped_tiles_swiglu(aq, a_s, bq, bs, lay, dt, q1, s1)
+    assert ops.device_status()[0] == 0
+    assert bool((canary[pairs * inter:] == 0xA5).all())
+    valid = int(lay.offsets.cpu()[-1].item())          # rows that belong to some expert
+    assert torch.equal(q1[:valid], q2[:valid]) and torch.equal(s1[:valid], s2[:valid])
+
+
+def test_swiglu_epilogue_rejects_bad_arguments(ops):
+    from inference_b200 import _capi
+    t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p = t.data_ptr()
+    f = _capi.lib.inferop_w8a8_block_fp8_gemm_grouped_tiles_swiglu
+    assert f(p, p, p, p, p, p, p, p, p, 4, 4, 2, 200, 128, 128, 128, 2, None) == _capi.ERR_SHAPE    # inter % 128
+    assert f(p, p, p, p, p, p, p, p, p, 4, 4, 2, 256, 128, 128, 128, 0, None) == _capi.ERR_DTYPE    # fp32 middle type
+    assert f(p + 8, p, p, p, p, p, p, p, p, 4, 4, 2, 256, 128, 128, 128, 2, None) == _capi.ERR_POINTER
+
+
 # ------------------------------------------------------------------------------ the whole layer
-def test_layer_equals_the_reference_style_composition(ops):
-    """Seven launches with no host step against the reference's way of composing its operators:
+@pytest.mark.parametrize("fused", [True, False])
+def test_layer_equals_the_reference_style_composition(ops, fused):
+    """Six (or seven) launches with no host step against the reference's way of composing its operators:
     routing, then per expert quant -> GEMM -> SwiGLU -> quant -> GEMM on that expert's tokens, then
     the weighted sum."""
     from inference_b200 import synth
@@ -204,7 +248,7 @@ def test_layer_equals_the_reference_style_composition(ops):
     wd, sd = synth.quantised_weights(experts * hidden, inter, seed=7)
     wgu, sgu = wgu.view(experts, 2 * inter, hidden), sgu.view(experts, 2 * inter // 128, hidden // 128)
     wd, sd = wd.view(experts, hidden, inter), sd.view(experts, hidden // 128, inter // 128)
-    layer = MoEFP8Layer(wgu, sgu, wd, sd, topk, tokens)
+    layer = MoEFP8Layer(wgu, sgu, wd, sd, topk, tokens, fused_swiglu=fused)
     got = layer.forward(x, logits)
     assert ops.device_status()[0] == 0
 
