@@ -435,6 +435,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
     uint8_t* my_buf = store_buf + half * kStoreBufBytes;
     const bool issuer = (quarter == 0 && lane == 0);
     uint32_t kiter = 0;
+    bool gave_up = false;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       bool ok = true;
       const TileInfo ti = tile_info<kGrouped, BN, kSwiglu>(t, p, tab);
@@ -500,10 +501,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           promote32(acc + 16, v1, s);
         }
       }
-      // A warp whose wait ran out must not leave its siblings alone at the named barriers of the
-      // epilogue: the four warps of a column half agree here, through a reducing barrier, whether
-      // the tile is abandoned, and leave together.
-      if (named_bar_or(kSwiglu ? 3 : 1 + half, kSwiglu ? 256 : 128, !ok)) break;
+      if (!ok) {
+        gave_up = true;
+        break;
+      }
 
       // ---- epilogue: this thread holds C[gm, col .. col + 128) in fp32
       if constexpr (kSwiglu) {
@@ -669,6 +670,20 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       }
     }
     if (issuer) tma_store_wait_all();
+    if (gave_up) {
+      // This warp's wait ran out (the CTA's abort flag is set, the call will report
+      // INFEROP_ERR_DEVICE_WAIT).  A sibling whose own wait on the same barrier succeeded a moment
+      // later may already stand at one of the named barriers of the tile's epilogue, waiting for
+      // this warp.  It must not wait for ever: arrive at those barriers, without blocking, as
+      // often as an epilogue has barriers, with pauses in which the siblings move on.  They then
+      // fail their next wait (the MMA warps stop without this warp's releases) and come here too.
+      for (int i = 0; i < 8; ++i) {
+        named_bar_arrive(kSwiglu ? 3 : 1 + half, kSwiglu ? 256 : 128);
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4096) {
+        }
+      }
+    }
   }
 
   tc_fence_before_sync();
