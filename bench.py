@@ -85,6 +85,7 @@ def parse_args():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU-baseline sample budget")
     ap.add_argument("--moe-only", action="store_true",
                     help="run only the MoE section (grouped GEMMs and the expert layer) and print it")
+    ap.add_argument("--refcuda-only", action="store_true", help="run only the secondary GPU baseline (the reference's CUDA kernels)")
     ap.add_argument("--sweep-only", action="store_true", help="run only the decode / prefill shape sweep and print it")
     ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE",
                     help="library tuning option (inferop_set_option), e.g. --set gemm_pair=0; may be repeated")
@@ -261,6 +262,69 @@ def parity_gate(x, aq, a_s, bq, bs, c, seed=0, rows_per_band=16, n_cols=512, b_r
     if not ok:
         raise AssertionError(f"parity gate failed: {rec}")
     return rec
+
+
+# ----------------------------------------------------------------------------- secondary GPU baseline
+def reference_cuda_baseline(m=4096, n=18432, k=7168, iters=3):
+    """The reference's own CUDA kernels for this path (kernels/quant.cu + kernels/gemm/w8a8_block_fp8.cu,
+    compiled unmodified for sm_100 into oracle/_ref/libinferop_ref_cuda.so) timed on this GPU through
+    the same operator arguments, beside this library on the same inputs; their results are compared."""
+    import ctypes as C
+    import torch
+    from inference_b200 import ops, synth
+    path = os.path.join(ROOT, "oracle", "_ref", "libinferop_ref_cuda.so")
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/libinferop_ref_cuda.so has not been built (needs the reference tree)"}
+    ref = C.CDLL(path)
+    vp, i64, i32 = C.c_void_p, C.c_int64, C.c_int32
+    ref.refcuda_quant_fp8_per_token_group.argtypes = [vp, vp, vp, i32, i64, i64, i32, vp]
+    ref.refcuda_quant_fp8_per_token_group.restype = None
+    ref.refcuda_w8a8_block_fp8_gemm.argtypes = [vp] * 5 + [i64] * 3 + [i32] * 3 + [vp]
+    ref.refcuda_w8a8_block_fp8_gemm.restype = None
+    x = synth.activations(m, k, seed=0)
+    bq, bs = synth.quantised_weights(n, k, seed=1)
+    aq = torch.empty((m, k), dtype=torch.uint8, device="cuda")
+    a_s = torch.empty((m, k // 128), dtype=torch.float32, device="cuda")
+    c_ref = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def ref_step():
+        ref.refcuda_quant_fp8_per_token_group(aq.data_ptr(), a_s.data_ptr(), x.data_ptr(), 2, m, k, 128, stream)
+        ref.refcuda_w8a8_block_fp8_gemm(c_ref.data_ptr(), aq.data_ptr(), a_s.data_ptr(), bq.data_ptr(), bs.data_ptr(),
+                                        m, n, k, 128, 128, 2, stream)
+
+    aq2, a_s2 = torch.empty_like(aq), torch.empty_like(a_s)
+    c_ours = torch.empty_like(c_ref)
+
+    def our_step():
+        ops.quant_fp8_per_token_group(x, 128, aq2, a_s2)
+        ops.w8a8_block_fp8_gemm(aq2, a_s2, bq, bs, out=c_ours)
+
+    out = {"m": m, "n": n, "k": k}
+    for name, fn, reps in (("reference_cuda", ref_step, iters), ("this_library", our_step, 10)):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = e0.elapsed_time(e1) * 1e-3 / reps
+        out[name] = {"ms": round(t * 1e3, 3), "tflops": round(2.0 * m * n * k / t / 1e12, 1)}
+    out["speedup"] = round(out["reference_cuda"]["ms"] / out["this_library"]["ms"], 1)
+    # the reference multiplies by a reciprocal scale, the oracle (and this library) divide: bytes may
+    # differ by a rounding step on a few elements, so quantisation is compared as a mismatch rate
+    out["quant_bytes_differing"] = float((aq != aq2).float().mean().item())
+    out["quant_scales_equal"] = bool(torch.equal(a_s, a_s2))
+    # GEMM against GEMM on identical quantised inputs
+    ref.refcuda_w8a8_block_fp8_gemm(c_ref.data_ptr(), aq2.data_ptr(), a_s2.data_ptr(), bq.data_ptr(), bs.data_ptr(),
+                                    m, n, k, 128, 128, 2, stream)
+    torch.cuda.synchronize()
+    d = (c_ref.float() - c_ours.float())
+    out["gemm_rel_frobenius_vs_reference_cuda"] = float((d.norm() / c_ref.float().norm()).item())
+    out["what"] = "quant + GEMM, bf16 out; the reference's CUDA-core kernels (software E4M3 decode, 128x64 tiles) on the same B200"
+    return out
 
 
 # ----------------------------------------------------------------------------- shape sweep
@@ -869,6 +933,8 @@ def run_ours(args):
                          "shapes": shape_sweep(peaks)}
         torch.cuda.empty_cache()
         line["moe"] = moe_config(peaks, experts=args.moe_experts, tokens=args.moe_tokens)
+        torch.cuda.empty_cache()
+        line["extra"] = {"reference_cuda": reference_cuda_baseline()}
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         smp = sized_cpu_sample(k, threads, args.cpu_seconds)
@@ -897,6 +963,8 @@ def main():
     try:
         if args.impl == "reference":
             run_reference(args)
+        elif args.refcuda_only:
+            print_result(json.dumps({"reference_cuda": reference_cuda_baseline()}))
         elif args.moe_only or args.sweep_only:
             from inference_b200 import ops
             for kv in args.set:

@@ -28,7 +28,8 @@ _int = C.c_int
 
 
 def build(reference_root: str | None = None) -> None:
-    """Compile the checker (and the reference's CPU code when its tree is present)."""
+    """Compile the checker (and, when the reference tree is present, the reference's own CPU code
+    and its CUDA kernels for this path: the two baselines of the benchmark)."""
     cmd = ["make", "-s", "-C", _HERE]
     if reference_root:
         cmd.append(f"REF={reference_root}")

@@ -1,0 +1,25 @@
+// C entry points over the reference's own CUDA kernels for this path (kernels/quant.cu,
+// kernels/gemm/w8a8_block_fp8.cu), compiled unmodified from the reference tree for sm_100.
+// TEST / BENCHMARK INFRASTRUCTURE ONLY: the secondary GPU baseline of bench.py (the reference's
+// CUDA-core kernels timed on the same B200) and a cross-check of results.  Nothing in the
+// shipped package links or loads this.
+#include <stdint.h>
+
+#include "internal.h"   // the reference's kernels/internal.h (dispatch entries per translation unit)
+
+extern "C" {
+
+__attribute__((visibility("default"))) void refcuda_quant_fp8_per_token_group(
+    void* q, void* scales, const void* x, int32_t dt, int64_t rows, int64_t cols, int32_t group_size, void* stream) {
+  inferop::kernels::quant_fp8_per_token_group_impl(q, scales, x, static_cast<inferop::dtype>(dt), rows, cols,
+                                                   group_size, stream);
+}
+
+__attribute__((visibility("default"))) void refcuda_w8a8_block_fp8_gemm(
+    void* c, const void* a_q, const void* a_scales, const void* b_q, const void* b_scales, int64_t m, int64_t n,
+    int64_t k, int32_t group_size, int32_t block_n, int32_t out_dt, void* stream) {
+  inferop::kernels::w8a8_block_fp8_gemm_impl(c, a_q, a_scales, b_q, b_scales, m, n, k, group_size, block_n,
+                                             static_cast<inferop::dtype>(out_dt), stream);
+}
+
+}  // extern "C"

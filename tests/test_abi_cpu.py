@@ -111,3 +111,14 @@ extern "C" void e2f(const uint8_t* h, float* f, long n){ for(long i=0;i<n;++i) f
         b = np.arange(256, dtype=np.uint8)
         lib.e2f(b.ctypes.data_as(C.c_void_p), f.ctypes.data_as(C.c_void_p), C.c_long(256))
         assert np.array_equal(f[:256].view(np.uint32), oracle.e4m3_decode(b).view(np.uint32))
+
+
+def test_reference_cuda_baseline_library_exports_its_two_entry_points():
+    """oracle/_ref/libinferop_ref_cuda.so (the reference's CUDA kernels for this path, built from the
+    reference tree by oracle/Makefile) is what bench.py times as the secondary GPU baseline."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "_ref", "libinferop_ref_cuda.so")
+    if not os.path.exists(path):
+        pytest.skip("not built here (needs the reference tree)")
+    lib = ctypes.CDLL(path)
+    assert hasattr(lib, "refcuda_quant_fp8_per_token_group") and hasattr(lib, "refcuda_w8a8_block_fp8_gemm")

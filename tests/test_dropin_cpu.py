@@ -10,7 +10,8 @@ import pytest
 
 from conftest import ROOT
 
-REF = os.environ.get("INFEROP_REFERENCE", "/root/reference")
+# the reference tree: INFEROP_REFERENCE, else a directory "reference" beside this repository
+REF = os.environ.get("INFEROP_REFERENCE", os.path.abspath(os.path.join(ROOT, "..", "reference")))
 pytestmark = pytest.mark.skipif(not os.path.exists(os.path.join(REF, "tests", "test_gemm.cpp")),
                                 reason="reference tree not present")
 
