@@ -384,6 +384,22 @@ def shape_sweep(peaks):
         else:
             rec["frac_of_nominal_fp8_peak"] = round(flops / t / 1e12 / NOMINAL_FP8_TFLOPS, 3)
         rec["parity"] = parity_gate(x, aq, a_s, bq, bs, c, seed=m + n)
+        if m >= 1024:
+            # the same step through the one-call entry point (quantisation as the GEMM's A prologue:
+            # for this many rows the quantiser and the GEMM chained by programmatic dependent launch)
+            c2 = torch.empty_like(c)
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs, out=c2)
+                torch.cuda.synchronize()
+                e0.record(side)
+                for _ in range(5):
+                    ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs, out=c2)
+                e1.record(side)
+                torch.cuda.synchronize()
+            rec["fused_prologue_us"] = round(e0.elapsed_time(e1) * 1e3 / 5, 2)
+            rec["fused_equals_separate"] = bool(torch.equal(c, c2))
+            del c2
         out.append(rec)
         del g
     return out

@@ -86,13 +86,17 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void
                                 int32_t group_size, int32_t block_n, int32_t out_dt,
                                 void* stream);
 
-/* ---- quantisation fused into the GEMM as its A-operand prologue (a few tokens)
+/* ---- quantisation as the GEMM's A-operand prologue: one call for quantise + GEMM
  * Same result, bit for bit, as inferop_quant_fp8_per_token_group (group 128) followed by
- * inferop_w8a8_block_fp8_gemm (reference include/inferop/ops.h:64-65 then :81-84), in one launch
- * and without the q / scales round trip: the kernel's prologue warps quantise each K block of
- * the activations on the fly.  a [M, K] in a_dt (1 = fp16, 2 = bf16), 16-byte aligned; M <= 32
- * (INFEROP_ERR_LIMIT beyond: with more tokens every CTA would repeat too much quantisation work,
- * use the two calls).  Scratch as for the small-M GEMM path. */
+ * inferop_w8a8_block_fp8_gemm (reference include/inferop/ops.h:64-65 then :81-84).
+ * a [M, K] in a_dt (1 = fp16, 2 = bf16), 16-byte aligned.
+ *   M <= 32: one launch, without the q / scales round trip: the small-M kernel's prologue warps
+ *     quantise each K block of the activations on the fly (scratch as for the small-M GEMM path).
+ *   M > 32: quantising inside the GEMM would repeat the work once per column tile (N / 256
+ *     times), so the call is two launches chained by programmatic dependent launch: the
+ *     quantiser writes into library-owned scratch of this stream (M * K + 4 * M * K / 128 bytes,
+ *     grown by a cudaMalloc whenever a call is larger than any before it on the stream: make the
+ *     largest call before a stream capture) and the GEMM sets itself up underneath it. */
 INFEROP_API int inferop_w8a8_block_fp8_gemm_fused_quant(void* c, const void* a, int32_t a_dt, const void* b_q,
                                             const void* b_scales, int64_t m, int64_t n, int64_t k,
                                             int32_t group_size, int32_t block_n, int32_t out_dt,

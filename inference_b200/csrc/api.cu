@@ -155,6 +155,42 @@ bool decode_scratch(DeviceCtx* ctx, cudaStream_t stream, float** ws, int** count
   return true;
 }
 
+int quant_scratch(DeviceCtx* ctx, cudaStream_t stream, size_t q_bytes, size_t s_bytes, void** q, void** s) {
+  static std::mutex m;
+  std::lock_guard<std::mutex> lock(m);
+  int i = 0;
+  for (; i < ctx->n_qscratch; ++i)
+    if (ctx->qscratch_stream[i] == stream) break;
+  if (i == ctx->n_qscratch) {
+    if (ctx->n_qscratch >= DeviceCtx::kMaxStreams) return INFEROP_ERR_LIMIT;
+    ctx->qscratch_stream[i] = stream;
+    ++ctx->n_qscratch;
+  }
+  if (ctx->qscratch_q_bytes[i] < q_bytes || ctx->qscratch_s_bytes[i] < s_bytes) {
+    // growing: earlier calls on this stream may still read the old buffers
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    if (ctx->qscratch_q[i]) cudaFree(ctx->qscratch_q[i]);
+    if (ctx->qscratch_s[i]) cudaFree(ctx->qscratch_s[i]);
+    ctx->qscratch_q[i] = ctx->qscratch_s[i] = nullptr;
+    ctx->qscratch_q_bytes[i] = ctx->qscratch_s_bytes[i] = 0;
+    void *nq = nullptr, *ns = nullptr;
+    e = cudaMalloc(&nq, q_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ns, s_bytes);
+    if (e != cudaSuccess) {
+      if (nq) cudaFree(nq);
+      return note_cuda_error(e);
+    }
+    ctx->qscratch_q[i] = nq;
+    ctx->qscratch_s[i] = ns;
+    ctx->qscratch_q_bytes[i] = q_bytes;
+    ctx->qscratch_s_bytes[i] = s_bytes;
+  }
+  *q = ctx->qscratch_q[i];
+  *s = ctx->qscratch_s[i];
+  return INFEROP_OK;
+}
+
 }  // namespace ib200
 
 using namespace ib200;
@@ -231,6 +267,24 @@ static bool small_m_kernel(const DeviceCtx* ctx, int64_t m, int64_t n) {
   return false;
 }
 
+// Small M: the weight-streaming kernel, which needs scratch memory for split tiles.  The
+// scratch is created on the first such call of each stream (a cudaMalloc: make that call
+// before any stream capture); with more than DeviceCtx::kMaxStreams streams, or when the
+// allocation fails, the large-tile kernel serves the call instead.  From two 128-row tiles on,
+// the CTA-pair kernel.
+static int gemm_dispatch(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, const void* b_q,
+                         const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt, cudaStream_t s) {
+  if (small_m_kernel(ctx, m, n)) {
+    float* ws = nullptr;
+    int* counters = nullptr;
+    if (decode_scratch(ctx, s, &ws, &counters)) {
+      return launch_gemm_decode(ctx, ws, counters, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
+    }
+  }
+  if (use_pair_kernel(m)) return launch_gemm_pair(ctx, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
+  return launch_gemm(ctx, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
+}
+
 int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, const void* b_q,
                                 const void* b_scales, int64_t m, int64_t n, int64_t k,
                                 int32_t group_size, int32_t block_n, int32_t out_dt,
@@ -253,19 +307,7 @@ int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, 
   if ((reinterpret_cast<uintptr_t>(a_q) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u)) {
     return INFEROP_ERR_POINTER;
   }
-  // Small M: the weight-streaming kernel, which needs scratch memory for split tiles.  The
-  // scratch is created on the first such call of each stream (a cudaMalloc: make that call
-  // before any stream capture); with more than DeviceCtx::kMaxStreams streams, or when the
-  // allocation fails, the large-tile kernel serves the call instead.
-  if (small_m_kernel(ctx, m, n)) {
-    float* ws = nullptr;
-    int* counters = nullptr;
-    if (decode_scratch(ctx, s, &ws, &counters)) {
-      return launch_gemm_decode(ctx, ws, counters, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
-    }
-  }
-  if (use_pair_kernel(m)) return launch_gemm_pair(ctx, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
-  return launch_gemm(ctx, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
+  return gemm_dispatch(ctx, c, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
 }
 
 int inferop_w8a8_block_fp8_gemm_fused_quant(void* c, const void* a, int32_t a_dt, const void* b_q,
@@ -276,7 +318,8 @@ int inferop_w8a8_block_fp8_gemm_fused_quant(void* c, const void* a, int32_t a_dt
     return INFEROP_ERR_SHAPE;
   }
   if (out_dt < 0 || out_dt > 2 || (a_dt != 1 && a_dt != 2)) return INFEROP_ERR_DTYPE;
-  if (m > kFusedMaxM || (n + 127) / 128 > kDecodeMaxTiles || k > 0x7FFFFF00LL) return INFEROP_ERR_LIMIT;
+  if (m > 0x7FFFFF00LL || n > 0x7FFFFF00LL || k > 0x7FFFFF00LL) return INFEROP_ERR_LIMIT;
+  if (m <= kFusedMaxM && (n + 127) / 128 > kDecodeMaxTiles) return INFEROP_ERR_LIMIT;
   if (!c || !a || !b_q || !b_scales) return INFEROP_ERR_POINTER;
   if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u)) {
     return INFEROP_ERR_POINTER;
@@ -285,6 +328,19 @@ int inferop_w8a8_block_fp8_gemm_fused_quant(void* c, const void* a, int32_t a_dt
   DeviceCtx* ctx = current_ctx(&err);
   if (!ctx) return err;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (m > kFusedMaxM) {
+    // More than a few tokens: quantising inside the GEMM would repeat the work once per column
+    // tile (N / 256 times), so the one call is two launches: the quantiser writes into scratch of
+    // this stream (grown on demand: a cudaMalloc when a call is larger than any before it on the
+    // stream) and signals its dependents at once; the GEMM, launched with programmatic stream
+    // serialisation, sets itself up underneath it.  Same bits as the two separate calls.
+    void *q = nullptr, *qs = nullptr;
+    int rc = quant_scratch(ctx, s, static_cast<size_t>(m) * k, static_cast<size_t>(m) * (k / 128) * 4, &q, &qs);
+    if (rc != INFEROP_OK) return rc;
+    rc = launch_quant(q, qs, a, a_dt, m, k, 128, s, ctx->sm_count);
+    if (rc != INFEROP_OK) return rc;
+    return gemm_dispatch(ctx, c, q, qs, b_q, b_scales, m, n, k, out_dt, s);
+  }
   float* ws = nullptr;
   int* counters = nullptr;
   if (!decode_scratch(ctx, s, &ws, &counters)) return INFEROP_ERR_LIMIT;   // no scratch set left for this stream

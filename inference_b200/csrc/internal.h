@@ -27,6 +27,14 @@ struct DeviceCtx {
   cudaStream_t scratch_stream[kMaxStreams] = {};
   float* scratch_ws[kMaxStreams] = {};
   int* scratch_counters[kMaxStreams] = {};
+  // Quantised activations of the one-call quantise + GEMM entry point for large M, one pair of
+  // buffers per stream, grown on demand (never shrunk).
+  int n_qscratch = 0;
+  cudaStream_t qscratch_stream[kMaxStreams] = {};
+  void* qscratch_q[kMaxStreams] = {};
+  void* qscratch_s[kMaxStreams] = {};
+  size_t qscratch_q_bytes[kMaxStreams] = {};
+  size_t qscratch_s_bytes[kMaxStreams] = {};
 };
 // Context of the current device (nullptr + *err set when there is none / wrong arch).
 DeviceCtx* current_ctx(int* err);
@@ -46,6 +54,8 @@ struct Options {
 };
 Options& options();
 bool decode_scratch(DeviceCtx* ctx, cudaStream_t stream, float** ws, int** counters);
+// Buffers of at least q_bytes / s_bytes for `stream` (INFEROP_OK, or ERR_LIMIT / ERR_CUDA).
+int quant_scratch(DeviceCtx* ctx, cudaStream_t stream, size_t q_bytes, size_t s_bytes, void** q, void** s);
 
 // quant.cu
 int launch_quant(void* q, void* scales, const void* x, int32_t dt, int64_t rows, int64_t cols,

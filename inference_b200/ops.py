@@ -121,8 +121,10 @@ def w8a8_block_fp8_gemm(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: torch.Te
 def w8a8_block_fp8_gemm_fused_quant(a: torch.Tensor, b_q: torch.Tensor, b_scales: torch.Tensor,
                                     out_dtype=torch.bfloat16, out: torch.Tensor | None = None,
                                     stream=None) -> torch.Tensor:
-    """quant_fp8_per_token_group(a) followed by w8a8_block_fp8_gemm, fused into one launch
-    (M <= 32, a in bf16 / fp16).  Bit-identical to the two separate calls."""
+    """quant_fp8_per_token_group(a) followed by w8a8_block_fp8_gemm as one call (a in bf16 /
+    fp16): one launch with the quantisation as the GEMM's A-operand prologue for M <= 32; for
+    larger M the quantiser and the GEMM are chained by programmatic dependent launch through
+    library-owned scratch.  Bit-identical to the two separate calls."""
     for t, name in ((a, "a"), (b_q, "b_q"), (b_scales, "b_scales")):
         _dev_tensor(t, name)
     if a.dtype not in (torch.float16, torch.bfloat16):

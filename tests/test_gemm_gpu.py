@@ -286,7 +286,7 @@ def test_grouped_launch_rejects_bad_arguments(ops):
 
 
 # ------------------------------------------------------------------ quantisation fused as the A prologue
-@pytest.mark.parametrize("m", [1, 3, 16, 17, 32])
+@pytest.mark.parametrize("m", [1, 3, 16, 17, 32, 33, 129, 1024])
 @pytest.mark.parametrize("n,k", [(384, 512), (1000, 1536), (18432, 7168)])
 def test_fused_quant_prologue_is_bit_identical_to_the_two_calls(ops, m, n, k):
     from inference_b200 import synth
@@ -297,7 +297,7 @@ def test_fused_quant_prologue_is_bit_identical_to_the_two_calls(ops, m, n, k):
     bq, bs = synth.quantised_weights(n, k, seed=2)
     aq, a_s = ops.quant_fp8_per_token_group(x)
     for dt in (torch.bfloat16, torch.float32):
-        ops.set_option("gemm_path", 2)
+        ops.set_option("gemm_path", 2 if m <= 32 else 0)   # up to 32 tokens the one-launch form is the small-M kernel
         try:
             two = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, dt)
         finally:
@@ -318,6 +318,6 @@ def test_fused_quant_prologue_limits(ops):
     t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
     p = t.data_ptr()
     lib = _capi.lib
-    assert lib.inferop_w8a8_block_fp8_gemm_fused_quant(p, p, 2, p, p, 33, 256, 128, 128, 128, 2, None) == _capi.ERR_LIMIT
+    assert lib.inferop_w8a8_block_fp8_gemm_fused_quant(p, p, 2, p, p, 4, 128 * 70000, 128, 128, 128, 2, None) == _capi.ERR_LIMIT
     assert lib.inferop_w8a8_block_fp8_gemm_fused_quant(p, p, 0, p, p, 4, 256, 128, 128, 128, 2, None) == _capi.ERR_DTYPE
     assert lib.inferop_w8a8_block_fp8_gemm_fused_quant(p, p, 2, p, p, 4, 256, 100, 128, 128, 2, None) == _capi.ERR_SHAPE
