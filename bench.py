@@ -897,6 +897,34 @@ def run_ours(args):
                                    "link_gbs_out_per_rank": 2 * m * n_loc * (world - 1) / tf / 1e9}
                 status = ops.device_status()
                 assert status[0] == 0, f"device-side wait ran out: {status}"
+                # the same gather by the copy engines: the GEMM in row panels, each finished panel pushed
+                # into every rank's [M, N] buffer by one 2-D DMA copy per destination
+                progress("all-gather by the copy engines, panel by panel")
+                del po
+                pg = shard.PanelGather(m, n, torch.bfloat16, dev, panels=8)
+
+                def ce_step():
+                    ops.quant_fp8_per_token_group(x, 128, aq, a_s)
+                    pg(aq, a_s, bq, bs)
+
+                for _ in range(2):
+                    ce_step()
+                sync_all()
+                g0.record(stream)
+                for _ in range(args.steps):
+                    ce_step()
+                g1.record(stream)
+                torch.cuda.synchronize()
+                tc = max_over_ranks(g0.elapsed_time(g1) * 1e-3 / args.steps)
+                same_ce = all(torch.equal(pg.out.local[:, r * n_loc:(r + 1) * n_loc], blocked[r]) for r in range(world))
+                gather["copy_engine_panels"] = {"ms_per_step": tc * 1e3, "value": flops_total / tc / 1e12, "panels": pg.panels,
+                                                "layout": "[M][N] row-major on every rank", "equals_nccl_gather": bool(same_ce),
+                                                "link_gbs_out_per_rank": 2 * m * n_loc * (world - 1) / tc / 1e9}
+                best = min((("nccl_after_gemm", tg), ("nccl_panel_pipelined", tp), ("gemm_epilogue_peer_stores", tf),
+                            ("copy_engine_panels", tc)), key=lambda kv: kv[1])
+                gather["fastest_form"] = best[0]
+                del pg
+                po = None
             else:
                 gather["fused"] = {"unavailable": peer_error or "peer mapping failed on another rank"}
             del c_all, po

@@ -159,6 +159,15 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm_scatter(void* const* slot_peers, int
 INFEROP_API int inferop_reduce_slots(void* out, int32_t out_dt, const void* slots, int32_t n_peers, int64_t rows,
                          int64_t n, void* stream);
 
+/* 2-D copy by the copy engines (cudaMemcpy2DAsync, device to device, peer-mapped addresses
+ * allowed): `rows` rows of width_bytes from src (row pitch src_pitch_bytes) to dst (row pitch
+ * dst_pitch_bytes), enqueued on `stream`.  No counterpart in the reference (it has no multi-GPU
+ * code); used to push finished row panels of a column shard's result into every rank's [M, N]
+ * buffer while the tensor cores work on the next panel, without taking SMs or epilogue time
+ * from the GEMM. */
+INFEROP_API int inferop_copy_2d_async(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes,
+                          int64_t width_bytes, int64_t rows, void* stream);
+
 /* ---- mixture-of-experts layer around the grouped GEMM
  * Every step stays on the device: the experts' row counts are never copied to the host, the
  * grouped GEMM reads the M-tile list that inferop_moe_align wrote.  The steps of a layer:
@@ -215,6 +224,15 @@ INFEROP_API int inferop_moe_align(const int32_t* topk_ids, int64_t tokens, int32
 INFEROP_API int inferop_moe_scatter_quant(void* q, void* scales, const void* x, int32_t dt, const int32_t* pos,
                               int64_t tokens, int64_t cols, int32_t topk, int32_t group_size,
                               void* stream);
+
+/* Rows of row_bytes bytes (a multiple of 16; dst and src 16-byte aligned) moved by a permutation
+ * held in device memory: gather == 0: dst[perm[i]] = src[i]; gather != 0: dst[i] = src[perm[i]];
+ * i in [0, rows), rows with perm[i] < 0 are skipped.  No counterpart in the reference; an
+ * expert-parallel layer uses it to put the rows it received from the other ranks into
+ * expert-sorted order (perm = the pos array of inferop_moe_align over the received expert ids)
+ * and to put the experts' outputs back into arrival order for the way home. */
+INFEROP_API int inferop_moe_permute_rows(void* dst, const void* src, const int32_t* perm, int64_t rows,
+                             int64_t row_bytes, int32_t gather, void* stream);
 
 /* out[t, :] = sum_k topk_weights[t, k] * y[pos[t * topk + k], :] for y [tokens * topk, hidden]
  * and out [tokens, hidden] in dt (1 fp16 / 2 bf16): products and sums in fp32, each rounded, in

@@ -445,6 +445,19 @@ int inferop_reduce_slots(void* out, int32_t out_dt, const void* slots, int32_t n
                              ctx->sm_count);
 }
 
+int inferop_copy_2d_async(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes,
+                          int64_t width_bytes, int64_t rows, void* stream) {
+  if (width_bytes <= 0 || rows <= 0 || dst_pitch_bytes < width_bytes || src_pitch_bytes < width_bytes) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (!dst || !src) return INFEROP_ERR_POINTER;
+  const cudaError_t e = cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_pitch_bytes), src,
+                                          static_cast<size_t>(src_pitch_bytes), static_cast<size_t>(width_bytes),
+                                          static_cast<size_t>(rows), cudaMemcpyDeviceToDevice,
+                                          static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? INFEROP_OK : note_cuda_error(e);
+}
+
 int inferop_topk_softmax(int32_t* topk_ids, void* topk_weights, const void* logits, int32_t tokens,
                          int32_t num_experts, int32_t topk, int32_t renormalize, void* stream) {
   if (tokens <= 0 || num_experts <= 0 || num_experts > 1024 || topk <= 0 || topk > num_experts) {
@@ -517,6 +530,18 @@ int inferop_moe_scatter_quant(void* q, void* scales, const void* x, int32_t dt, 
   if (!ctx) return err;
   return launch_moe_scatter_quant(q, scales, x, dt, pos, tokens, cols, topk,
                                   static_cast<cudaStream_t>(stream), ctx->sm_count);
+}
+
+int inferop_moe_permute_rows(void* dst, const void* src, const int32_t* perm, int64_t rows, int64_t row_bytes,
+                             int32_t gather, void* stream) {
+  if (rows <= 0 || row_bytes <= 0 || row_bytes % 16 != 0) return INFEROP_ERR_SHAPE;
+  if (!dst || !src || !perm) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(dst) & 15u) || (reinterpret_cast<uintptr_t>(src) & 15u)) return INFEROP_ERR_POINTER;
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_permute_rows(dst, src, perm, rows, row_bytes, gather ? 1 : 0, static_cast<cudaStream_t>(stream),
+                             ctx->sm_count);
 }
 
 int inferop_moe_combine(void* out, const void* y, const void* topk_weights, const int32_t* pos, int32_t dt,

@@ -131,6 +131,8 @@ int launch_moe_align(const int32_t* ids, int64_t tokens, int32_t topk, int32_t e
                      int32_t* tile_meta, int32_t* num_mtiles, cudaStream_t stream);
 int launch_moe_scatter_quant(void* q, void* scales, const void* x, int32_t dt, const int32_t* pos,
                              int64_t tokens, int64_t cols, int32_t topk, cudaStream_t stream, int sms);
+int launch_permute_rows(void* dst, const void* src, const int32_t* perm, int64_t rows, int64_t row_bytes,
+                        int32_t gather, cudaStream_t stream, int sms);
 int launch_moe_combine(void* out, const void* y, const float* w, const int32_t* pos, int32_t dt,
                        int64_t tokens, int64_t hidden, int32_t topk, cudaStream_t stream, int sms);
 

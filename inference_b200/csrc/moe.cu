@@ -528,6 +528,41 @@ int launch_moe_scatter_quant(void* q, void* scales, const void* x, int32_t dt, c
   return check_launch();
 }
 
+namespace {
+// Rows of row_bytes bytes moved by a permutation: scatter (dst[perm[i]] = src[i]) or gather
+// (dst[i] = src[perm[i]]); rows with perm < 0 are skipped.  16 bytes per thread and step.
+// Expert-parallel layers use it to bring rows received from other ranks into expert-sorted
+// order and the experts' outputs back into the order they arrived in.
+template <bool kGather>
+__global__ void __launch_bounds__(kThreads)
+permute_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, const int32_t* __restrict__ perm,
+                    int64_t rows, int64_t vec_per_row) {
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
+    const int64_t pr = __ldg(perm + r);
+    if (pr < 0) continue;
+    if (kGather) dst[i] = __ldg(src + pr * vec_per_row + c);
+    else dst[pr * vec_per_row + c] = __ldg(src + i);
+  }
+}
+}  // namespace
+
+int launch_permute_rows(void* dst, const void* src, const int32_t* perm, int64_t rows, int64_t row_bytes,
+                        int32_t gather, cudaStream_t stream, int sms) {
+  const int64_t vec = row_bytes / 16;
+  const int grid = grid_for((rows * vec + kThreads - 1) / kThreads, sms, 8);
+  if (gather) {
+    permute_rows_kernel<true><<<grid, kThreads, 0, stream>>>(static_cast<uint4*>(dst), static_cast<const uint4*>(src),
+                                                             perm, rows, vec);
+  } else {
+    permute_rows_kernel<false><<<grid, kThreads, 0, stream>>>(static_cast<uint4*>(dst), static_cast<const uint4*>(src),
+                                                              perm, rows, vec);
+  }
+  return check_launch();
+}
+
 int launch_moe_combine(void* out, const void* y, const float* w, const int32_t* pos, int32_t dt,
                        int64_t tokens, int64_t hidden, int32_t topk, cudaStream_t stream, int sms) {
   const int64_t h8 = hidden / 8;

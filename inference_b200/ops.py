@@ -206,6 +206,17 @@ def w8a8_block_fp8_gemm_scatter(slot_ptrs, rank: int, a_q: torch.Tensor, a_scale
               "w8a8_block_fp8_gemm_scatter")
 
 
+def copy_2d_async(dst_ptr: int, dst_pitch_bytes: int, src: torch.Tensor, stream=None) -> None:
+    """Copy the 2-D tensor `src` (rows contiguous) to the device address dst_ptr with row pitch
+    dst_pitch_bytes, by the copy engines, on `stream`.  dst_ptr may be a peer-mapped address."""
+    _dev_tensor(src, "src")
+    rows, cols = src.shape
+    width = cols * src.element_size()
+    with torch.cuda.device(src.device):
+        check(lib.inferop_copy_2d_async(int(dst_ptr), int(dst_pitch_bytes), src.data_ptr(), width, width, rows,
+                                        _stream_ptr(stream)), "copy_2d_async")
+
+
 def reduce_slots(slots: torch.Tensor, out_dtype=torch.bfloat16, out: torch.Tensor | None = None,
                  stream=None) -> torch.Tensor:
     """slots fp32 [G, rows, N] -> out [rows, N]: the sum over G in order, rounded once."""
@@ -312,6 +323,23 @@ def moe_scatter_quant(x: torch.Tensor, layout: MoeLayout, q: torch.Tensor | None
                                             int(_TORCH2CODE[x.dtype]), layout.pos.data_ptr(), tokens, cols,
                                             layout.topk, 128, _stream_ptr(stream)), "moe_scatter_quant")
     return q, scales
+
+
+def moe_permute_rows(src: torch.Tensor, perm: torch.Tensor, dst: torch.Tensor, gather: bool, stream=None) -> torch.Tensor:
+    """gather: dst[i] = src[perm[i]]; else dst[perm[i]] = src[i] (rows with perm < 0 skipped).
+    src / dst are 2-D with the same row size in bytes (a multiple of 16); perm int32 with one
+    entry per row of the side that is walked in order (dst for gather, src for scatter)."""
+    _dev_tensor(src, "src")
+    _dev_tensor(dst, "dst")
+    _dev_tensor(perm, "perm")
+    row_bytes = src.shape[1] * src.element_size()
+    if perm.dtype != torch.int32 or dst.shape[1] * dst.element_size() != row_bytes:
+        raise ValueError("perm must be int32 and src / dst rows must have the same size")
+    rows = perm.numel()
+    with torch.cuda.device(src.device):
+        check(lib.inferop_moe_permute_rows(dst.data_ptr(), src.data_ptr(), perm.data_ptr(), rows, row_bytes,
+                                           1 if gather else 0, _stream_ptr(stream)), "moe_permute_rows")
+    return dst
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor, layout: MoeLayout, out: torch.Tensor | None = None,

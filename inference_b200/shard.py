@@ -93,6 +93,52 @@ class PeerOutput:
             dist.all_reduce(self._flag, group=self.group)
 
 
+class PanelGather:
+    """Column-parallel GEMM whose result reaches every rank's row-major [M, N] buffer through the
+    copy engines: the GEMM runs in row panels, and as soon as a panel of this rank's [M, N/G]
+    result is complete, one 2-D copy per destination (a stream per destination, destinations
+    rotated so that the ranks do not all target the same GPU at once) pushes it over NVLink into
+    columns [rank N/G, (rank + 1) N/G) of that rank's buffer while the tensor cores work on the
+    next panel.  Peer STORES by DMA only: no SM and no epilogue time of the GEMM is spent on the
+    transfer, and nothing is loaded from another GPU.  The ranks meet once at the end."""
+
+    def __init__(self, m: int, n_total: int, dtype=torch.bfloat16, device=None, group=None, panels: int = 8):
+        self.out = PeerOutput(m, n_total, dtype, device, group)
+        self.world, self.rank = self.out.world, self.out.rank
+        self.m, self.n_total = m, n_total
+        self.n_loc = n_total // self.world
+        while panels > 1 and m % (panels * BLOCK) != 0:
+            panels //= 2
+        self.panels = panels
+        self.rows = m // panels
+        self.c_local = torch.empty((m, self.n_loc), dtype=dtype, device=device)
+        self.streams = [torch.cuda.Stream(device) for _ in range(self.world)]
+        self.events = [torch.cuda.Event() for _ in range(panels)]
+        self.elem = self.c_local.element_size()
+
+    def __call__(self, a_q, a_scales, b_q, b_scales) -> torch.Tensor:
+        """Enqueue GEMM + gather; returns this rank's full [M, N] buffer (complete on the current
+        stream once the call's last enqueued operation, the meeting of the ranks, has run)."""
+        from . import ops
+        cur = torch.cuda.current_stream()
+        pitch = self.n_total * self.elem
+        for st in self.streams:
+            st.wait_stream(cur)          # the previous step's readers of the destination buffers are done
+        for p in range(self.panels):
+            r0, r1 = p * self.rows, (p + 1) * self.rows
+            ops.w8a8_block_fp8_gemm(a_q[r0:r1], a_scales[r0:r1], b_q, b_scales, out=self.c_local[r0:r1])
+            self.events[p].record(cur)
+            for i, st in enumerate(self.streams):
+                d = (self.rank + 1 + i) % self.world       # own buffer last
+                st.wait_event(self.events[p])
+                dst = self.out.ptrs[d] + (r0 * self.n_total + self.rank * self.n_loc) * self.elem
+                ops.copy_2d_async(dst, pitch, self.c_local[r0:r1], stream=st)
+        for st in self.streams:
+            cur.wait_stream(st)
+        self.out.barrier()
+        return self.out.local
+
+
 # ----------------------------------------------------------------------------- row-parallel (K shards)
 def k_shard_bounds(k: int, world: int, rank: int) -> tuple[int, int]:
     """Columns [lo, hi) of A_q / B_q owned by `rank` when K is split; whole 128-wide scale groups."""

@@ -42,6 +42,17 @@ def main() -> int:
                 bad = (out.local != want).nonzero()
                 print(f"rank {rank}: {m}x{n}x{k} rep {rep}: {bad.shape[0]} elements differ, first {bad[0].tolist()}",
                       flush=True)
+        # the same gather done by the copy engines, panel by panel
+        pg = shard.PanelGather(m, n, torch.bfloat16, dev, panels=4)
+        for rep in range(2):
+            pg.out.local.fill_(float(rep))
+            pg.out.barrier()
+            got = pg(a_q, a_s, wq, ws)
+            torch.cuda.synchronize()
+            same = torch.equal(got, want)
+            ok &= same
+            if not same:
+                print(f"rank {rank}: panel gather {m}x{n}x{k} rep {rep} differs", flush=True)
         assert ops.device_status()[0] == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

@@ -105,6 +105,21 @@ def test_only_the_ranks_own_columns_are_written(ops):
         assert not bool((b[:, lo:hi] == 3.0).all())
 
 
+def test_panel_gather_by_the_copy_engines_on_one_rank_equals_the_plain_gemm(ops):
+    """Without a process group the gather degrades to one destination (this rank's own buffer):
+    panels of the GEMM copied in by the copy engines must reproduce the plain GEMM."""
+    from inference_b200 import shard
+    for (m, n, k, panels) in [(1024, 384, 512, 8), (256, 1152, 1024, 2), (130, 256, 256, 8)]:
+        aq, a_s, bq, bs = [cuda(t) for t in case(m, n, k, seed=m + n)]
+        want = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs)
+        pg = shard.PanelGather(m, n, torch.bfloat16, "cuda", panels=panels)
+        for _ in range(2):
+            got = pg(aq, a_s, bq, bs)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want)
+    assert ops.device_status()[0] == 0
+
+
 def test_rejected_calls(ops):
     from inference_b200._capi import InferopError
     aq, a_s, bq, bs = case(64, 256, 256, seed=1)
