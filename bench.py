@@ -77,7 +77,7 @@ def parse_args():
     ap.add_argument("--gather", action="store_true",
                     help="(default for N > 1) also time the all-gather of C: NCCL, and the GEMM's own epilogue")
     ap.add_argument("--no-gather", action="store_true", help="skip the all-gather measurements")
-    ap.add_argument("--collective-seconds", type=int, default=180,
+    ap.add_argument("--collective-seconds", type=int, default=300,
                     help="deadline for the collective sections (N > 1); the main result is printed without them after it")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the decode / prefill shape sweep (N=1 only)")
@@ -641,6 +641,70 @@ def row_parallel_bench(args, world, rank, dev, max_over_ranks, sync_all, m=M_FUL
     return res
 
 
+def moe_ep_bench(args, world, rank, dev, max_over_ranks, sync_all, experts=256, hidden=7168, inter=2048,
+                 tokens_total=4096, topk=8):
+    """The MoE configuration sharded expert-parallel: every rank owns experts / G experts and
+    tokens_total / G tokens; FP8 rows travel to the experts' owners and bf16 results back over
+    NCCL all-to-all.  Timed: the whole layer per rank (max over ranks); checked: rank 0's output
+    against the single-device layer on the same tokens (bit for bit)."""
+    import torch
+    import torch.distributed as dist
+    from inference_b200 import synth
+    from inference_b200.expert_parallel import ExpertParallelMoE, expert_bounds
+    from inference_b200.moe import MoEFP8Layer
+    if experts % (32 * world) or tokens_total % world:
+        return {"unavailable": "experts / tokens do not split over the ranks"}
+    lo, hi = expert_bounds(experts, world, rank)
+    tokens = tokens_total // world
+
+    def weights(e0, e1, n, k, seed):
+        bq = torch.empty((e1 - e0, n, k), dtype=torch.uint8, device=dev)
+        bs = torch.empty((e1 - e0, n // 128, k // 128), dtype=torch.float32, device=dev)
+        for c0 in range(e0, e1, 32):     # chunks of 32 experts, seeded by the first expert of the chunk
+            q, s_ = synth.quantised_weights(32 * n, k, seed=seed + c0, device=dev)
+            bq[c0 - e0:c0 - e0 + 32] = q.view(32, n, k)
+            bs[c0 - e0:c0 - e0 + 32] = s_.view(32, n // 128, k // 128)
+            del q, s_
+        return bq, bs
+
+    wgu, sgu = weights(lo, hi, 2 * inter, hidden, 300)
+    wd, sd = weights(lo, hi, hidden, inter, 700)
+    layer = ExpertParallelMoE(wgu, sgu, wd, sd, experts, topk, world, rank)
+    x = synth.activations(tokens, hidden, seed=50 + rank, device=dev)
+    g = torch.Generator(device="cpu").manual_seed(60 + rank)
+    logits = torch.randn((tokens, experts), generator=g).to(dev)
+    out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
+    for _ in range(2):
+        layer.forward(x, logits, out)
+    sync_all()
+    stream = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters = max(3, min(args.steps, 10))
+    e0.record(stream)
+    for _ in range(iters):
+        layer.forward(x, logits, out)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t = max_over_ranks(e0.elapsed_time(e1) * 1e-3 / iters)
+    pairs = tokens_total * topk
+    flops = 2.0 * pairs * hidden * (2 * inter) + 2.0 * pairs * inter * hidden
+    res = {"experts": experts, "experts_per_rank": hi - lo, "tokens_total": tokens_total, "tokens_per_rank": tokens, "topk": topk,
+           "layer_ms": t * 1e3, "tflops": flops / t / 1e12,
+           "bytes_sent_per_rank_estimate": tokens * topk * (world - 1) // world * (hidden + hidden // 32 + 4 + 2 * hidden),
+           "exchange": "NCCL all_to_all_single: FP8 rows + scales + ids out, bf16 rows back; one host copy of the row counts per call"}
+    del wgu, sgu, wd, sd, layer
+    torch.cuda.empty_cache()
+    if rank == 0:
+        # the single-device layer with all experts on rank 0's tokens: the expert-parallel result must equal it
+        fgu, fsgu = weights(0, experts, 2 * inter, hidden, 300)
+        fd, fsd = weights(0, experts, hidden, inter, 700)
+        want = MoEFP8Layer(fgu, fsgu, fd, fsd, topk, tokens).forward(x, logits)
+        res["equals_single_device_layer"] = bool(torch.equal(out, want))
+        del fgu, fsgu, fd, fsd, want
+        torch.cuda.empty_cache()
+    return res
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def run_ours(args):
     import torch
@@ -934,6 +998,8 @@ def run_ours(args):
         if world > 1 and not args.no_gather:
             progress("row-parallel partner")
             row_parallel = row_parallel_bench(args, world, rank, dev, max_over_ranks, sync_all)
+            progress("expert-parallel MoE layer")
+            row_parallel = {"row_parallel": row_parallel, "moe_ep": moe_ep_bench(args, world, rank, dev, max_over_ranks, sync_all)}
             progress("collective sections done")
         return gather, row_parallel
 
@@ -969,7 +1035,8 @@ def run_ours(args):
         if gather:
             line["gather"] = gather
         if row_parallel:
-            line["row_parallel"] = row_parallel
+            line["row_parallel"] = row_parallel["row_parallel"]
+            line["moe_ep"] = row_parallel["moe_ep"]
     if world == 1 and not args.no_sweep:
         del x, bq, bs, aq, a_s, c
         torch.cuda.empty_cache()
