@@ -79,8 +79,22 @@ INFEROP_API int inferop_dequant_fp8_per_token_group(void* x, int32_t dt, const v
  * (INFEROP_ERR_POINTER otherwise); c may have any alignment and N any value.
  * Calls with few tokens (M <= 32, and M <= 64 when ceil(N/128) is below 3/4 of the SM count)
  * take a weight-streaming kernel that keeps a library-owned scratch
- * buffer (about 10 MB) per stream; it is allocated by the first such call on a stream, so
- * make that call before capturing the stream into a CUDA graph. */
+ * buffer (about 19 MB) per stream; it is allocated by the first such call on a stream, so
+ * make that call before capturing the stream into a CUDA graph (up to 64 streams per device
+ * get scratch; calls on further streams are served by the large-tile kernel).  Calls with
+ * M > 128 take the CTA-pair kernel (clusters of two CTAs, tcgen05.mma.cta_group::2).
+ *
+ * Programmatic dependent launch: the weight-streaming and the CTA-pair kernels are launched
+ * with programmatic stream serialisation and may start their set-up while the kernel queued
+ * before them on the stream is still running; the weight-streaming kernel also requests its
+ * first weight tiles (b_q) before it waits for that kernel.  a_q, a_scales and c are touched
+ * only after the wait.  So b_q and b_scales must not be PRODUCED by the kernel queued
+ * immediately before the call if that kernel triggers its dependents early
+ * (griddepcontrol.launch_dependents), as this library's quantiser does; weights written by an
+ * ordinary kernel, a copy, or anything earlier on the stream are fine.  A caller that rewrites
+ * weights with such a kernel right before the GEMM sets the options "decode_pdl" and
+ * "gemm_pdl" to 0 (inferop_set_option).  The same holds for the fused-quant, all-gather,
+ * strided-output and fixed-scratch entry points. */
 INFEROP_API int inferop_w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_scales, const void* b_q,
                                 const void* b_scales, int64_t m, int64_t n, int64_t k,
                                 int32_t group_size, int32_t block_n, int32_t out_dt,
@@ -158,6 +172,15 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm_scatter(void* const* slot_peers, int
                                         int32_t group_size, int32_t block_n, void* stream);
 INFEROP_API int inferop_reduce_slots(void* out, int32_t out_dt, const void* slots, int32_t n_peers, int64_t rows,
                          int64_t n, void* stream);
+
+/* inferop_w8a8_block_fp8_gemm (reference include/inferop/ops.h:81-84) with a strided output: the
+ * [M, N] result goes to columns [col0, col0 + N) of a row-major buffer c_base with ldc columns
+ * (out_dt 1 fp16 / 2 bf16; N % 128 == 0; col0 and ldc multiples of 8; c_base 16-byte aligned).
+ * A column shard's GEMM can so write straight into its place in the full [M, N_total] result. */
+INFEROP_API int inferop_w8a8_block_fp8_gemm_into(void* c_base, int64_t ldc, int64_t col0, const void* a_q,
+                                     const void* a_scales, const void* b_q, const void* b_scales, int64_t m,
+                                     int64_t n, int64_t k, int32_t group_size, int32_t block_n, int32_t out_dt,
+                                     void* stream);
 
 /* 2-D copy by the copy engines (cudaMemcpy2DAsync, device to device, peer-mapped addresses
  * allowed): `rows` rows of width_bytes from src (row pitch src_pitch_bytes) to dst (row pitch
@@ -278,12 +301,14 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm_grouped_tiles_swiglu(void* q, void* 
  * synchronisation).  Same arguments, contract and results as inferop_w8a8_block_fp8_gemm,
  * restricted to M <= 32, N <= 524288 and devices with at most 160 SMs (INFEROP_ERR_LIMIT
  * beyond).  The scratch the small-M kernel needs for split tiles is a fixed array of about
- * 2.6 MB inside the library image, resident on every GPU that loads the library until the
+ * 5.3 MB inside the library image, resident on every GPU that loads the library until the
  * process exits; this call uses cudaMalloc, cudaFree and allocating library routines nowhere.
  * The first call on a device looks the array's device address up (once per device, with
  * that device current); make that first call before any stream capture.  All calls on a
  * device share the array: calls that can overlap on the GPU (different streams) race on it
- * and must be ordered by the caller. */
+ * and must be ordered by the caller.  If a wait inside the kernel ever runs out, the record is
+ * kept inside the same array and inferop_device_status (which allocates nothing either)
+ * reports and resets it. */
 INFEROP_API int inferop_w8a8_block_fp8_gemm_fixed_scratch(void* c, const void* a_q, const void* a_scales,
                                               const void* b_q, const void* b_scales, int64_t m,
                                               int64_t n, int64_t k, int32_t group_size,
@@ -292,8 +317,14 @@ INFEROP_API int inferop_w8a8_block_fp8_gemm_fixed_scratch(void* c, const void* a
 /* ---- diagnostics
  * Synchronises the current device and copies out the device-side status record
  * {code, block, aux0, aux1}.  code == 0 means no bounded wait has run out since
- * the last reset.  Returns INFEROP_OK, INFEROP_ERR_DEVICE_WAIT (record non-zero)
- * or INFEROP_ERR_CUDA.  `out4` (host, 4 x uint32) may be NULL. */
+ * the last reset.  Two records exist per device: the one of the library-owned context (all
+ * entry points but one) and the one inside the fixed scratch array of
+ * inferop_w8a8_block_fp8_gemm_fixed_scratch; whichever is non-zero is reported (the context's
+ * first), both are reset when `reset` is set.  The call itself allocates nothing.  Returns
+ * INFEROP_OK, INFEROP_ERR_DEVICE_WAIT (record non-zero) or INFEROP_ERR_CUDA.  `out4` (host,
+ * 4 x uint32) may be NULL.
+ * Options that concern the waits (inferop_set_option): "wait_budget_us": how long a wait may
+ * last before it gives up (0 = default, about a second), kept per device beside the record. */
 INFEROP_API int inferop_device_status(uint32_t* out4, int reset);
 
 /* Self-test of the hardware fp32 -> E4M3 converter used by the quantiser against the

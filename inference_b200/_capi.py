@@ -35,6 +35,8 @@ SIGNATURES = {
     "inferop_w8a8_block_fp8_gemm_scatter": (C.c_int, [C.POINTER(_vp), _i32, _i32, _vp, _vp, _vp, _vp, _i64, _i64,
                                                       _i64, _i32, _i32, _vp]),
     "inferop_reduce_slots": (C.c_int, [_vp, _i32, _vp, _i32, _i64, _i64, _vp]),
+    "inferop_w8a8_block_fp8_gemm_into": (C.c_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32,
+                                                   _vp]),
     "inferop_copy_2d_async": (C.c_int, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "inferop_topk_softmax": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "inferop_silu_and_mul": (C.c_int, [_vp, _vp, _i32, _i64, _i64, _vp]),

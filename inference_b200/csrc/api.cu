@@ -412,6 +412,35 @@ int inferop_w8a8_block_fp8_gemm_allgather(void* const* c_peers, int32_t n_peers,
                                out_dt, s);
 }
 
+int inferop_w8a8_block_fp8_gemm_into(void* c_base, int64_t ldc, int64_t col0, const void* a_q, const void* a_scales,
+                                     const void* b_q, const void* b_scales, int64_t m, int64_t n, int64_t k,
+                                     int32_t group_size, int32_t block_n, int32_t out_dt, void* stream) {
+  if (group_size != 128 || block_n != 128 || k <= 0 || k % 128 != 0 || m <= 0 || n <= 0 || n % 128 != 0 ||
+      ldc <= 0 || col0 < 0 || col0 + n > ldc || col0 % 8 != 0 || ldc % 8 != 0) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (out_dt != 1 && out_dt != 2) return INFEROP_ERR_DTYPE;
+  if (m > 0x7FFFFF00LL || ldc > 0x7FFFFF00LL || k > 0x7FFFFF00LL) return INFEROP_ERR_LIMIT;
+  if (!c_base || !a_q || !a_scales || !b_q || !b_scales) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(a_q) & 15u) || (reinterpret_cast<uintptr_t>(b_q) & 15u) ||
+      (reinterpret_cast<uintptr_t>(c_base) & 15u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (small_m_kernel(ctx, m, n)) {
+    float* ws;
+    int* counters;
+    if (decode_scratch(ctx, s, &ws, &counters)) {
+      void* dst[1] = {c_base};
+      return launch_gemm_decode_to(ctx, ws, counters, dst, 1, ldc, col0, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
+    }
+  }
+  return launch_gemm_into(ctx, c_base, ldc, col0, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, s);
+}
+
 int inferop_w8a8_block_fp8_gemm_scatter(void* const* slot_peers, int32_t n_peers, int32_t rank,
                                         const void* a_q, const void* a_scales, const void* b_q,
                                         const void* b_scales, int64_t m, int64_t n, int64_t k,

@@ -967,23 +967,13 @@ int launch_gemm_grouped(DeviceCtx* ctx, void* c, const void* a_q, const void* a_
   return flush(count);
 }
 
-int launch_gemm_allgather(DeviceCtx* ctx, void* const* c_peers, int32_t n_peers, int32_t rank,
-                          const void* a_q, const void* a_scales, const void* b_q,
-                          const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
-                          cudaStream_t stream) {
+// Shared by the all-gather launch and the strided-output launch: this call's [m, n] result goes
+// to columns [col_offset, col_offset + n) of `count` row-major two-byte buffers of n_total
+// columns each (dsts in the order the stores are issued).
+static int launch_gemm_to_wide(DeviceCtx* ctx, void* const* dsts, int count, int64_t n_total, int64_t col_offset,
+                               const void* a_q, const void* a_scales, const void* b_q, const void* b_scales,
+                               int64_t m, int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream) {
   const Options& opt = options();
-  if (out_dt != 1 && out_dt != 2) return INFEROP_ERR_DTYPE;
-  if (n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return INFEROP_ERR_SHAPE;
-  // a store box is 64 columns wide and must not reach into the next rank's columns; the weight
-  // scales of a shard are whole 128-row blocks
-  if (n % 128 != 0) return INFEROP_ERR_SHAPE;
-  const int64_t n_total = n * n_peers;
-  if (n_total > 0x7FFFFFFF) return INFEROP_ERR_LIMIT;
-  for (int d = 0; d < n_peers; ++d) {
-    if (c_peers[d] == nullptr) return INFEROP_ERR_POINTER;
-    if (reinterpret_cast<uintptr_t>(c_peers[d]) % 16 != 0) return INFEROP_ERR_POINTER;
-  }
-
   GemmParams p;
   p.a_scales = static_cast<const float*>(a_scales);
   p.b_scales = static_cast<const float*>(b_scales);
@@ -1011,18 +1001,48 @@ int launch_gemm_allgather(DeviceCtx* ctx, void* const* c_peers, int32_t n_peers,
   rc = make_tensor_map_2d(&mb, b_q, 1, n, k, k, BN, BK, true);
   if (rc != INFEROP_OK) return rc;
   static thread_local PeerMaps peers;
-  peers.count = n_peers;
-  peers.col_offset = static_cast<int>(rank * n);
-  for (int i = 0; i < n_peers; ++i) {
-    const int d = (rank + 1 + i) % n_peers;  // own buffer last
-    rc = make_tensor_map_2d(&peers.map[i], c_peers[d], 2, m, n_total, n_total * 2, 128, 64, true);
+  peers.count = count;
+  peers.col_offset = static_cast<int>(col_offset);
+  for (int i = 0; i < count; ++i) {
+    rc = make_tensor_map_2d(&peers.map[i], dsts[i], 2, m, n_total, n_total * 2, 128, 64, true);
     if (rc != INFEROP_OK) return rc;
   }
-  for (int i = n_peers; i < kMaxPeers; ++i) peers.map[i] = peers.map[0];
+  for (int i = count; i < kMaxPeers; ++i) peers.map[i] = peers.map[0];
   int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
   if (ctas > p.num_tiles) ctas = p.num_tiles;
   return out_dt == 1 ? launch_gather_t<__half>(ma, mb, p, peers, ctas, stream)
                      : launch_gather_t<__nv_bfloat16>(ma, mb, p, peers, ctas, stream);
+}
+
+int launch_gemm_allgather(DeviceCtx* ctx, void* const* c_peers, int32_t n_peers, int32_t rank,
+                          const void* a_q, const void* a_scales, const void* b_q,
+                          const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
+                          cudaStream_t stream) {
+  if (out_dt != 1 && out_dt != 2) return INFEROP_ERR_DTYPE;
+  if (n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return INFEROP_ERR_SHAPE;
+  // a store box is 64 columns wide and must not reach into the next rank's columns; the weight
+  // scales of a shard are whole 128-row blocks
+  if (n % 128 != 0) return INFEROP_ERR_SHAPE;
+  const int64_t n_total = n * n_peers;
+  if (n_total > 0x7FFFFFFF) return INFEROP_ERR_LIMIT;
+  void* dsts[kMaxPeers];
+  for (int i = 0; i < n_peers; ++i) {
+    dsts[i] = c_peers[(rank + 1 + i) % n_peers];   // own buffer last
+    if (dsts[i] == nullptr || reinterpret_cast<uintptr_t>(dsts[i]) % 16 != 0) return INFEROP_ERR_POINTER;
+  }
+  return launch_gemm_to_wide(ctx, dsts, n_peers, n_total, static_cast<int64_t>(rank) * n, a_q, a_scales, b_q,
+                             b_scales, m, n, k, out_dt, stream);
+}
+
+int launch_gemm_into(DeviceCtx* ctx, void* c_base, int64_t ldc, int64_t col0, const void* a_q,
+                     const void* a_scales, const void* b_q, const void* b_scales, int64_t m, int64_t n, int64_t k,
+                     int32_t out_dt, cudaStream_t stream) {
+  if (out_dt != 1 && out_dt != 2) return INFEROP_ERR_DTYPE;
+  if (n % 128 != 0 || col0 % 8 != 0 || ldc % 8 != 0 || col0 < 0 || col0 + n > ldc) return INFEROP_ERR_SHAPE;
+  if (ldc > 0x7FFFFFFF) return INFEROP_ERR_LIMIT;
+  if (c_base == nullptr || reinterpret_cast<uintptr_t>(c_base) % 16 != 0) return INFEROP_ERR_POINTER;
+  void* dsts[1] = {c_base};
+  return launch_gemm_to_wide(ctx, dsts, 1, ldc, col0, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, stream);
 }
 
 int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales,

@@ -91,6 +91,12 @@ int launch_gemm_allgather(DeviceCtx* ctx, void* const* c_peers, int32_t n_peers,
                           const void* b_scales, int64_t m, int64_t n, int64_t k, int32_t out_dt,
                           cudaStream_t stream);
 
+// Strided-output launch: the [m, n] result goes to columns [col0, col0 + n) of a row-major
+// two-byte buffer with ldc columns (n % 128 == 0, col0 and ldc multiples of 8).
+int launch_gemm_into(DeviceCtx* ctx, void* c_base, int64_t ldc, int64_t col0, const void* a_q,
+                     const void* a_scales, const void* b_q, const void* b_scales, int64_t m, int64_t n, int64_t k,
+                     int32_t out_dt, cudaStream_t stream);
+
 // Grouped launch whose M-tile list and its length live in device memory (written by moe_align);
 // max_mtiles bounds the list, m_total is the number of rows of a_q / c.
 int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales,

@@ -43,6 +43,28 @@ def _dev_tensor(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
+def _check_quantised(a_q, a_scales, b_q, b_scales, grouped: bool = False) -> None:
+    """Types and exact shapes of a quantised operand set: a mis-shaped scale tensor would make a
+    kernel read out of bounds on the device, so it is rejected here."""
+    if a_q.dtype != torch.uint8 or b_q.dtype != torch.uint8:
+        raise ValueError("a_q and b_q must be uint8 (E4M3 bytes)")
+    if a_scales.dtype != torch.float32 or b_scales.dtype != torch.float32:
+        raise ValueError("a_scales and b_scales must be fp32")
+    if a_q.dim() != 2 or b_q.dim() != (3 if grouped else 2):
+        raise ValueError("a_q must be [M, K] and b_q [N, K]" + (" per group: [G, N, K]" if grouped else ""))
+    m, k = a_q.shape
+    n = b_q.shape[-2]
+    if b_q.shape[-1] != k:
+        raise ValueError("a_q and b_q disagree on K")
+    if k % 128 != 0:
+        raise InferopError(_capi.ERR_SHAPE, "K must be a multiple of 128")
+    if tuple(a_scales.shape) != (m, k // 128):
+        raise ValueError(f"a_scales must be [M, K/128] = [{m}, {k // 128}], got {tuple(a_scales.shape)}")
+    want = ((b_q.shape[0],) if grouped else ()) + ((n + 127) // 128, k // 128)
+    if tuple(b_scales.shape) != want:
+        raise ValueError(f"b_scales must be {list(want)}, got {list(b_scales.shape)}")
+
+
 def has_cuda() -> bool:
     return bool(lib.inferop_has_cuda())
 
@@ -84,7 +106,11 @@ def dequant_fp8_per_token_group(q: torch.Tensor, scales: torch.Tensor, out_dtype
                                 group_size: int = 128, stream=None) -> torch.Tensor:
     _dev_tensor(q, "q")
     _dev_tensor(scales, "scales")
+    if q.dim() != 2 or q.dtype != torch.uint8 or scales.dtype != torch.float32:
+        raise ValueError("q must be a 2-D uint8 tensor and scales fp32")
     rows, cols = q.shape
+    if group_size <= 0 or cols % group_size != 0 or tuple(scales.shape) != (rows, cols // group_size):
+        raise ValueError("scales must be [rows, cols / group_size]")
     with torch.cuda.device(q.device):
         x = torch.empty((rows, cols), dtype=out_dtype, device=q.device)
         check(lib.inferop_dequant_fp8_per_token_group(x.data_ptr(), int(_TORCH2CODE[out_dtype]),
@@ -104,13 +130,14 @@ def w8a8_block_fp8_gemm(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: torch.Te
     """
     for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
         _dev_tensor(t, name)
+    _check_quantised(a_q, a_scales, b_q, b_scales)
     m, k = a_q.shape
     n = b_q.shape[0]
-    if b_q.shape[1] != k:
-        raise ValueError("a_q and b_q disagree on K")
     with torch.cuda.device(a_q.device):
         if out is None:
             out = torch.empty((m, n), dtype=out_dtype, device=a_q.device)
+        elif tuple(out.shape) != (m, n) or not out.is_contiguous():
+            raise ValueError("out must be a contiguous [M, N] tensor")
         check(lib.inferop_w8a8_block_fp8_gemm(out.data_ptr(), a_q.data_ptr(), a_scales.data_ptr(),
                                               b_q.data_ptr(), b_scales.data_ptr(), m, n, k, group_size,
                                               block_n, int(_TORCH2CODE[out.dtype]), _stream_ptr(stream)),
@@ -127,10 +154,13 @@ def w8a8_block_fp8_gemm_fused_quant(a: torch.Tensor, b_q: torch.Tensor, b_scales
     library-owned scratch.  Bit-identical to the two separate calls."""
     for t, name in ((a, "a"), (b_q, "b_q"), (b_scales, "b_scales")):
         _dev_tensor(t, name)
-    if a.dtype not in (torch.float16, torch.bfloat16):
-        raise ValueError("a must be fp16 or bf16")
+    if a.dtype not in (torch.float16, torch.bfloat16) or a.dim() != 2:
+        raise ValueError("a must be a 2-D fp16 or bf16 tensor")
     m, k = a.shape
     n = b_q.shape[0]
+    if b_q.dtype != torch.uint8 or b_q.dim() != 2 or b_q.shape[1] != k or b_scales.dtype != torch.float32 or \
+            k % 128 != 0 or tuple(b_scales.shape) != ((n + 127) // 128, k // 128):
+        raise ValueError("b_q must be uint8 [N, K] and b_scales fp32 [ceil(N/128), K/128]")
     with torch.cuda.device(a.device):
         if out is None:
             out = torch.empty((m, n), dtype=out_dtype, device=a.device)
@@ -151,6 +181,7 @@ def w8a8_block_fp8_gemm_grouped(a_q: torch.Tensor, a_scales: torch.Tensor, b_q: 
     """
     for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
         _dev_tensor(t, name)
+    _check_quantised(a_q, a_scales, b_q, b_scales, grouped=True)
     groups, n, k = b_q.shape
     counts = (C.c_int64 * groups)(*[int(v) for v in m_per_group])
     m_total = int(sum(counts))
@@ -179,6 +210,7 @@ def w8a8_block_fp8_gemm_allgather(peer_ptrs, rank: int, a_q: torch.Tensor, a_sca
     """
     for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
         _dev_tensor(t, name)
+    _check_quantised(a_q, a_scales, b_q, b_scales)
     m, k = a_q.shape
     n = b_q.shape[0]
     ptrs = (C.c_void_p * len(peer_ptrs))(*[int(p) for p in peer_ptrs])
@@ -196,6 +228,7 @@ def w8a8_block_fp8_gemm_scatter(slot_ptrs, rank: int, a_q: torch.Tensor, a_scale
     of the rank that owns the rows (slot_ptrs[d] = base of rank d's [G][M/G][N] fp32 slots)."""
     for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
         _dev_tensor(t, name)
+    _check_quantised(a_q, a_scales, b_q, b_scales)
     m, k = a_q.shape
     n = b_q.shape[0]
     ptrs = (C.c_void_p * len(slot_ptrs))(*[int(p) for p in slot_ptrs])
@@ -206,15 +239,35 @@ def w8a8_block_fp8_gemm_scatter(slot_ptrs, rank: int, a_q: torch.Tensor, a_scale
               "w8a8_block_fp8_gemm_scatter")
 
 
-def copy_2d_async(dst_ptr: int, dst_pitch_bytes: int, src: torch.Tensor, stream=None) -> None:
-    """Copy the 2-D tensor `src` (rows contiguous) to the device address dst_ptr with row pitch
-    dst_pitch_bytes, by the copy engines, on `stream`.  dst_ptr may be a peer-mapped address."""
-    _dev_tensor(src, "src")
-    rows, cols = src.shape
-    width = cols * src.element_size()
-    with torch.cuda.device(src.device):
-        check(lib.inferop_copy_2d_async(int(dst_ptr), int(dst_pitch_bytes), src.data_ptr(), width, width, rows,
-                                        _stream_ptr(stream)), "copy_2d_async")
+def w8a8_block_fp8_gemm_into(out: torch.Tensor, col0: int, a_q: torch.Tensor, a_scales: torch.Tensor,
+                             b_q: torch.Tensor, b_scales: torch.Tensor, stream=None) -> torch.Tensor:
+    """The GEMM with its [M, N] result written to columns [col0, col0 + N) of the wider row-major
+    tensor `out` [M, ldc] (fp16 / bf16, rows contiguous)."""
+    for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
+        _dev_tensor(t, name)
+    if not out.is_cuda or out.dim() != 2 or out.stride(1) != 1:
+        raise ValueError("out must be a 2-D CUDA tensor with contiguous rows")
+    _check_quantised(a_q, a_scales, b_q, b_scales)
+    m, k = a_q.shape
+    n = b_q.shape[0]
+    if out.shape[0] != m:
+        raise ValueError("out does not have M rows")
+    with torch.cuda.device(a_q.device):
+        check(lib.inferop_w8a8_block_fp8_gemm_into(out.data_ptr(), out.stride(0), int(col0), a_q.data_ptr(),
+                                                   a_scales.data_ptr(), b_q.data_ptr(), b_scales.data_ptr(), m, n, k,
+                                                   128, 128, int(_TORCH2CODE[out.dtype]), _stream_ptr(stream)),
+              "w8a8_block_fp8_gemm_into")
+    return out
+
+
+def copy_2d_async(dst_ptr: int, dst_pitch_bytes: int, src_ptr: int, src_pitch_bytes: int, width_bytes: int, rows: int,
+                  device, stream=None) -> None:
+    """`rows` rows of width_bytes from the device address src_ptr (row pitch src_pitch_bytes) to
+    dst_ptr (row pitch dst_pitch_bytes), by the copy engines, on `stream`.  Either address may
+    be peer-mapped."""
+    with torch.cuda.device(device):
+        check(lib.inferop_copy_2d_async(int(dst_ptr), int(dst_pitch_bytes), int(src_ptr), int(src_pitch_bytes),
+                                        int(width_bytes), int(rows), _stream_ptr(stream)), "copy_2d_async")
 
 
 def reduce_slots(slots: torch.Tensor, out_dtype=torch.bfloat16, out: torch.Tensor | None = None,
@@ -363,6 +416,7 @@ def w8a8_block_fp8_gemm_grouped_tiles(a_q: torch.Tensor, a_scales: torch.Tensor,
     """The grouped GEMM driven by the device-side tile list of a MoeLayout (no host round trip)."""
     for t, name in ((a_q, "a_q"), (a_scales, "a_scales"), (b_q, "b_q"), (b_scales, "b_scales")):
         _dev_tensor(t, name)
+    _check_quantised(a_q, a_scales, b_q, b_scales, grouped=True)
     groups, n, k = b_q.shape
     m_total = a_q.shape[0]
     with torch.cuda.device(a_q.device):
@@ -387,6 +441,7 @@ def w8a8_block_fp8_gemm_grouped_tiles_swiglu(a_q: torch.Tensor, a_scales: torch.
         _dev_tensor(t, name)
     if mid_dtype not in (torch.float16, torch.bfloat16):
         raise ValueError("mid_dtype must be fp16 or bf16")
+    _check_quantised(a_q, a_scales, b_q, b_scales, grouped=True)
     groups, n2, k = b_q.shape
     inter = n2 // 2
     m_total = a_q.shape[0]

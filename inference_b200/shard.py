@@ -95,11 +95,11 @@ class PeerOutput:
 
 class PanelGather:
     """Column-parallel GEMM whose result reaches every rank's row-major [M, N] buffer through the
-    copy engines: the GEMM runs in row panels, and as soon as a panel of this rank's [M, N/G]
-    result is complete, one 2-D copy per destination (a stream per destination, destinations
-    rotated so that the ranks do not all target the same GPU at once) pushes it over NVLink into
-    columns [rank N/G, (rank + 1) N/G) of that rank's buffer while the tensor cores work on the
-    next panel.  Peer STORES by DMA only: no SM and no epilogue time of the GEMM is spent on the
+    copy engines: the GEMM runs in row panels and writes each panel straight into its place in
+    this rank's own buffer (columns [rank N/G, (rank + 1) N/G)); as soon as a panel is complete,
+    one 2-D copy per other rank (a stream per destination, destinations rotated so that the ranks
+    do not all target the same GPU at once) pushes it over NVLink into the same place of that
+    rank's buffer while the tensor cores work on the next panel.  Peer STORES by DMA only: no SM and no epilogue time of the GEMM is spent on the
     transfer, and nothing is loaded from another GPU.  The ranks meet once at the end."""
 
     def __init__(self, m: int, n_total: int, dtype=torch.bfloat16, device=None, group=None, panels: int = 8):
@@ -111,10 +111,10 @@ class PanelGather:
             panels //= 2
         self.panels = panels
         self.rows = m // panels
-        self.c_local = torch.empty((m, self.n_loc), dtype=dtype, device=device)
-        self.streams = [torch.cuda.Stream(device) for _ in range(self.world)]
+        self.device = self.out.local.device
+        self.streams = [torch.cuda.Stream(self.device) for _ in range(max(self.world - 1, 0))]
         self.events = [torch.cuda.Event() for _ in range(panels)]
-        self.elem = self.c_local.element_size()
+        self.elem = self.out.local.element_size()
 
     def __call__(self, a_q, a_scales, b_q, b_scales) -> torch.Tensor:
         """Enqueue GEMM + gather; returns this rank's full [M, N] buffer (complete on the current
@@ -124,15 +124,17 @@ class PanelGather:
         pitch = self.n_total * self.elem
         for st in self.streams:
             st.wait_stream(cur)          # the previous step's readers of the destination buffers are done
+        col0 = self.rank * self.n_loc
         for p in range(self.panels):
             r0, r1 = p * self.rows, (p + 1) * self.rows
-            ops.w8a8_block_fp8_gemm(a_q[r0:r1], a_scales[r0:r1], b_q, b_scales, out=self.c_local[r0:r1])
+            ops.w8a8_block_fp8_gemm_into(self.out.local[r0:r1], col0, a_q[r0:r1], a_scales[r0:r1], b_q, b_scales)
             self.events[p].record(cur)
+            offset = (r0 * self.n_total + col0) * self.elem
             for i, st in enumerate(self.streams):
-                d = (self.rank + 1 + i) % self.world       # own buffer last
+                d = (self.rank + 1 + i) % self.world
                 st.wait_event(self.events[p])
-                dst = self.out.ptrs[d] + (r0 * self.n_total + self.rank * self.n_loc) * self.elem
-                ops.copy_2d_async(dst, pitch, self.c_local[r0:r1], stream=st)
+                ops.copy_2d_async(self.out.ptrs[d] + offset, pitch, self.out.ptrs[self.rank] + offset, pitch,
+                                  self.n_loc * self.elem, r1 - r0, self.device, stream=st)
         for st in self.streams:
             cur.wait_stream(st)
         self.out.barrier()

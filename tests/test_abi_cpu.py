@@ -122,3 +122,24 @@ def test_reference_cuda_baseline_library_exports_its_two_entry_points():
         pytest.skip("not built here (needs the reference tree)")
     lib = ctypes.CDLL(path)
     assert hasattr(lib, "refcuda_quant_fp8_per_token_group") and hasattr(lib, "refcuda_w8a8_block_fp8_gemm")
+
+
+def test_python_wrappers_reject_mistyped_or_misshaped_operands_before_the_c_call():
+    """A wrong scale shape would make a kernel read out of bounds; ops.py refuses it on the host."""
+    import torch
+    from inference_b200 import ops
+    m, n, k = 4, 256, 256
+    aq = torch.zeros((m, k), dtype=torch.uint8)
+    a_s = torch.zeros((m, k // 128))
+    bq = torch.zeros((n, k), dtype=torch.uint8)
+    bs = torch.zeros((n // 128, k // 128))
+    ops._check_quantised(aq, a_s, bq, bs)
+    for bad in [(aq.float(), a_s, bq, bs), (aq, a_s.double(), bq, bs), (aq, a_s[:, :1], bq, bs),
+                (aq, a_s, bq, bs[:1]), (aq, a_s, bq[:, :128], bs), (aq[0], a_s, bq, bs)]:
+        with pytest.raises((ValueError, ops.InferopError)):
+            ops._check_quantised(*bad)
+    ops._check_quantised(aq, a_s, bq.view(2, 128, k), bs.view(2, 1, k // 128), grouped=True)
+    with pytest.raises(ValueError):
+        ops._check_quantised(aq, a_s, bq.view(2, 128, k), bs, grouped=True)
+    with pytest.raises(ValueError):      # CUDA tensors are required
+        ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs)

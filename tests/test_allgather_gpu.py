@@ -105,6 +105,18 @@ def test_only_the_ranks_own_columns_are_written(ops):
         assert not bool((b[:, lo:hi] == 3.0).all())
 
 
+def test_strided_output_gemm_writes_only_its_column_block(ops):
+    for (m, n, k, ldc, col0) in [(300, 256, 512, 1024, 512), (130, 128, 256, 136, 8), (16, 384, 512, 1152, 768)]:
+        aq, a_s, bq, bs = [cuda(t) for t in case(m, n, k, seed=m + ldc)]
+        want = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs)
+        wide = torch.full((m, ldc), 5.0, dtype=torch.bfloat16, device="cuda")
+        ops.w8a8_block_fp8_gemm_into(wide, col0, aq, a_s, bq, bs)
+        torch.cuda.synchronize()
+        assert torch.equal(wide[:, col0:col0 + n], want)
+        assert bool((wide[:, :col0] == 5.0).all()) and bool((wide[:, col0 + n:] == 5.0).all())
+    assert ops.device_status()[0] == 0
+
+
 def test_panel_gather_by_the_copy_engines_on_one_rank_equals_the_plain_gemm(ops):
     """Without a process group the gather degrades to one destination (this rank's own buffer):
     panels of the GEMM copied in by the copy engines must reproduce the plain GEMM."""
