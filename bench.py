@@ -829,7 +829,7 @@ def run_ours(args):
     quant_bytes = 3 * m * k + 4 * m * (k // 128)
     achieved = gemm_flops / t_gemm_max / 1e12
     roofline = {
-        "bound": "tensor", "kernel": "w8a8_gemm_kernel", "achieved": achieved, "peak": fp8_peak,
+        "bound": "tensor", "kernel": "w8a8_pair_gemm_kernel", "achieved": achieved, "peak": fp8_peak,
         "unit": "TFLOP/s", "frac": achieved / fp8_peak,
         "peak_source": f"2 x bf16_tflops{'' if burst_basis else '_sustained'} of {peaks['source']} peaks (no measured FP8 figure; "
                        f"sampled SM clock {clk} MHz {'above' if burst_basis else 'at or below'} the sustained figure's 1290 MHz)",
