@@ -723,6 +723,10 @@ int inferop_set_option(const char* key, int64_t value) {
   } else if (!strcmp(key, "gemm_pair")) {
     if (value < -1 || value > 1) return INFEROP_ERR_SHAPE;
     o.gemm_pair = static_cast<int>(value);
+  } else if (!strcmp(key, "pdl_trigger")) {
+    o.pdl_trigger = value != 0;
+  } else if (!strcmp(key, "quant_pdl")) {
+    o.quant_pdl = value != 0;
   } else if (!strcmp(key, "gemm_pdl")) {
     o.gemm_pdl = value != 0;
   } else if (!strcmp(key, "gemm_ctas")) {

@@ -75,6 +75,7 @@ struct DecodeParams {
   int m, n, kb, n_tiles;
   long long units;         // n_tiles * kb
   int no_loads;            // test hook: the producer issues no load
+  int trigger;    // let kernels queued behind this one with programmatic stream serialisation start early
   DeviceStatus* status;
 };
 
@@ -204,6 +205,10 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_slot, 0);
+  // A kernel queued behind this one with programmatic stream serialisation (the quantiser of the
+  // next step, and behind it the next GEMM) may be launched from now on: it takes SMs as this
+  // grid's CTAs leave them and waits for this grid's completion before it touches memory.
+  if (p.trigger) pdl_launch_dependents();
 
   // This CTA's piece: tiles [t_first, ...) from K block kb_first, `count` units in all.  A unit
   // is one (weight tile, K block) pair = 16 KiB of weights.  Default: the n_tiles * kb units are
@@ -636,6 +641,7 @@ int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, vo
   p.n_tiles = static_cast<int>((n + TN - 1) / TN);
   p.units = static_cast<long long>(p.n_tiles) * p.kb;
   p.no_loads = options().debug_no_loads;
+  p.trigger = options().pdl_trigger;
   p.status = ctx->status;
   CUtensorMap mw;
   const int rc = make_tensor_map_2d(&mw, b_q, 1, n, k, k, TN, BK, true);
@@ -692,6 +698,7 @@ int launch_gemm_decode_to(DeviceCtx* ctx, float* workspace, int* counters, void*
   p.n_tiles = static_cast<int>((n + TN - 1) / TN);
   p.units = static_cast<long long>(p.n_tiles) * p.kb;
   p.no_loads = options().debug_no_loads;
+  p.trigger = options().pdl_trigger;
   p.status = ctx->status;
 
   CUtensorMap mw, ma;

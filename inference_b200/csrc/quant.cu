@@ -95,6 +95,10 @@ quant128_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, const T* __
   // a GEMM queued behind this kernel may begin its preamble (barriers, tensor memory, weight
   // prefetch); it waits for this kernel's completion before it reads q or scales
   pdl_launch_dependents();
+  // launched with programmatic stream serialisation this kernel may itself have started under the
+  // tail of the kernel before it (a GEMM that still reads q and scales, or the producer of x):
+  // nothing is read or written before that kernel has completed (a no-op after an ordinary launch)
+  pdl_wait();
   const int sub = threadIdx.x & 15;
   const int64_t hw = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 4;
   const int64_t hw_total = (static_cast<int64_t>(gridDim.x) * kThreads) >> 4;
@@ -282,12 +286,26 @@ int launch_quant(void* q, void* scales, const void* x, int32_t dt, int64_t rows,
   if (vec_ok) {
     const int64_t groups_per_block = (kThreads / 16) * kUnroll;
     const int grid = grid_for((groups + groups_per_block - 1) / groups_per_block, sms);
+    // programmatic stream serialisation: the launch itself may overlap the tail of the kernel
+    // queued before it when that kernel lets its dependents start early (the small-M GEMM does)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = options().quant_pdl ? 1 : 0;
+    cudaError_t e;
     switch (dt) {
-      case 0: quant128_kernel<float><<<grid, kThreads, 0, stream>>>(qp, sp, static_cast<const float*>(x), groups); break;
-      case 1: quant128_kernel<__half><<<grid, kThreads, 0, stream>>>(qp, sp, static_cast<const __half*>(x), groups); break;
-      case 2: quant128_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(qp, sp, static_cast<const __nv_bfloat16*>(x), groups); break;
+      case 0: e = cudaLaunchKernelEx(&cfg, quant128_kernel<float>, qp, sp, static_cast<const float*>(x), groups); break;
+      case 1: e = cudaLaunchKernelEx(&cfg, quant128_kernel<__half>, qp, sp, static_cast<const __half*>(x), groups); break;
+      case 2: e = cudaLaunchKernelEx(&cfg, quant128_kernel<__nv_bfloat16>, qp, sp, static_cast<const __nv_bfloat16*>(x), groups); break;
       default: return INFEROP_ERR_DTYPE;
     }
+    if (e != cudaSuccess) return note_cuda_error(e);
   } else {
     const int64_t groups_per_block = kThreads / 32;
     const int grid = grid_for((groups + groups_per_block - 1) / groups_per_block, sms);
