@@ -321,3 +321,47 @@ def test_fused_quant_prologue_limits(ops):
     assert lib.inferop_w8a8_block_fp8_gemm_fused_quant(p, p, 2, p, p, 4, 128 * 70000, 128, 128, 128, 2, None) == _capi.ERR_LIMIT
     assert lib.inferop_w8a8_block_fp8_gemm_fused_quant(p, p, 0, p, p, 4, 256, 128, 128, 128, 2, None) == _capi.ERR_DTYPE
     assert lib.inferop_w8a8_block_fp8_gemm_fused_quant(p, p, 2, p, p, 4, 256, 100, 128, 128, 2, None) == _capi.ERR_SHAPE
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 18432, 7168), (4, 24576, 1536), (64, 7168, 18432), (48, 18432, 7168)])
+def test_back_to_back_steps_share_buffers_without_a_race(ops, m, n, k):
+    """quant -> GEMM steps queued without a synchronisation, every step re-quantising different
+    activations into the SAME q / scales buffers that the previous step's GEMM reads: the
+    quantiser is launched with programmatic stream serialisation and may start under the tail of
+    the small-M GEMM, so it must not write before that GEMM has completed.  Every step's result
+    is compared with the same step run on its own."""
+    from inference_b200 import synth
+    bq, bs = synth.quantised_weights(n, k, seed=21)
+    xs = [synth.activations(m, k, seed=30 + i) for i in range(4)]
+    want = []
+    for x in xs:
+        aq, a_s = ops.quant_fp8_per_token_group(x)
+        want.append(ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs))
+        torch.cuda.synchronize()
+    aq = torch.empty((m, k), dtype=torch.uint8, device="cuda")
+    a_s = torch.empty((m, k // 128), dtype=torch.float32, device="cuda")
+    outs = [torch.empty((m, n), dtype=torch.bfloat16, device="cuda") for _ in range(24)]
+    for i, c in enumerate(outs):
+        ops.quant_fp8_per_token_group(xs[i % 4], 128, aq, a_s)
+        ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, out=c)
+    torch.cuda.synchronize()
+    assert ops.device_status()[0] == 0
+    for i, c in enumerate(outs):
+        assert torch.equal(c, want[i % 4]), f"step {i} differs from the same step run alone"
+    # the same chain replayed from a CUDA graph (programmatic edges are captured as such)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, out=outs[0])   # creates this stream's scratch before the capture
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i, c in enumerate(outs):
+                ops.quant_fp8_per_token_group(xs[i % 4], 128, aq, a_s)
+                ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, out=c)
+        for c in outs:
+            c.zero_()
+        g.replay()
+        g.replay()
+        torch.cuda.synchronize()
+    for i, c in enumerate(outs):
+        assert torch.equal(c, want[i % 4]), f"graph replay: step {i} differs"
