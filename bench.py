@@ -354,24 +354,30 @@ def shape_sweep(peaks):
             ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, out=c)
 
         side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            for _ in range(3):
-                step()           # warm-up; also creates this stream's GEMM scratch before capture
-            torch.cuda.synchronize()
-            reps = 10 if m <= 64 else 3
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                for _ in range(reps):
-                    step()
-            g.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(side)
-            for _ in range(3):
+        reps = 10 if m <= 64 else 3
+
+        def graph_time(fn):
+            """Seconds per call of fn, replayed from a CUDA graph of `reps` calls on the side stream."""
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    fn()         # warm-up; also creates this stream's GEMM scratch before capture
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(reps):
+                        fn()
                 g.replay()
-            e1.record(side)
-            torch.cuda.synchronize()
-        t = e0.elapsed_time(e1) * 1e-3 / (3 * reps)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(side)
+                for _ in range(3):
+                    g.replay()
+                e1.record(side)
+                torch.cuda.synchronize()
+            del g
+            return e0.elapsed_time(e1) * 1e-3 / (3 * reps)
+
+        t = graph_time(step)
         flops = 2.0 * m * n * k
         byt = 3 * m * k + 4 * m * (k // 128) + m * k + 4 * m * (k // 128) + n * k + 4 * (n // 128) * (k // 128) + 2 * m * n
         rec = {"m": m, "n": n, "k": k, "us": round(t * 1e6, 2), "tflops": round(flops / t / 1e12, 1),
@@ -384,24 +390,24 @@ def shape_sweep(peaks):
         else:
             rec["frac_of_nominal_fp8_peak"] = round(flops / t / 1e12 / NOMINAL_FP8_TFLOPS, 3)
         rec["parity"] = parity_gate(x, aq, a_s, bq, bs, c, seed=m + n)
-        if m >= 1024:
-            # the same step through the one-call entry point (quantisation as the GEMM's A prologue:
-            # for this many rows the quantiser and the GEMM chained by programmatic dependent launch)
+        # the same step through the one-call entry point (quantisation as the GEMM's A prologue): the
+        # quantiser and the GEMM chained by programmatic dependent launch
+        if m <= 16 or m >= 1024:
             c2 = torch.empty_like(c)
-            with torch.cuda.stream(side):
-                for _ in range(2):
-                    ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs, out=c2)
-                torch.cuda.synchronize()
-                e0.record(side)
-                for _ in range(5):
-                    ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs, out=c2)
-                e1.record(side)
-                torch.cuda.synchronize()
-            rec["fused_prologue_us"] = round(e0.elapsed_time(e1) * 1e3 / 5, 2)
+            t2 = graph_time(lambda: ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs, out=c2))
+            rec["fused_prologue_us"] = round(t2 * 1e6, 2)
             rec["fused_equals_separate"] = bool(torch.equal(c, c2))
+            if m <= 16:
+                # and with the quantisation inside the small-M kernel (one launch; option fused_prologue)
+                ops.set_option("fused_prologue", 1)
+                try:
+                    t3 = graph_time(lambda: ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs, out=c2))
+                finally:
+                    ops.set_option("fused_prologue", 0)
+                rec["in_kernel_prologue_us"] = round(t3 * 1e6, 2)
+                rec["in_kernel_equals_separate"] = bool(torch.equal(c, c2))
             del c2
         out.append(rec)
-        del g
     return out
 
 

@@ -328,23 +328,26 @@ int inferop_w8a8_block_fp8_gemm_fused_quant(void* c, const void* a, int32_t a_dt
   DeviceCtx* ctx = current_ctx(&err);
   if (!ctx) return err;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (m > kFusedMaxM) {
-    // More than a few tokens: quantising inside the GEMM would repeat the work once per column
-    // tile (N / 256 times), so the one call is two launches: the quantiser writes into scratch of
-    // this stream (grown on demand: a cudaMalloc when a call is larger than any before it on the
-    // stream) and signals its dependents at once; the GEMM, launched with programmatic stream
-    // serialisation, sets itself up underneath it.  Same bits as the two separate calls.
-    void *q = nullptr, *qs = nullptr;
-    int rc = quant_scratch(ctx, s, static_cast<size_t>(m) * k, static_cast<size_t>(m) * (k / 128) * 4, &q, &qs);
-    if (rc != INFEROP_OK) return rc;
-    rc = launch_quant(q, qs, a, a_dt, m, k, 128, s, ctx->sm_count);
-    if (rc != INFEROP_OK) return rc;
-    return gemm_dispatch(ctx, c, q, qs, b_q, b_scales, m, n, k, out_dt, s);
+  if (m <= kFusedMaxM && options().fused_prologue) {
+    // A few tokens, on request (option fused_prologue): one launch.  Four warps of every CTA of the
+    // small-M kernel quantise the token tiles of its units into a shared-memory ring, ahead of the
+    // weight stream.  Level with the chained pair below at M = 1 and slower from M = 4 on (every CTA
+    // repeats the quantisation and four warps do not keep up with the weight stream), so not the default.
+    float* ws = nullptr;
+    int* counters = nullptr;
+    if (!decode_scratch(ctx, s, &ws, &counters)) return INFEROP_ERR_LIMIT;   // no scratch set left for this stream
+    return launch_gemm_decode_fused(ctx, ws, counters, c, a, a_dt, b_q, b_scales, m, n, k, out_dt, s);
   }
-  float* ws = nullptr;
-  int* counters = nullptr;
-  if (!decode_scratch(ctx, s, &ws, &counters)) return INFEROP_ERR_LIMIT;   // no scratch set left for this stream
-  return launch_gemm_decode_fused(ctx, ws, counters, c, a, a_dt, b_q, b_scales, m, n, k, out_dt, s);
+  // More tokens (quantising inside the GEMM would repeat the work once per column tile): two launches.  The quantiser writes into scratch of this
+  // stream (grown on demand: a cudaMalloc when a call is larger than any before it on the stream)
+  // and signals its dependents at once; the GEMM, launched with programmatic stream
+  // serialisation, sets itself up underneath it.  Same bits as the two separate calls.
+  void *q = nullptr, *qs = nullptr;
+  int rc = quant_scratch(ctx, s, static_cast<size_t>(m) * k, static_cast<size_t>(m) * (k / 128) * 4, &q, &qs);
+  if (rc != INFEROP_OK) return rc;
+  rc = launch_quant(q, qs, a, a_dt, m, k, 128, s, ctx->sm_count);
+  if (rc != INFEROP_OK) return rc;
+  return gemm_dispatch(ctx, c, q, qs, b_q, b_scales, m, n, k, out_dt, s);
 }
 
 int inferop_w8a8_block_fp8_gemm_grouped(void* c, const void* a_q, const void* a_scales, const void* b_q,
@@ -725,6 +728,8 @@ int inferop_set_option(const char* key, int64_t value) {
     o.gemm_pair = static_cast<int>(value);
   } else if (!strcmp(key, "pdl_trigger")) {
     o.pdl_trigger = value != 0;
+  } else if (!strcmp(key, "fused_prologue")) {
+    o.fused_prologue = value != 0;
   } else if (!strcmp(key, "quant_pdl")) {
     o.quant_pdl = value != 0;
   } else if (!strcmp(key, "gemm_pdl")) {

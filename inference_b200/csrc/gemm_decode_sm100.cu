@@ -47,6 +47,9 @@ constexpr int BK = 128;
 constexpr int kThreads = 256;
 constexpr int kFusedThreads = 384;   // fused prologue: four more warps that quantise the token tile
 constexpr int kBytesW = TN * BK;
+constexpr int kMaxStages = 10;       // barrier slots of the ring
+constexpr int kFusedMaxSmem = 227 * 1024;   // fused prologue: dynamic shared memory the launcher may ask for
+constexpr int kMaxSlots = 16;        // fused prologue: barrier slots of the token-tile ring
 
 template <int MP>
 struct DCfg {
@@ -71,6 +74,7 @@ struct DecodeParams {
   int n_dst, ldc, col0;
   float* workspace;        // [gridDim.x][2][MP][128] fp32 partials (slot 0: the CTA's first tile, slot 1: its last)
   int splits;              // 0: units dealt evenly (below); else K parts per tile (1 = runs of whole tiles)
+  int stages, a_slots;     // fused prologue: depth of the weight ring and of the token-tile ring
   int* counters;           // [n_tiles], zero between launches
   int m, n, kb, n_tiles;
   long long units;         // n_tiles * kb
@@ -153,10 +157,12 @@ template <>
 __device__ __forceinline__ void unpack8<void>(const uint4&, float (&)[8]) {}
 
 // AT = void: the token tile arrives quantised through TMA and a scale warp prepares the scale
-// vectors.  AT = bf16 / fp16 (the fused prologue): warps 8-11 quantise the token tile of
-// every unit themselves, straight from the unquantised activations, into the swizzled layout a
-// TMA load would have produced, and write the scale vectors; the stand-alone quantisation
-// kernel and its q / scales round trip through HBM disappear.
+// vectors.  AT = bf16 / fp16 (the fused prologue): warps 8-11 quantise the token tile of every
+// unit themselves, straight from the unquantised activations, into a ring of their own in
+// shared memory (swizzled [MP x 128 B] tiles, the layout a TMA load would have produced, plus
+// the group scales), running ahead of the weight stream by up to the ring's depth; the producer
+// streams weights only.  The stand-alone quantisation kernel, its launch and its q / scales
+// round trip through HBM disappear.
 template <int MP, typename OutT, typename AT>
 __global__ void __launch_bounds__(std::is_same<AT, void>::value ? kThreads : kFusedThreads, 1)
 w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
@@ -168,14 +174,23 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  float* sv = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);   // [kBufs][MP]
+  // ring stages: weight tile + token tile; fused: weight tile only, depth chosen by the launcher
+  const uint32_t nst = kFused ? static_cast<uint32_t>(p.stages) : static_cast<uint32_t>(C::kStages);
+  constexpr uint32_t kStride = kFused ? kBytesW : C::kStageBytes;
+  const uint32_t a_slots = kFused ? static_cast<uint32_t>(p.a_slots) : 0u;  // fused: ring of quantised token tiles (a power of two)
+  const uint32_t a_mask = a_slots - 1u, a_shift = 31u - static_cast<uint32_t>(__clz(static_cast<int>(a_slots | 1u)));
+  uint8_t* a_res = smem + nst * kStride;                                    // [a_slots][MP x 128 B], swizzled
+  float* sa_res = reinterpret_cast<float*>(a_res + a_slots * (MP * BK));     // [a_slots][MP] group scales
+  float* sv = sa_res + a_slots * MP;                                         // [kBufs][MP]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sv) + C::kScaleBytes);
-  uint64_t* full = bars;                         // [kStages] TMA -> MMA
-  uint64_t* empty = full + C::kStages;           // [kStages] MMA -> TMA
-  uint64_t* tmem_full = empty + C::kStages;      // [kBufs]   MMA -> promotion
+  uint64_t* full = bars;                         // [kMaxStages] TMA -> MMA
+  uint64_t* empty = full + kMaxStages;           // [kMaxStages] MMA -> TMA
+  uint64_t* tmem_full = empty + kMaxStages;      // [kBufs]   MMA -> promotion
   uint64_t* tmem_empty = tmem_full + C::kBufs;   // [kBufs]   promotion -> MMA, scale warp
   uint64_t* sv_full = tmem_empty + C::kBufs;     // [kBufs]   scale warp -> promotion
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sv_full + C::kBufs);
+  uint64_t* a_full = sv_full + C::kBufs;         // [a_slots] fused: quantising warps -> MMA, scale warp
+  uint64_t* a_empty = a_full + (kFused ? kMaxSlots : 0);   // [a_slots] fused: MMA + scale warp -> quantising warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(a_empty + (kFused ? kMaxSlots : 0));
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* last_flag = tmem_slot + 2;
 
@@ -183,9 +198,13 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(&full[s], kFused ? 2 : 1);
+    for (uint32_t s = 0; s < nst; ++s) {
+      mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+    }
+    for (uint32_t j = 0; j < a_slots; ++j) {
+      mbar_init(&a_full[j], 1);
+      mbar_init(&a_empty[j], 2);   // the unit's MMAs have read the tile, the scale warp its scales
     }
     for (int b = 0; b < C::kBufs; ++b) {
       mbar_init(&tmem_full[b], 1);
@@ -244,7 +263,7 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     int t = t_first, kb = kb_first;
     uint32_t armed = 0;
     bool ok = true;
-    const uint32_t head = count < static_cast<uint32_t>(C::kStages) ? count : static_cast<uint32_t>(C::kStages);
+    const uint32_t head = count < nst ? count : nst;
     if (p.no_loads) {
       // test hook: nothing is ever loaded, so every other role's wait runs out
     } else if (!kFused) {
@@ -272,20 +291,19 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           ++t;
         }
       }
-    } else {
-      pdl_wait();
     }
+    // (fused: this warp touches weights only, which never depend on the kernel queued before)
     for (uint32_t i = (kFused ? 0u : head); i < count && !p.no_loads; ++i) {
-      const uint32_t stage = i % C::kStages;
-      const uint32_t phase = (i / C::kStages) & 1u;
+      const uint32_t stage = i % nst;
+      const uint32_t phase = (i / nst) & 1u;
       if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteDProducerEmpty)) {
         ok = false;
         break;
       }
       __syncwarp();
-      uint8_t* dst = smem + stage * C::kStageBytes;
+      uint8_t* dst = smem + stage * kStride;
       if (elect_one()) {
-        mbar_arrive_expect_tx(&full[stage], kFused ? kBytesW : C::kStageBytes);
+        mbar_arrive_expect_tx(&full[stage], kStride);
         tma_load_2d(dst, &map_w, &full[stage], kb * BK, t * TN);
         if (!kFused) tma_load_2d(dst + kBytesW, &map_a, &full[stage], kb * BK, 0);
       }
@@ -298,10 +316,10 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     if (!ok && lane == 0) {
       // wind-down: let the copies this warp started land before the CTA exits
-      const uint32_t lo = armed > C::kStages ? armed - C::kStages : 0u;
+      const uint32_t lo = armed > nst ? armed - nst : 0u;
       for (uint32_t i = lo; i < armed; ++i) {
         const long long t0 = clock64();
-        while (!mbar_test_wait(&full[i % C::kStages], (i / C::kStages) & 1u)) {
+        while (!mbar_test_wait(&full[i % nst], (i / nst) & 1u)) {
           if (clock64() - t0 > kWaitBudgetCycles) break;
         }
       }
@@ -314,17 +332,19 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     constexpr uint32_t idesc = umma_idesc_e4m3_f32(TN, MP);
     const uint32_t smem_base = smem_u32(smem);
     for (uint32_t i = (warp == 3) ? 1u : 0u; i < count; i += 2) {
-      const uint32_t stage = i % C::kStages;
-      const uint32_t phase = (i / C::kStages) & 1u;
+      const uint32_t stage = i % nst;
+      const uint32_t phase = (i / nst) & 1u;
       const uint32_t buf = i % C::kBufs;
       const uint32_t use = i / C::kBufs;
+      const uint32_t slot = kFused ? (i & a_mask) : 0u;   // fused: the unit's slot in the token-tile ring
       if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kSiteDMmaFull)) break;
+      if (kFused && !mbar_wait(&a_full[slot], (i >> a_shift) & 1u, abort_flag, p.status, kSiteDQuantEmpty)) break;
       if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, kSiteDMmaTmemEmpty)) break;
       __syncwarp();
       tc_fence_after_sync();
-      const uint32_t w_addr = smem_base + stage * C::kStageBytes;
+      const uint32_t w_addr = smem_base + stage * kStride;
       const uint64_t dw = umma_desc_k_sw128(w_addr);
-      const uint64_t da = umma_desc_k_sw128(w_addr + kBytesW);
+      const uint64_t da = umma_desc_k_sw128(kFused ? smem_u32(a_res) + slot * (MP * BK) : w_addr + kBytesW);
       const uint32_t d_tmem = tmem_base + buf * MP;
       if (elect_one()) {
 #pragma unroll
@@ -333,99 +353,110 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
         umma_commit(&tmem_full[buf]);
         umma_commit(&empty[stage]);
+        if (kFused) umma_commit(&a_empty[slot]);
       }
       __syncwarp();
     }
   } else if (kFused && warp >= 8) {
     // ------------------------------ quantising prologue (fused) -----------
-    // A half warp owns one token row of the unit: 16 lanes x 8 elements = the 128-wide group.
-    // Row r of step s: r = 2 * (qw + kQuantWarps * s) + half_warp.  The activations of the
-    // next two units are always in flight (registers cur / nx1 / nx2), because the round trip
-    // to L2 is longer than the time one unit takes.
+    // Warp w takes the units w, w + 4, ...: all token rows of the unit's K block, two per step (a
+    // half warp owns one row's 128-wide group: 16 lanes x 8 elements), the next unit's
+    // activations in flight while the current one is quantised.  Rows beyond M are zero: they are
+    // written once, before the loop, and never touched again.
     if constexpr (kFused) {
-      // Each of the four warps takes every fourth unit whole (all MP token rows, two per
-      // step), so that the per-unit costs (barrier probes, proxy fence, arrivals) are paid by
-      // one warp per unit, and it has four unit times to do the work.  The activations of its
-      // next unit are in flight while it quantises the current one.
       constexpr int STEPS = MP / 2;
       const int qw = warp - 8, hw = lane >> 4, sub = lane & 15;
       const AT* src = static_cast<const AT*>(p.a_src);
       const int64_t ld = static_cast<int64_t>(p.kb) * BK;
+      const int live_steps = (p.m + 1) >> 1;   // steps that hold at least one real row
+      for (uint32_t j = qw; j < a_slots; j += kQuantWarps) {
+#pragma unroll
+        for (int s2 = 0; s2 < STEPS; ++s2) {
+          const int r = 2 * s2 + hw;
+          if (r >= p.m) {
+            *reinterpret_cast<uint2*>(a_res + j * (MP * BK) + r * 128 + (((sub >> 1) ^ (r & 7)) << 4) + ((sub & 1) << 3)) =
+                make_uint2(0u, 0u);
+            if (sub == 0) sa_res[j * MP + r] = 0.0f;
+          }
+        }
+      }
       uint4 cur[STEPS], nxt[STEPS];
       pdl_wait();   // the activations may come from the kernel queued before this one
       auto fetch = [&](uint4 (&dst)[STEPS], uint32_t unit) {
-        // unit -> K block (the token tile does not depend on the weight tile)
         const int kbx = static_cast<int>((static_cast<uint32_t>(kb_first) + unit) % static_cast<uint32_t>(p.kb));
 #pragma unroll
         for (int s2 = 0; s2 < STEPS; ++s2) {
           const int r = 2 * s2 + hw;
-          dst[s2] = (r < p.m && unit < count)
-                        ? __ldg(reinterpret_cast<const uint4*>(src + r * ld + kbx * BK + sub * 8))
-                        : make_uint4(0u, 0u, 0u, 0u);
+          if (s2 < live_steps) {
+            dst[s2] = (r < p.m && unit < count)
+                          ? __ldg(reinterpret_cast<const uint4*>(src + r * ld + kbx * BK + sub * 8))
+                          : make_uint4(0u, 0u, 0u, 0u);
+          }
         }
       };
       fetch(cur, qw);
       for (uint32_t i = qw; i < count; i += kQuantWarps) {
         fetch(nxt, i + kQuantWarps);
-        const uint32_t stage = i % C::kStages;
-        const uint32_t phase = (i / C::kStages) & 1u;
-        const uint32_t buf = i % C::kBufs;
-        const uint32_t use = i / C::kBufs;
-        const uint32_t lin = static_cast<uint32_t>(kb_first) + i;
-        const int t = t_first + static_cast<int>(lin / static_cast<uint32_t>(p.kb));
-        const int kb = static_cast<int>(lin % static_cast<uint32_t>(p.kb));
-        const float sb = __ldg(p.b_scales + static_cast<int64_t>(t) * p.kb + kb);
-        if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteDQuantEmpty)) break;
-        if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, kSiteDQuantTmem)) break;
+        const uint32_t slot = (i & a_mask);
+        if (!mbar_wait(&a_empty[slot], ((i >> a_shift) & 1u) ^ 1u, abort_flag, p.status, kSiteDQuantEmpty)) break;
         __syncwarp();
-        uint8_t* tile = smem + stage * C::kStageBytes + kBytesW;
+        uint8_t* tile = a_res + slot * (MP * BK);
 #pragma unroll
         for (int s2 = 0; s2 < STEPS; ++s2) {
-          const int r = 2 * s2 + hw;
-          float f[8];
-          unpack8<AT>(cur[s2], f);
-          float amax = 0.0f;
+          if (s2 < live_steps) {
+            const int r = 2 * s2 + hw;
+            float f[8];
+            unpack8<AT>(cur[s2], f);
+            float amax = 0.0f;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+            for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
 #pragma unroll
-          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-          const float scale = group_scale(amax);
-          const uint2 bytes = fast_div_ok(amax) ? quantise8_fast16(cur[s2], f, scale, __frcp_rn(scale))
-                                                : quantise8<false>(f, scale, 0.0f);
-          // swizzled K-major layout of a TMA SWIZZLE_128B load: 16-byte chunk c of row r sits at
-          // chunk c ^ (r & 7); this lane's 8 bytes are half of chunk sub / 2
-          *reinterpret_cast<uint2*>(tile + r * 128 + (((sub >> 1) ^ (r & 7)) << 4) + ((sub & 1) << 3)) = bytes;
-          if (sub == 0) sv[buf * MP + r] = (r < p.m) ? scale * sb : 0.0f;
+            for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+            const float scale = group_scale(amax);
+            const uint2 bytes = fast_div_ok(amax) ? quantise8_fast16(cur[s2], f, scale, __frcp_rn(scale))
+                                                  : quantise8<false>(f, scale, 0.0f);
+            if (r < p.m) {
+              // swizzled K-major layout of a TMA SWIZZLE_128B load: 16-byte chunk c of row r sits at
+              // chunk c ^ (r & 7); this lane's 8 bytes are half of chunk sub / 2
+              *reinterpret_cast<uint2*>(tile + r * 128 + (((sub >> 1) ^ (r & 7)) << 4) + ((sub & 1) << 3)) = bytes;
+              if (sub == 0) sa_res[slot * MP + r] = scale;
+            }
+          }
         }
         fence_proxy_async_smem();   // the tensor core reads the tile through the async proxy
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&full[stage]);
-          mbar_arrive(&sv_full[buf]);
-        }
+        if (lane == 0) mbar_arrive(&a_full[slot]);
 #pragma unroll
         for (int s2 = 0; s2 < STEPS; ++s2) cur[s2] = nxt[s2];
       }
     }
-  } else if (!kFused && warp == 2) {
+  } else if (warp == 2) {
     // ------------------------------ scale warp ----------------------------
-    pdl_wait();   // a_scales may come from the kernel queued before this one
+    if (!kFused) pdl_wait();   // a_scales may come from the kernel queued before this one
     int t = t_first, kb = kb_first;
     for (uint32_t i = 0; i < count; ++i) {
       const uint32_t buf = i % C::kBufs;
       const uint32_t use = i / C::kBufs;
       if (!mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, kSiteDScaleEmpty)) break;
       const float sb = __ldg(p.b_scales + static_cast<int64_t>(t) * p.kb + kb);
+      // fused: the group scales of this unit are in shared memory once its tile is published
+      const uint32_t slot = kFused ? (i & a_mask) : 0u;
+      if (kFused && !mbar_wait(&a_full[slot], (i >> a_shift) & 1u, abort_flag, p.status, kSiteDQuantTmem)) break;
 #pragma unroll
       for (int m0 = 0; m0 < MP; m0 += 32) {
         const int m = m0 + lane;
         if (m < MP) {
-          const float sa = (m < p.m) ? __ldg(p.a_scales + static_cast<int64_t>(m) * p.kb + kb) : 0.0f;
+          float sa;
+          if (kFused) sa = sa_res[slot * MP + m];
+          else sa = (m < p.m) ? __ldg(p.a_scales + static_cast<int64_t>(m) * p.kb + kb) : 0.0f;
           sv[buf * MP + m] = sa * sb;
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sv_full[buf]);
+      if (lane == 0) {
+        mbar_arrive(&sv_full[buf]);
+        if (kFused) mbar_arrive(&a_empty[slot]);
+      }
       if (++kb == p.kb) {
         kb = 0;
         ++t;
@@ -561,14 +592,17 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 template <int MP, typename OutT, typename AT = void>
 int launch_decode_t(const CUtensorMap& mw, const CUtensorMap& ma, const DecodeParams& p, int ctas,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, int smem_bytes = 0) {
   using C = DCfg<MP>;
+  constexpr bool kFused = !std::is_same<AT, void>::value;
+  if (!kFused) smem_bytes = C::kSmemBytes;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(w8a8_decode_kernel<MP, OutT, AT>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kFused ? kFusedMaxSmem : C::kSmemBytes);
     if (e != cudaSuccess) return note_cuda_error(e);
     attr_done[dev] = true;
   }
@@ -577,7 +611,7 @@ int launch_decode_t(const CUtensorMap& mw, const CUtensorMap& ma, const DecodePa
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(ctas);
   cfg.blockDim = dim3(std::is_same<AT, void>::value ? kThreads : kFusedThreads);
-  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -591,17 +625,17 @@ int launch_decode_t(const CUtensorMap& mw, const CUtensorMap& ma, const DecodePa
 
 template <typename OutT, typename AT>
 int launch_decode_fused_mp(int mp, const CUtensorMap& mw, const DecodeParams& p, int ctas,
-                           cudaStream_t stream) {
-  return mp == 16 ? launch_decode_t<16, OutT, AT>(mw, mw, p, ctas, stream)
-                  : launch_decode_t<32, OutT, AT>(mw, mw, p, ctas, stream);
+                           cudaStream_t stream, int smem_bytes) {
+  return mp == 16 ? launch_decode_t<16, OutT, AT>(mw, mw, p, ctas, stream, smem_bytes)
+                  : launch_decode_t<32, OutT, AT>(mw, mw, p, ctas, stream, smem_bytes);
 }
 template <typename AT>
 int launch_decode_fused_out(int out_dt, int mp, const CUtensorMap& mw, const DecodeParams& p, int ctas,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, int smem_bytes) {
   switch (out_dt) {
-    case 0: return launch_decode_fused_mp<float, AT>(mp, mw, p, ctas, stream);
-    case 1: return launch_decode_fused_mp<__half, AT>(mp, mw, p, ctas, stream);
-    case 2: return launch_decode_fused_mp<__nv_bfloat16, AT>(mp, mw, p, ctas, stream);
+    case 0: return launch_decode_fused_mp<float, AT>(mp, mw, p, ctas, stream, smem_bytes);
+    case 1: return launch_decode_fused_mp<__half, AT>(mp, mw, p, ctas, stream, smem_bytes);
+    case 2: return launch_decode_fused_mp<__nv_bfloat16, AT>(mp, mw, p, ctas, stream, smem_bytes);
     default: return INFEROP_ERR_DTYPE;
   }
 }
@@ -650,11 +684,7 @@ int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, vo
   int max_ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
   if (max_ctas > ctx->sm_count) max_ctas = ctx->sm_count;
   int ctas;
-  if (opt.decode_deal == 0) {
-    // every (tile, K block) unit dealt evenly over one CTA per SM
-    p.splits = 0;
-    ctas = p.units < max_ctas ? static_cast<int>(p.units) : max_ctas;
-  } else if (p.n_tiles >= max_ctas) {
+  if (p.n_tiles >= max_ctas) {
     p.splits = 1;
     ctas = max_ctas;
   } else {
@@ -663,8 +693,15 @@ int launch_gemm_decode_fused(DeviceCtx* ctx, float* workspace, int* counters, vo
     if (opt.decode_splits > 0 && opt.decode_splits <= p.splits) p.splits = opt.decode_splits;
     ctas = p.n_tiles * p.splits;
   }
-  if (a_dt == 2) return launch_decode_fused_out<__nv_bfloat16>(out_dt, mp, mw, p, ctas, stream);
-  if (a_dt == 1) return launch_decode_fused_out<__half>(out_dt, mp, mw, p, ctas, stream);
+  // token-tile ring of 32 KiB beside a full-depth weight ring
+  p.a_slots = 32 * 1024 / (mp * BK);
+  if (p.a_slots > kMaxSlots) p.a_slots = kMaxSlots;
+  const int bufs = (512 / mp) < 8 ? (512 / mp) : 8;
+  const int fixed = p.a_slots * mp * (BK + 4) + bufs * mp * 4 + 1024 /* barriers */ + 1024 /* alignment slack */;
+  p.stages = kMaxStages;
+  const int smem_bytes = p.stages * kBytesW + fixed;
+  if (a_dt == 2) return launch_decode_fused_out<__nv_bfloat16>(out_dt, mp, mw, p, ctas, stream, smem_bytes);
+  if (a_dt == 1) return launch_decode_fused_out<__half>(out_dt, mp, mw, p, ctas, stream, smem_bytes);
   return INFEROP_ERR_DTYPE;
 }
 
@@ -683,6 +720,8 @@ int launch_gemm_decode_to(DeviceCtx* ctx, float* workspace, int* counters, void*
   const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
   DecodeParams p;
   p.a_src = nullptr;
+  p.stages = 0;
+  p.a_slots = 0;
   p.a_scales = static_cast<const float*>(a_scales);
   p.b_scales = static_cast<const float*>(b_scales);
   if (n_dst < 1 || n_dst > 8) return INFEROP_ERR_SHAPE;

@@ -302,15 +302,48 @@ def test_fused_quant_prologue_is_bit_identical_to_the_two_calls(ops, m, n, k):
             two = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, dt)
         finally:
             ops.set_option("gemm_path", 0)
-        one = ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs, dt)
-        assert ops.device_status()[0] == 0
-        assert torch.equal(one.view(torch.int16 if dt == torch.bfloat16 else torch.int32),
-                           two.view(torch.int16 if dt == torch.bfloat16 else torch.int32))
+        for in_kernel in ((0, 1) if m <= 32 else (0,)):   # the chained pair (default) and the one-launch form
+            ops.set_option("fused_prologue", in_kernel)
+            try:
+                one = ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs, dt)
+            finally:
+                ops.set_option("fused_prologue", 0)
+            assert ops.device_status()[0] == 0
+            assert torch.equal(one.view(torch.int16 if dt == torch.bfloat16 else torch.int32),
+                               two.view(torch.int16 if dt == torch.bfloat16 else torch.int32))
+    ops.set_option("fused_prologue", 1 if m <= 32 else 0)
     xh = x.half()
     aq, a_s = ops.quant_fp8_per_token_group(xh)
     two = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs, torch.float32)
-    one = ops.w8a8_block_fp8_gemm_fused_quant(xh, bq, bs, torch.float32)
+    try:
+        one = ops.w8a8_block_fp8_gemm_fused_quant(xh, bq, bs, torch.float32)
+    finally:
+        ops.set_option("fused_prologue", 0)
     assert torch.equal(one.view(torch.int32), two.view(torch.int32))
+
+
+@pytest.mark.parametrize("m,n,k", [(4, 7168, 18432), (16, 7168, 18432), (32, 7168, 18432), (16, 24576, 1536),
+                                   (32, 24576, 1536), (5, 2048, 10240), (16, 128, 10240), (16, 128, 20480)])
+def test_fused_quant_prologue_ring(ops, m, n, k):
+    """Shapes that exercise the token-tile ring of the one-launch form: K parts of a split tile
+    (72 blocks of 144), whole tiles with two tiles per CTA (the K range repeats), K ranges far
+    longer than the ring: always the bits of the two separate calls, and of the quantiser + GEMM
+    pair that the option selects."""
+    from inference_b200 import synth
+    x = synth.activations(m, k, seed=m + k)
+    bq, bs = synth.quantised_weights(n, k, seed=3)
+    aq, a_s = ops.quant_fp8_per_token_group(x)
+    two = ops.w8a8_block_fp8_gemm(aq, a_s, bq, bs)
+    ops.set_option("fused_prologue", 1)
+    try:
+        for rep in range(3):
+            one = ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs)
+            assert ops.device_status()[0] == 0
+            assert torch.equal(one.view(torch.int16), two.view(torch.int16)), f"repeat {rep}"
+    finally:
+        ops.set_option("fused_prologue", 0)
+    pair = ops.w8a8_block_fp8_gemm_fused_quant(x, bq, bs)   # default: quantiser + GEMM chained in one call
+    assert torch.equal(pair.view(torch.int16), two.view(torch.int16))
 
 
 def test_fused_quant_prologue_limits(ops):
