@@ -280,6 +280,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
   using TL = Tile<TBN>;
   constexpr int BN = TL::BN, CT = TL::CT, kStages = TL::kStages, kStageBytes = TL::kStageBytes,
                 kSlices = TL::kSlices;
+  // The two MMA issuer warps alternate K blocks.  With an even number of stages (and of
+  // accumulator buffers) a stage always belongs to the same warp, whose parity waits on its
+  // barrier follow one another in program order.  With an odd number a stage would alternate
+  // between the warps, and one warp's wait could be answered by the phase the other warp is still
+  // waiting for whenever two TMA loads complete out of order (seen as a launch failure at full
+  // size on 4 GPUs in a three-stage experiment); such a variant needs one barrier per stage AND warp.
+  static_assert(kStages % 2 == 0 && kSlices % 2 == 0, "a ring stage must always belong to the same issuer warp");
   // a device-built tile list comes with its length in device memory (at most p.tiles_m entries)
   const int num_tiles =
       (kGrouped && num_mtiles_dev != nullptr) ? min(__ldg(num_mtiles_dev), p.tiles_m) * p.tiles_n
