@@ -58,6 +58,7 @@ struct DCfg {
   // (twelve stages of 18 KiB fit too and measured 3 % slower than ten)
   static constexpr int kStages = (200 * 1024 / kStageBytes) < 10 ? (200 * 1024 / kStageBytes) : 10;
   static_assert(kStages % 2 == 0, "the two MMA issuer warps alternate units: a stage must always belong to the same warp");
+  static_assert(kStages % 2 == 0, "the two MMA issuer warps alternate units: a stage must always belong to the same warp");
   static constexpr int kBufs = (512 / MP) < 8 ? (512 / MP) : 8;
   static constexpr int kTmemCols = (kBufs * MP) < 32 ? 32 : (kBufs * MP);
   static constexpr int kScaleBytes = kBufs * MP * 4;
