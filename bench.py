@@ -18,6 +18,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import subprocess
 import sys
 import threading
 import time
@@ -80,6 +81,8 @@ def parse_args():
     ap.add_argument("--collective-seconds", type=int, default=300,
                     help="deadline for the collective sections (N > 1); the main result is printed without them after it")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-numa-bind", action="store_true",
+                    help="end-to-end section: do not restrict the process to the CPUs next to its GPU")
     ap.add_argument("--no-sweep", action="store_true", help="skip the decode / prefill shape sweep (N=1 only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU-baseline sample budget")
@@ -796,7 +799,17 @@ def run_ours(args):
     # ---- end-to-end through the public API with host buffers
     e2e = None
     if not args.no_e2e:
-        from inference_b200.host import HostLinearFP8
+        from inference_b200.host import HostLinearFP8, bind_to_device_numa_node
+        # one process per GPU: keep the pinned buffers (allocated next) in the memory next to this GPU
+        numa = None
+        cpus_before = os.sched_getaffinity(0)
+        if not args.no_numa_bind:
+            try:
+                bus_id = subprocess.run(["nvidia-smi", "-i", str(physical_gpu_index(local)), "--query-gpu=pci.bus_id",
+                                         "--format=csv,noheader"], capture_output=True, text=True, timeout=20).stdout
+                numa = bind_to_device_numa_node(bus_id)
+            except Exception:
+                numa = None
         x_host = x.cpu().pin_memory()
         c_host = torch.empty((m, n_loc), dtype=torch.bfloat16).pin_memory()
         lin = HostLinearFP8(bq, bs, max_rows=m, panel_rows=2048,   # the public host-buffer call
@@ -818,10 +831,11 @@ def run_ours(args):
         e2e = {"value": flops_total / te / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": x_host.numel() * 2 // world, "d2h_bytes_per_step": c_host.numel() * 2,
                "bytes_are": "per rank (every rank uploads 1/G of the activation rows and reads back its [M, N/G] result)",
-               "ms_per_step": te * 1e3, "steps": n_e2e, "parity": {"row": e2e_par["row"], "fro": e2e_par["fro"], "ok": True},
+               "ms_per_step": te * 1e3, "steps": n_e2e, "host_numa_binding": numa, "parity": {"row": e2e_par["row"], "fro": e2e_par["fro"], "ok": True},
                "api": "inference_b200.host.HostLinearFP8: 2048-row panels, copy-in / quant (+ all-gather of the FP8 rows "
                       "at N > 1) + GEMM / copy-out on three streams"}
         del x_host, c_host, lin
+        os.sched_setaffinity(0, cpus_before)   # the CPU baseline below uses every core it is allowed
 
     peaks = measured_peaks()
     # No FP8 figure was measured on this pool: the denominator is twice a measured bf16 cuBLAS

@@ -22,6 +22,36 @@ import torch
 from . import ops
 
 
+def bind_to_device_numa_node(pci_bus_id: str, sysfs_root: str = "/sys/bus/pci/devices") -> dict | None:
+    """Restrict this process to the CPUs next to the GPU with PCI address `pci_bus_id`
+    ("0000:1b:00.0" or the 8-digit-domain form nvidia-smi prints), so that host buffers pinned
+    afterwards land in that NUMA node's memory (first touch) and the copies between them and the
+    GPU do not cross the socket interconnect.  One process per GPU, called before the pinned
+    buffers are allocated.  Returns {"node", "cpus"} or None when the topology is not exposed
+    (nothing is changed then)."""
+    import os
+    try:
+        dom, bus, rest = pci_bus_id.strip().lower().split(":")
+        path = os.path.join(sysfs_root, f"{dom[-4:]}:{bus}:{rest}")
+        with open(os.path.join(path, "numa_node")) as f:
+            node = int(f.read().strip())
+        with open(os.path.join(path, "local_cpulist")) as f:
+            spec = f.read().strip()
+        cpus = set()
+        for part in spec.split(","):
+            if not part:
+                continue
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)          # never widen what the container allows
+        if node < 0 or not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return {"node": node, "cpus": len(cpus)}
+    except (OSError, ValueError):
+        return None
+
+
 def rank_rows(rows: int, world: int, rank: int) -> tuple[int, int]:
     """Rows [lo, hi) of a `rows`-row panel that `rank` uploads and quantises: equal contiguous
     chunks in rank order (what an all-gather into one tensor reassembles in row order).  `rows`
