@@ -56,6 +56,22 @@ INFEROP_EXPORT void w8a8_block_fp8_gemm(void* c, const void* a_q, const void* a_
                          int group_size = 128, int block_n = 128, dtype out_dt = dtype::bf16,
                          void* stream = nullptr);
 
+// out[r, c] = weight[c] * in[r, c] / sqrt(mean(in[r, :]^2) + eps); in / out [rows, cols], weight [cols] in dt.
+INFEROP_EXPORT void rmsnorm(void* out, const void* in, const void* weight, dtype dt, int64_t rows,
+             int64_t cols, float eps = 1e-6f, void* stream = nullptr);
+
+// residual[r, c] += x[r, c] (in place);  out = rmsnorm(residual).
+INFEROP_EXPORT void fused_add_rmsnorm(void* residual, void* out, const void* x, const void* weight,
+                       dtype dt, int64_t rows, int64_t cols, float eps = 1e-6f,
+                       void* stream = nullptr);
+
+// Rotary position embedding (GPT-NeoX style, half-dim rotation, in place) on qkv
+// [tokens, heads, head_dim]; positions int64 [tokens]; rotary_dim <= head_dim, even;
+// theta = position * base^(-2 i / rotary_dim) * yarn_factor.  A bad rotary_dim is a silent no-op.
+INFEROP_EXPORT void rope_neox(void* qkv, const int64_t* positions, dtype dt, int64_t tokens, int heads,
+               int head_dim, int rotary_dim, float base = 10000.0f, float yarn_factor = 1.0f,
+               void* stream = nullptr);
+
 // out[t, i] = silu(gate_up[t, i]) * gate_up[t, d + i];  gate_up [tokens, 2d], out [tokens, d] in dt.
 INFEROP_EXPORT void silu_and_mul(void* out, const void* gate_up, dtype dt, int64_t tokens, int64_t d,
                   void* stream = nullptr);

@@ -208,6 +208,27 @@ INFEROP_API int inferop_copy_2d_async(void* dst, int64_t dst_pitch_bytes, const 
 INFEROP_API int inferop_topk_softmax(int32_t* topk_ids, void* topk_weights, const void* logits, int32_t tokens,
                          int32_t num_experts, int32_t topk, int32_t renormalize, void* stream);
 
+/* RMSNorm (reference include/inferop/ops.h:30-31, kernels/rmsnorm.cu:21-36, CPU
+ * reference/reference.cpp:11-21): out[r, c] = in[r, c] / sqrt(mean(in[r, :]^2) + eps) * weight[c]
+ * for in / out [rows, cols] and weight [cols] in dt (0 fp32, 1 fp16, 2 bf16), computed in fp32. */
+INFEROP_API int inferop_rmsnorm(void* out, const void* in, const void* weight, int32_t dt, int64_t rows,
+                    int64_t cols, float eps, void* stream);
+
+/* Residual add + RMSNorm (reference ops.h:35-37, kernels/rmsnorm.cu:38-59, CPU
+ * reference.cpp:23-35): residual[r, :] += x[r, :] in place (stored in dt), out = RMSNorm of the
+ * sum.  As in the reference's kernel the mean uses the unrounded sums and the output the stored ones. */
+INFEROP_API int inferop_fused_add_rmsnorm(void* residual, void* out, const void* x, const void* weight, int32_t dt,
+                              int64_t rows, int64_t cols, float eps, void* stream);
+
+/* Rotary position embedding, GPT-NeoX layout, in place (reference ops.h:46-48, kernels/rope.cu:19-41,
+ * CPU reference.cpp:37-53): qkv [tokens, heads, head_dim] in dt, positions int64 [tokens] (device);
+ * for i < rotary_dim / 2: theta = position * base^(-2 i / rotary_dim) * yarn_factor and
+ * (x_i, x_{i + rotary_dim/2}) is rotated by theta; elements from rotary_dim on are untouched.
+ * rotary_dim even, 2 <= rotary_dim <= head_dim, rotary_dim <= 1024 (INFEROP_ERR_LIMIT beyond);
+ * the reference returns silently on a bad rotary_dim, this returns INFEROP_ERR_SHAPE. */
+INFEROP_API int inferop_rope_neox(void* qkv, const int64_t* positions, int32_t dt, int64_t tokens, int32_t heads,
+                      int32_t head_dim, int32_t rotary_dim, float base, float yarn_factor, void* stream);
+
 /* SwiGLU (reference include/inferop/ops.h:54-55, kernels/silu_mul.cu:16-28, CPU
  * reference/reference.cpp:55-63): out[t, i] = silu(gate_up[t, i]) * gate_up[t, d + i] for
  * gate_up [tokens, 2d] and out [tokens, d] in dt (0 fp32, 1 fp16, 2 bf16), computed in fp32. */

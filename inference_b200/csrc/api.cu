@@ -504,6 +504,43 @@ int inferop_topk_softmax(int32_t* topk_ids, void* topk_weights, const void* logi
                              static_cast<cudaStream_t>(stream));
 }
 
+int inferop_rmsnorm(void* out, const void* in, const void* weight, int32_t dt, int64_t rows, int64_t cols,
+                    float eps, void* stream) {
+  if (rows <= 0 || cols <= 0) return INFEROP_ERR_SHAPE;
+  if (dt < 0 || dt > 2) return INFEROP_ERR_DTYPE;
+  if (!out || !in || !weight) return INFEROP_ERR_POINTER;
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_rmsnorm(out, nullptr, in, weight, dt, rows, cols, eps, static_cast<cudaStream_t>(stream));
+}
+
+int inferop_fused_add_rmsnorm(void* residual, void* out, const void* x, const void* weight, int32_t dt,
+                              int64_t rows, int64_t cols, float eps, void* stream) {
+  if (rows <= 0 || cols <= 0) return INFEROP_ERR_SHAPE;
+  if (dt < 0 || dt > 2) return INFEROP_ERR_DTYPE;
+  if (!residual || !out || !x || !weight) return INFEROP_ERR_POINTER;
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_rmsnorm(out, residual, x, weight, dt, rows, cols, eps, static_cast<cudaStream_t>(stream));
+}
+
+int inferop_rope_neox(void* qkv, const int64_t* positions, int32_t dt, int64_t tokens, int32_t heads,
+                      int32_t head_dim, int32_t rotary_dim, float base, float yarn_factor, void* stream) {
+  if (tokens <= 0 || heads <= 0 || head_dim <= 0 || rotary_dim <= 0 || rotary_dim > head_dim ||
+      (rotary_dim & 1) != 0) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (dt < 0 || dt > 2) return INFEROP_ERR_DTYPE;
+  if (!qkv || !positions) return INFEROP_ERR_POINTER;
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_rope_neox(qkv, positions, dt, tokens, heads, head_dim, rotary_dim, base, yarn_factor,
+                          static_cast<cudaStream_t>(stream));
+}
+
 int inferop_silu_and_mul(void* out, const void* gate_up, int32_t dt, int64_t tokens, int64_t d,
                          void* stream) {
   if (tokens <= 0 || d <= 0) return INFEROP_ERR_SHAPE;
@@ -798,6 +835,23 @@ void topk_softmax(int32_t* topk_ids, void* topk_weights, const void* logits, int
                   int num_experts, int topk, bool renormalize, void* stream) {
   report("topk_softmax", inferop_topk_softmax(topk_ids, topk_weights, logits, tokens, num_experts, topk,
                                               renormalize ? 1 : 0, stream));
+}
+
+void rmsnorm(void* out, const void* in, const void* weight, dtype dt, int64_t rows, int64_t cols, float eps,
+             void* stream) {
+  report("rmsnorm", inferop_rmsnorm(out, in, weight, static_cast<int32_t>(dt), rows, cols, eps, stream));
+}
+
+void fused_add_rmsnorm(void* residual, void* out, const void* x, const void* weight, dtype dt, int64_t rows,
+                       int64_t cols, float eps, void* stream) {
+  report("fused_add_rmsnorm",
+         inferop_fused_add_rmsnorm(residual, out, x, weight, static_cast<int32_t>(dt), rows, cols, eps, stream));
+}
+
+void rope_neox(void* qkv, const int64_t* positions, dtype dt, int64_t tokens, int heads, int head_dim,
+               int rotary_dim, float base, float yarn_factor, void* stream) {
+  report("rope_neox", inferop_rope_neox(qkv, positions, static_cast<int32_t>(dt), tokens, heads, head_dim,
+                                        rotary_dim, base, yarn_factor, stream));
 }
 
 void silu_and_mul(void* out, const void* gate_up, dtype dt, int64_t tokens, int64_t d, void* stream) {

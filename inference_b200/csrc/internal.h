@@ -130,6 +130,12 @@ int launch_reduce_slots(void* out, int32_t out_dt, const void* slots, int32_t ra
 // moe.cu
 int launch_topk_softmax(int32_t* ids, float* weights, const float* logits, int32_t tokens,
                         int32_t experts, int32_t topk, int32_t renorm, cudaStream_t stream);
+// norm_rope.cu : RMSNorm (residual == nullptr) or residual += in followed by RMSNorm of the sum,
+// and the NeoX rotary embedding in place.
+int launch_rmsnorm(void* out, void* residual, const void* in, const void* weight, int32_t dt, int64_t rows,
+                   int64_t cols, float eps, cudaStream_t stream);
+int launch_rope_neox(void* qkv, const int64_t* positions, int32_t dt, int64_t tokens, int heads, int head_dim,
+                     int rotary_dim, float base, float yarn, cudaStream_t stream);
 int launch_silu_and_mul(void* out, const void* gate_up, int32_t dt, int64_t rows, int64_t d,
                         cudaStream_t stream, int sms);
 int launch_silu_and_mul_quant(void* q, void* scales, const void* gate_up, int32_t dt, int64_t rows,

@@ -1,0 +1,293 @@
+// RMSNorm, residual add + RMSNorm, and the NeoX rotary embedding for sm_100: the operators that sit
+// in front of the quantise + GEMM path in a transformer block (reference kernels/rmsnorm.cu:21-59,
+// kernels/rope.cu:19-41; CPU golden reference/reference.cpp:11-53).  All three are HBM-bound:
+// every element is read once and written once.
+//
+//   * rmsnorm_vec_kernel: a row lives in registers between the two passes the reference makes over
+//     it (16-byte loads, up to eight vectors per thread), so it is read from memory once; 32 to 256
+//     threads per row depending on its length, several rows per CTA when rows are short.
+//   * rope_kernel: the angle of (position, i) does not depend on the head, so a CTA computes the
+//     cos / sin table of its token once (frequencies in double precision, which reproduces the
+//     CPU golden's powf bit for bit; at position 100 000 two units in the last place of a
+//     single-precision powf are 0.02 rad) and applies it to a block of heads with 16-byte accesses.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "internal.h"
+
+namespace ib200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxVec = 8;   // 16-byte vectors of a row that one thread keeps in registers
+
+template <typename T>
+struct VecOf {
+  static constexpr int N = 16 / sizeof(T);
+};
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T>
+__device__ __forceinline__ void unpack(const uint4& raw, float (&f)[VecOf<T>::N]) {
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < VecOf<T>::N; ++i) f[i] = to_f32<T>(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack(const float (&f)[VecOf<T>::N]) {
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < VecOf<T>::N; ++i) e[i] = from_f32<T>(f[i]);
+  return raw;
+}
+
+// kAdd: residual[r, :] += x[r, :] first (stored in T), then the norm of the sum.  As in the
+// reference's kernel the sum of squares uses the unrounded sums and the output the stored ones.
+// tpr = threads per row (a power of two, 32 .. 256); rows per CTA = 256 / tpr.
+template <typename T, bool kAdd>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_vec_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __restrict__ in,
+                   const T* __restrict__ weight, float eps, int64_t rows, int cols, int tpr) {
+  constexpr int V = VecOf<T>::N;
+  __shared__ float red[kThreads / 32];
+  const int lane_in_row = threadIdx.x & (tpr - 1);
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (kThreads / tpr) + (threadIdx.x / tpr);
+  const bool live = row < rows;
+  const int nvec = cols / V;
+  const uint4* src = reinterpret_cast<const uint4*>(in + (live ? row : 0) * cols);
+  uint4* res = kAdd ? reinterpret_cast<uint4*>(residual + (live ? row : 0) * cols) : nullptr;
+
+  float v[kMaxVec][V];
+  float partial = 0.0f;
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int j = lane_in_row + k * tpr;
+    if (live && j < nvec) {
+      unpack<T>(__ldg(src + j), v[k]);
+      if constexpr (kAdd) {
+        float r[V];
+        unpack<T>(res[j], r);
+#pragma unroll
+        for (int i = 0; i < V; ++i) r[i] = __fadd_rn(r[i], v[k][i]);
+#pragma unroll
+        for (int i = 0; i < V; ++i) partial = fmaf(r[i], r[i], partial);
+        const uint4 stored = pack<T>(r);
+        res[j] = stored;
+        unpack<T>(stored, v[k]);   // the output is computed from what was stored
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) partial = fmaf(v[k][i], v[k][i], partial);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) partial += __shfl_xor_sync(0xFFFFFFFFu, partial, o);
+  if (tpr > 32) {
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = partial;
+    __syncthreads();
+    const int w0 = (threadIdx.x / tpr) * (tpr >> 5);
+    partial = 0.0f;
+    for (int w = 0; w < (tpr >> 5); ++w) partial += red[w0 + w];
+  }
+  const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(partial, static_cast<float>(cols)), eps)));
+  uint4* dst = reinterpret_cast<uint4*>(out + (live ? row : 0) * cols);
+  const uint4* wv = reinterpret_cast<const uint4*>(weight);
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int j = lane_in_row + k * tpr;
+    if (live && j < nvec) {
+      float w[V], y[V];
+      unpack<T>(__ldg(wv + j), w);
+#pragma unroll
+      for (int i = 0; i < V; ++i) y[i] = __fmul_rn(__fmul_rn(v[k][i], inv), w[i]);
+      dst[j] = pack<T>(y);
+    }
+  }
+}
+
+// Any shape and alignment: one CTA per row, two strided passes (the reference's own scheme).
+template <typename T, bool kAdd>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_any_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __restrict__ in,
+                   const T* __restrict__ weight, float eps, int cols) {
+  __shared__ float red[kThreads / 32];
+  const int64_t row = blockIdx.x;
+  const T* x = in + row * cols;
+  T* res = kAdd ? residual + row * cols : nullptr;
+  float partial = 0.0f;
+  for (int i = threadIdx.x; i < cols; i += kThreads) {
+    float v = to_f32<T>(x[i]);
+    if constexpr (kAdd) {
+      v = __fadd_rn(to_f32<T>(res[i]), v);
+      res[i] = from_f32<T>(v);   // the same thread reads it back below
+    }
+    partial = fmaf(v, v, partial);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) partial += __shfl_xor_sync(0xFFFFFFFFu, partial, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = partial;
+  __syncthreads();
+  partial = 0.0f;
+  for (int w = 0; w < kThreads / 32; ++w) partial += red[w];
+  const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(partial, static_cast<float>(cols)), eps)));
+  T* y = out + row * cols;
+  for (int i = threadIdx.x; i < cols; i += kThreads) {
+    const float v = to_f32<T>(kAdd ? res[i] : x[i]);
+    y[i] = from_f32<T>(__fmul_rn(__fmul_rn(v, inv), to_f32<T>(weight[i])));
+  }
+}
+
+template <typename T, bool kAdd>
+int launch_rmsnorm_t(void* out, void* residual, const void* in, const void* weight, int64_t rows, int64_t cols,
+                     float eps, cudaStream_t stream) {
+  constexpr int V = VecOf<T>::N;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(in) |
+                         reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(residual)) & 15u) == 0;
+  const int64_t nvec = cols / V;
+  if (aligned && cols % V == 0 && nvec <= static_cast<int64_t>(kThreads) * kMaxVec) {
+    int tpr = 32;
+    while (tpr < kThreads && static_cast<int64_t>(tpr) * 4 < nvec) tpr <<= 1;   // about four vectors per thread
+    while (static_cast<int64_t>(tpr) * kMaxVec < nvec) tpr <<= 1;
+    const int rows_per_cta = kThreads / tpr;
+    const int64_t grid = (rows + rows_per_cta - 1) / rows_per_cta;
+    if (grid > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
+    rmsnorm_vec_kernel<T, kAdd><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+        static_cast<T*>(out), static_cast<T*>(residual), static_cast<const T*>(in), static_cast<const T*>(weight),
+        eps, rows, static_cast<int>(cols), tpr);
+  } else {
+    if (rows > 0x7FFFFFFFLL || cols > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
+    rmsnorm_any_kernel<T, kAdd><<<static_cast<unsigned>(rows), kThreads, 0, stream>>>(
+        static_cast<T*>(out), static_cast<T*>(residual), static_cast<const T*>(in), static_cast<const T*>(weight),
+        eps, static_cast<int>(cols));
+  }
+  return check_launch();
+}
+
+// ------------------------------------------------------------------------------------- rotary embedding
+constexpr int kRopeThreads = 128;
+constexpr int kRopeHeadsPerCta = 8;
+constexpr int kRopeMaxHalf = 512;   // rotary_dim up to 1024
+
+// grid (tokens, ceil(heads / kRopeHeadsPerCta)).  kVec: 16-byte accesses (rotary_dim / 2 a multiple
+// of the vector length, rows 16-byte aligned); otherwise element by element.
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(kRopeThreads)
+rope_kernel(T* __restrict__ qkv, const int64_t* __restrict__ positions, int heads, int head_dim, int rotary_dim,
+            float base, float yarn) {
+  constexpr int V = VecOf<T>::N;
+  __shared__ float2 cs[kRopeMaxHalf];   // (cos, sin) of this token's angles
+  const int half = rotary_dim >> 1;
+  const int64_t t = blockIdx.x;
+  const float pos = static_cast<float>(__ldg(positions + t));
+  for (int i = threadIdx.x; i < half; i += kRopeThreads) {
+    // the golden code: freq = powf(base, -2 i / rotary_dim) * yarn in fp32; the power itself in
+    // double precision and rounded once, which is what a correctly rounded powf returns
+    const float e = __fdiv_rn(__fmul_rn(-2.0f, static_cast<float>(i)), static_cast<float>(rotary_dim));
+    const float pw = static_cast<float>(pow(static_cast<double>(base), static_cast<double>(e)));
+    const float theta = __fmul_rn(pos, __fmul_rn(pw, yarn));
+    double s, c;
+    sincos(static_cast<double>(theta), &s, &c);
+    cs[i] = make_float2(static_cast<float>(c), static_cast<float>(s));
+  }
+  __syncthreads();
+  const int h0 = blockIdx.y * kRopeHeadsPerCta;
+  const int h1 = min(heads, h0 + kRopeHeadsPerCta);
+  T* tok = qkv + t * heads * head_dim;
+  if constexpr (kVec) {
+    const int vec_per_head = half / V;
+    const int work = (h1 - h0) * vec_per_head;
+    for (int wi = threadIdx.x; wi < work; wi += kRopeThreads) {
+      const int h = h0 + wi / vec_per_head, j = wi % vec_per_head;
+      uint4* p0 = reinterpret_cast<uint4*>(tok + h * head_dim) + j;
+      uint4* p1 = reinterpret_cast<uint4*>(tok + h * head_dim + half) + j;
+      float x0[V], x1[V], y0[V], y1[V];
+      unpack<T>(*p0, x0);
+      unpack<T>(*p1, x1);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float2 a = cs[j * V + i];
+        y0[i] = __fsub_rn(__fmul_rn(x0[i], a.x), __fmul_rn(x1[i], a.y));
+        y1[i] = __fadd_rn(__fmul_rn(x1[i], a.x), __fmul_rn(x0[i], a.y));
+      }
+      *p0 = pack<T>(y0);
+      *p1 = pack<T>(y1);
+    }
+  } else {
+    const int work = (h1 - h0) * half;
+    for (int wi = threadIdx.x; wi < work; wi += kRopeThreads) {
+      const int h = h0 + wi / half, i = wi % half;
+      T* p = tok + h * head_dim;
+      const float x0 = to_f32<T>(p[i]), x1 = to_f32<T>(p[i + half]);
+      const float2 a = cs[i];
+      p[i] = from_f32<T>(__fsub_rn(__fmul_rn(x0, a.x), __fmul_rn(x1, a.y)));
+      p[i + half] = from_f32<T>(__fadd_rn(__fmul_rn(x1, a.x), __fmul_rn(x0, a.y)));
+    }
+  }
+}
+
+template <typename T>
+int launch_rope_t(void* qkv, const int64_t* positions, int64_t tokens, int heads, int head_dim, int rotary_dim,
+                  float base, float yarn, cudaStream_t stream) {
+  constexpr int V = VecOf<T>::N;
+  const int half = rotary_dim / 2;
+  const bool vec = (reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 && half % V == 0 &&
+                   (static_cast<int64_t>(head_dim) * sizeof(T)) % 16 == 0;
+  const dim3 grid(static_cast<unsigned>(tokens), static_cast<unsigned>((heads + kRopeHeadsPerCta - 1) / kRopeHeadsPerCta));
+  if (vec) {
+    rope_kernel<T, true><<<grid, kRopeThreads, 0, stream>>>(static_cast<T*>(qkv), positions, heads, head_dim,
+                                                            rotary_dim, base, yarn);
+  } else {
+    rope_kernel<T, false><<<grid, kRopeThreads, 0, stream>>>(static_cast<T*>(qkv), positions, heads, head_dim,
+                                                             rotary_dim, base, yarn);
+  }
+  return check_launch();
+}
+
+}  // namespace
+
+int launch_rmsnorm(void* out, void* residual, const void* in, const void* weight, int32_t dt, int64_t rows,
+                   int64_t cols, float eps, cudaStream_t stream) {
+  const bool add = residual != nullptr;
+  switch (dt) {
+    case 0: return add ? launch_rmsnorm_t<float, true>(out, residual, in, weight, rows, cols, eps, stream)
+                       : launch_rmsnorm_t<float, false>(out, nullptr, in, weight, rows, cols, eps, stream);
+    case 1: return add ? launch_rmsnorm_t<__half, true>(out, residual, in, weight, rows, cols, eps, stream)
+                       : launch_rmsnorm_t<__half, false>(out, nullptr, in, weight, rows, cols, eps, stream);
+    case 2: return add ? launch_rmsnorm_t<__nv_bfloat16, true>(out, residual, in, weight, rows, cols, eps, stream)
+                       : launch_rmsnorm_t<__nv_bfloat16, false>(out, nullptr, in, weight, rows, cols, eps, stream);
+    default: return INFEROP_ERR_DTYPE;
+  }
+}
+
+int launch_rope_neox(void* qkv, const int64_t* positions, int32_t dt, int64_t tokens, int heads, int head_dim,
+                     int rotary_dim, float base, float yarn, cudaStream_t stream) {
+  if (rotary_dim / 2 > kRopeMaxHalf) return INFEROP_ERR_LIMIT;
+  if (tokens > 0x7FFFFFFFLL || (heads + kRopeHeadsPerCta - 1) / kRopeHeadsPerCta > 65535) return INFEROP_ERR_LIMIT;
+  switch (dt) {
+    case 0: return launch_rope_t<float>(qkv, positions, tokens, heads, head_dim, rotary_dim, base, yarn, stream);
+    case 1: return launch_rope_t<__half>(qkv, positions, tokens, heads, head_dim, rotary_dim, base, yarn, stream);
+    case 2: return launch_rope_t<__nv_bfloat16>(qkv, positions, tokens, heads, head_dim, rotary_dim, base, yarn, stream);
+    default: return INFEROP_ERR_DTYPE;
+  }
+}
+
+}  // namespace ib200

@@ -302,6 +302,56 @@ def topk_softmax(logits: torch.Tensor, topk: int, renormalize: bool = True, ids:
     return ids, weights
 
 
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, out: torch.Tensor | None = None,
+            stream=None) -> torch.Tensor:
+    """out[r, c] = weight[c] * x[r, c] / sqrt(mean(x[r, :]^2) + eps); x [rows, cols], weight [cols], one dtype."""
+    _dev_tensor(x, "x")
+    _dev_tensor(weight, "weight")
+    if x.dim() != 2 or x.dtype not in _TORCH2CODE or weight.dtype != x.dtype or tuple(weight.shape) != (x.shape[1],):
+        raise ValueError("x must be [rows, cols] and weight [cols] of the same fp32/fp16/bf16 dtype")
+    rows, cols = x.shape
+    with torch.cuda.device(x.device):
+        if out is None:
+            out = torch.empty_like(x)
+        check(lib.inferop_rmsnorm(out.data_ptr(), x.data_ptr(), weight.data_ptr(), int(_TORCH2CODE[x.dtype]),
+                                  rows, cols, float(eps), _stream_ptr(stream)), "rmsnorm")
+    return out
+
+
+def fused_add_rmsnorm(residual: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                      out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """residual += x in place; returns rmsnorm(residual)."""
+    for t, name in ((residual, "residual"), (x, "x"), (weight, "weight")):
+        _dev_tensor(t, name)
+    if (x.dim() != 2 or x.dtype not in _TORCH2CODE or residual.shape != x.shape or residual.dtype != x.dtype
+            or weight.dtype != x.dtype or tuple(weight.shape) != (x.shape[1],) or not residual.is_contiguous()):
+        raise ValueError("residual and x must be contiguous [rows, cols], weight [cols], one fp32/fp16/bf16 dtype")
+    rows, cols = x.shape
+    with torch.cuda.device(x.device):
+        if out is None:
+            out = torch.empty_like(x)
+        check(lib.inferop_fused_add_rmsnorm(residual.data_ptr(), out.data_ptr(), x.data_ptr(), weight.data_ptr(),
+                                            int(_TORCH2CODE[x.dtype]), rows, cols, float(eps),
+                                            _stream_ptr(stream)), "fused_add_rmsnorm")
+    return out
+
+
+def rope_neox(qkv: torch.Tensor, positions: torch.Tensor, rotary_dim: int, base: float = 10000.0,
+              yarn_factor: float = 1.0, stream=None) -> torch.Tensor:
+    """NeoX rotary embedding in place on qkv [tokens, heads, head_dim]; positions int64 [tokens]."""
+    _dev_tensor(qkv, "qkv")
+    _dev_tensor(positions, "positions")
+    if qkv.dim() != 3 or qkv.dtype not in _TORCH2CODE or positions.dtype != torch.int64 or \
+            positions.numel() != qkv.shape[0]:
+        raise ValueError("qkv must be [tokens, heads, head_dim] (fp32/fp16/bf16) and positions int64 [tokens]")
+    tokens, heads, head_dim = qkv.shape
+    with torch.cuda.device(qkv.device):
+        check(lib.inferop_rope_neox(qkv.data_ptr(), positions.data_ptr(), int(_TORCH2CODE[qkv.dtype]), tokens,
+                                    heads, head_dim, int(rotary_dim), float(base), float(yarn_factor),
+                                    _stream_ptr(stream)), "rope_neox")
+    return qkv
+
+
 def silu_and_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, d + i] (reference include/inferop/ops.h:54-55)."""
     _dev_tensor(gate_up, "gate_up")

@@ -193,6 +193,40 @@ def silu_and_mul(gate_up):
     return out
 
 
+def rmsnorm(x, weight, eps: float = 1e-6):
+    """x fp32 [rows, cols], weight fp32 [cols] -> fp32 [rows, cols] (reference/reference.cpp:11-21)."""
+    x, weight = _f32(x), _f32(weight)
+    rows, cols = x.shape
+    out = np.empty_like(x)
+    if _lib.orc_rmsnorm(_ptr(out), _ptr(x), _ptr(weight), _i64(rows), _i64(cols), C.c_float(eps)) != 0:
+        raise ValueError("bad shape")
+    return out
+
+
+def fused_add_rmsnorm(residual, x, weight, eps: float = 1e-6):
+    """-> (residual + x, rmsnorm(residual + x)), both fp32 (reference/reference.cpp:23-35)."""
+    res = _f32(residual).copy()
+    x, weight = _f32(x), _f32(weight)
+    rows, cols = x.shape
+    out = np.empty_like(x)
+    if _lib.orc_fused_add_rmsnorm(_ptr(res), _ptr(out), _ptr(x), _ptr(weight), _i64(rows), _i64(cols),
+                                  C.c_float(eps)) != 0:
+        raise ValueError("bad shape")
+    return res, out
+
+
+def rope_neox(qkv, positions, rotary_dim: int, base: float = 10000.0, yarn_factor: float = 1.0):
+    """qkv fp32 [tokens, heads, head_dim], positions int64 [tokens] -> rotated copy
+    (reference/reference.cpp:37-53)."""
+    q = _f32(qkv).copy()
+    pos = np.ascontiguousarray(positions, dtype=np.int64)
+    tokens, heads, head_dim = q.shape
+    if _lib.orc_rope_neox(_ptr(q), _ptr(pos), _i64(tokens), _int(heads), _int(head_dim), _int(rotary_dim),
+                          C.c_float(base), C.c_float(yarn_factor)) != 0:
+        raise ValueError("bad shape")
+    return q
+
+
 def moe_align(topk_ids, experts: int, tile_rows: int = 128):
     """Expert-sorted layout of a routing: the checker of the device kernel that has no reference
     counterpart (the reference loops over experts on the host).  Pairs (token, k) are sorted by
@@ -304,6 +338,27 @@ class _Reference:
                                                 _ptr(bs), _i64(m), _i64(n), _i64(k),
                                                 _int(group_size), _int(block_n), _int(threads))
         return out
+
+    def rmsnorm(self, x, weight, eps=1e-6):
+        x, weight = _f32(x), _f32(weight)
+        out = np.empty_like(x)
+        self.lib.ref_rmsnorm(_ptr(out), _ptr(x), _ptr(weight), _i64(x.shape[0]), _i64(x.shape[1]), C.c_float(eps))
+        return out
+
+    def fused_add_rmsnorm(self, residual, x, weight, eps=1e-6):
+        res, x, weight = _f32(residual).copy(), _f32(x), _f32(weight)
+        out = np.empty_like(x)
+        self.lib.ref_fused_add_rmsnorm(_ptr(res), _ptr(out), _ptr(x), _ptr(weight), _i64(x.shape[0]),
+                                       _i64(x.shape[1]), C.c_float(eps))
+        return res, out
+
+    def rope_neox(self, qkv, positions, rotary_dim, base=10000.0, yarn_factor=1.0):
+        q = _f32(qkv).copy()
+        pos = np.ascontiguousarray(positions, dtype=np.int64)
+        t, h, d = q.shape
+        self.lib.ref_rope_neox(_ptr(q), _ptr(pos), _i64(t), _int(h), _int(d), _int(rotary_dim), C.c_float(base),
+                               C.c_float(yarn_factor))
+        return q
 
     def silu_and_mul(self, gate_up):
         gate_up = _f32(gate_up)

@@ -268,3 +268,67 @@ int orc_silu_and_mul(float* out, const float* gate_up, int64_t tokens, int64_t d
   return 0;
 }
 
+/* ---- RMSNorm (reference/reference.cpp:11-21) -----------------------------
+ * Per row: ss = sum of x^2 accumulated left to right in fp32, inv = 1 / sqrtf(ss / cols + eps),
+ * y = (x * inv) * w, every operation rounded to fp32. */
+int orc_rmsnorm(float* out, const float* in, const float* weight, int64_t rows, int64_t cols, float eps) {
+  if (rows < 0 || cols <= 0) return -1;
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* x = in + r * cols;
+    float* y = out + r * cols;
+    volatile float ss = 0.0f;
+    for (int64_t c = 0; c < cols; ++c) {
+      volatile float sq = x[c] * x[c];
+      ss = ss + sq;
+    }
+    volatile float mean = ss / (float)cols;
+    volatile float den = sqrtf(mean + eps);
+    const float inv = 1.0f / den;
+    for (int64_t c = 0; c < cols; ++c) {
+      volatile float t = x[c] * inv;
+      y[c] = t * weight[c];
+    }
+  }
+  return 0;
+}
+
+/* ---- residual add + RMSNorm (reference/reference.cpp:23-35) ---------------
+ * residual += x (in place), then RMSNorm of the updated residual. */
+int orc_fused_add_rmsnorm(float* residual, float* out, const float* x, const float* weight, int64_t rows,
+                          int64_t cols, float eps) {
+  if (rows < 0 || cols <= 0) return -1;
+  for (int64_t r = 0; r < rows; ++r) {
+    float* res = residual + r * cols;
+    const float* xr = x + r * cols;
+    for (int64_t c = 0; c < cols; ++c) res[c] = res[c] + xr[c];
+  }
+  return orc_rmsnorm(out, residual, weight, rows, cols, eps);
+}
+
+/* ---- rotary embedding, GPT-NeoX layout (reference/reference.cpp:37-53) ------
+ * In place on qkv [tokens, heads, head_dim]: for i < rotary_dim / 2,
+ * freq = powf(base, -2 i / rotary_dim) * yarn_factor, theta = (float)position * freq,
+ * (x_i, x_{i+half}) rotated by theta; elements from rotary_dim on are left alone. */
+int orc_rope_neox(float* qkv, const int64_t* positions, int64_t tokens, int heads, int head_dim, int rotary_dim,
+                  float base, float yarn_factor) {
+  if (tokens < 0 || heads <= 0 || head_dim <= 0 || rotary_dim <= 0 || rotary_dim > head_dim || (rotary_dim & 1))
+    return -1;
+  const int half = rotary_dim / 2;
+  for (int64_t t = 0; t < tokens; ++t) {
+    for (int h = 0; h < heads; ++h) {
+      float* p = qkv + (t * heads + h) * head_dim;
+      for (int i = 0; i < half; ++i) {
+        volatile float e = -2.0f * (float)i / (float)rotary_dim;
+        volatile float pw = powf(base, e);
+        volatile float freq = pw * yarn_factor;
+        volatile float theta = (float)positions[t] * freq;
+        const float c = cosf(theta), s = sinf(theta);
+        const float x0 = p[i], x1 = p[i + half];
+        volatile float a = x0 * c, b = x1 * s, d = x1 * c, g = x0 * s;
+        p[i] = a - b;
+        p[i + half] = d + g;
+      }
+    }
+  }
+  return 0;
+}

@@ -47,6 +47,17 @@ void ref_topk_softmax(int32_t* ids, float* w, const float* logits, int64_t token
   r::topk_softmax(ids, w, logits, tokens, experts, topk, renorm != 0);
 }
 
+void ref_rmsnorm(float* out, const float* in, const float* weight, int64_t rows, int64_t cols, float eps) {
+  r::rmsnorm(out, in, weight, rows, cols, eps);
+}
+void ref_fused_add_rmsnorm(float* residual, float* out, const float* x, const float* weight, int64_t rows,
+                           int64_t cols, float eps) {
+  r::fused_add_rmsnorm(residual, out, x, weight, rows, cols, eps);
+}
+void ref_rope_neox(float* qkv, const int64_t* positions, int64_t tokens, int heads, int head_dim, int rotary_dim,
+                   float base, float yarn_factor) {
+  r::rope_neox(qkv, positions, tokens, heads, head_dim, rotary_dim, base, yarn_factor);
+}
 void ref_silu_and_mul(float* out, const float* gate_up, int64_t tokens, int64_t d) {
   r::silu_and_mul(out, gate_up, tokens, d);
 }

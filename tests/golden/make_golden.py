@@ -134,7 +134,36 @@ def moe():
     np.savez_compressed(os.path.join(HERE, "moe_golden.npz"), **out)
 
 
+def norm_rope():
+    """RMSNorm, residual add + RMSNorm and the NeoX rotary embedding from the reference's CPU
+    functions (reference.cpp:11-53) on cut-down shapes of its own tests (tests/test_rmsnorm.cpp:8-10,
+    tests/test_rope.cpp:8-11: fewer rows and heads, the same row length, head size, rotary size and
+    positions) plus long positions and a scaled base."""
+    rng = np.random.default_rng(33)
+    out = {}
+    x = rng.standard_normal((9, 1024)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, 1024).astype(np.float32)
+    res = rng.standard_normal((9, 1024)).astype(np.float32)
+    out["x"], out["w"], out["res"] = x, w, res
+    out["rms"] = R.rmsnorm(x, w, 1e-6)
+    out["fused_res"], out["fused_out"] = R.fused_add_rmsnorm(res, x, w, 1e-6)
+    q = rng.standard_normal((64, 3, 128)).astype(np.float32)
+    pos = np.array([t * 17 + (t % 3) for t in range(64)], np.int64)
+    out["q"], out["pos"] = q, pos
+    out["rope"] = R.rope_neox(q, pos, 64, 10000.0, 1.0)
+    q2 = rng.standard_normal((16, 4, 64)).astype(np.float32)
+    pos2 = rng.integers(0, 131072, 16).astype(np.int64)
+    out["q2"], out["pos2"] = q2, pos2
+    out["rope2"] = R.rope_neox(q2, pos2, 64, 500000.0, 0.25)
+    np.savez_compressed(os.path.join(HERE, "norm_rope_golden.npz"), **out)
+
+
 if __name__ == "__main__":
+    only = sys.argv[1:]
+    if only == ["norm_rope"]:
+        norm_rope()
+        sys.exit(0)
+    norm_rope()
     moe()
     codec()
     quant()

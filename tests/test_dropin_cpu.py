@@ -28,7 +28,8 @@ def _build(name, tmp_path):
     return exe
 
 
-@pytest.mark.parametrize("name", ["test_fp8", "test_quant", "test_gemm", "test_topk", "test_silu_mul"])
+@pytest.mark.parametrize("name", ["test_fp8", "test_quant", "test_gemm", "test_topk", "test_silu_mul", "test_rmsnorm",
+                                  "test_rope"])
 def test_reference_test_program_builds_and_its_cpu_half_passes(name, tmp_path):
     import torch
     exe = _build(name, tmp_path)

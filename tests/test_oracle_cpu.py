@@ -254,3 +254,71 @@ def test_sampled_checker_equals_the_full_oracle_on_the_sampled_entries():
     bad = aq.copy()
     bad[rows[2], 7] ^= 1
     assert not sampled.quant_rows_exact(x16, t(bad), t(a_s), rows)
+
+
+# ------------------------------------------------------------------ rmsnorm / rope (the "next" operators)
+def _norm_case(rows=33, cols=1024, seed=0):
+    rng = np.random.default_rng(seed)
+    return (rng.standard_normal((rows, cols)).astype(np.float32),
+            rng.uniform(0.5, 1.5, cols).astype(np.float32))
+
+
+def test_rmsnorm_properties_of_the_reference_test():
+    """tests/test_rmsnorm.cpp:12-43: unit weights give RMS 1; the fused form adds in place."""
+    x, w = _norm_case()
+    y1 = oracle.rmsnorm(x, np.ones_like(w))
+    assert abs(np.sqrt(np.mean(y1.astype(np.float64) ** 2)) - 1.0) < 1e-3
+    res, xr = _norm_case(seed=1)[0], _norm_case(seed=2)[0]
+    new_res, out = oracle.fused_add_rmsnorm(res, xr, w)
+    assert np.array_equal(new_res, res + xr)
+    assert np.array_equal(out, oracle.rmsnorm(new_res, w))
+
+
+def test_rope_properties_of_the_reference_test():
+    """tests/test_rope.cpp:14-52: pair norms preserved, position 0 is the identity, the tail beyond
+    rotary_dim is untouched."""
+    rng = np.random.default_rng(3)
+    tokens, heads, dim, rot = 64, 32, 128, 64
+    q = rng.standard_normal((tokens, heads, dim)).astype(np.float32)
+    pos = np.array([t * 17 + (t % 3) for t in range(tokens)], np.int64)
+    r = oracle.rope_neox(q, pos, rot)
+    half = rot // 2
+    n0 = np.hypot(q[..., :half].astype(np.float64), q[..., half:rot])
+    n1 = np.hypot(r[..., :half].astype(np.float64), r[..., half:rot])
+    assert np.abs(n0 - n1).max() < 1e-4
+    assert np.array_equal(r[..., rot:], q[..., rot:])
+    ident = oracle.rope_neox(q, np.zeros(tokens, np.int64), rot)
+    np.testing.assert_allclose(ident, q, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.skipif(not oracle.have_reference(), reason="reference tree not built here")
+def test_rmsnorm_and_rope_restatements_equal_the_reference_bit_for_bit():
+    R = oracle.reference
+    for rows, cols, seed in ((33, 1024, 0), (1, 7168, 1), (7, 130, 2), (4, 1, 3)):
+        x, w = _norm_case(rows, cols, seed)
+        for eps in (1e-6, 1e-5):
+            assert np.array_equal(oracle.rmsnorm(x, w, eps).view(np.uint32), R.rmsnorm(x, w, eps).view(np.uint32))
+            res = _norm_case(rows, cols, seed + 10)[0]
+            a, b = oracle.fused_add_rmsnorm(res, x, w, eps), R.fused_add_rmsnorm(res, x, w, eps)
+            assert np.array_equal(a[0].view(np.uint32), b[0].view(np.uint32))
+            assert np.array_equal(a[1].view(np.uint32), b[1].view(np.uint32))
+    rng = np.random.default_rng(5)
+    for tokens, heads, dim, rot, base, yarn in ((64, 32, 128, 64, 10000.0, 1.0), (5, 3, 64, 64, 500000.0, 0.25),
+                                                (9, 1, 256, 2, 10000.0, 1.0), (3, 8, 96, 48, 10000.0, 1.0)):
+        q = rng.standard_normal((tokens, heads, dim)).astype(np.float32)
+        pos = rng.integers(0, 131072, tokens).astype(np.int64)
+        pos[0] = 0
+        assert np.array_equal(oracle.rope_neox(q, pos, rot, base, yarn).view(np.uint32),
+                              R.rope_neox(q, pos, rot, base, yarn).view(np.uint32))
+
+
+def test_rmsnorm_and_rope_golden_vectors():
+    """Vectors written by the reference's own CPU functions (tests/golden/make_golden.py: norm_rope)."""
+    g = np.load(os.path.join(GOLDEN, "norm_rope_golden.npz"))
+    assert np.array_equal(oracle.rmsnorm(g["x"], g["w"]).view(np.uint32), g["rms"].view(np.uint32))
+    res, out = oracle.fused_add_rmsnorm(g["res"], g["x"], g["w"])
+    assert np.array_equal(res.view(np.uint32), g["fused_res"].view(np.uint32))
+    assert np.array_equal(out.view(np.uint32), g["fused_out"].view(np.uint32))
+    assert np.array_equal(oracle.rope_neox(g["q"], g["pos"], 64).view(np.uint32), g["rope"].view(np.uint32))
+    assert np.array_equal(oracle.rope_neox(g["q2"], g["pos2"], 64, 500000.0, 0.25).view(np.uint32),
+                          g["rope2"].view(np.uint32))
