@@ -89,6 +89,7 @@ def parse_args():
     ap.add_argument("--moe-only", action="store_true",
                     help="run only the MoE section (grouped GEMMs and the expert layer) and print it")
     ap.add_argument("--refcuda-only", action="store_true", help="run only the secondary GPU baseline (the reference's CUDA kernels)")
+    ap.add_argument("--block-ops-only", action="store_true", help="run only the RMSNorm / rotary-embedding timings")
     ap.add_argument("--sweep-only", action="store_true", help="run only the decode / prefill shape sweep and print it")
     ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE",
                     help="library tuning option (inferop_set_option), e.g. --set gemm_pair=0; may be repeated")
@@ -331,6 +332,68 @@ def reference_cuda_baseline(m=4096, n=18432, k=7168, iters=3):
 
 
 # ----------------------------------------------------------------------------- shape sweep
+def block_ops(peaks, rows=16384, cols=7168, heads=32, head_dim=128, rotary=64):
+    """The operators in front of the quantise + GEMM path in a transformer block (RMSNorm, residual add +
+    RMSNorm, NeoX rotary embedding), bf16, device-timed on tensors larger than L2, each checked against
+    the oracle on sampled rows after the timing."""
+    import numpy as np
+    import torch
+    import oracle
+    from inference_b200 import ops, synth
+    x = synth.activations(rows, cols, seed=41, outliers=False)
+    res = synth.activations(rows, cols, seed=42, outliers=False)
+    w = (0.5 + torch.rand(cols, device="cuda")).to(torch.bfloat16)
+    out = torch.empty_like(x)
+    qkv = synth.activations(rows, heads * head_dim, seed=43, outliers=False).view(rows, heads, head_dim)
+    pos = torch.arange(rows, dtype=torch.int64, device="cuda") * 7 % 131072
+
+    def timed(fn, iters=10):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / iters
+
+    rec = {}
+    rows_s = np.array([0, 1, rows // 2, rows - 1])
+    t = timed(lambda: ops.rmsnorm(x, w, 1e-6, out=out))
+    want = oracle.rmsnorm(x[rows_s].float().cpu().numpy(), w.float().cpu().numpy())
+    err = float(np.abs(out[rows_s].float().cpu().numpy() - want).max())
+    assert err <= 2e-2 * (1 + float(np.abs(want).max())), f"rmsnorm off by {err}"
+    byt = 4 * rows * cols
+    rec["rmsnorm"] = {"us": round(t * 1e6, 1), "gbs": round(byt / t / 1e9, 1),
+                      "frac_of_measured_hbm": round(byt / t / 1e9 / peaks["hbm_gbs"], 3), "max_abs_err": err}
+    res0 = res.clone()
+    t = timed(lambda: ops.fused_add_rmsnorm(res, x, w, 1e-6, out=out))
+    r1 = res0.clone()
+    ops.fused_add_rmsnorm(r1, x, w, 1e-6, out=out)
+    want_res, want_out = oracle.fused_add_rmsnorm(res0[rows_s].float().cpu().numpy(), x[rows_s].float().cpu().numpy(),
+                                                  w.float().cpu().numpy())
+    err = float(np.abs(out[rows_s].float().cpu().numpy() - want_out).max())
+    assert err <= 3e-2 * (1 + float(np.abs(want_out).max())), f"fused_add_rmsnorm off by {err}"
+    byt = 8 * rows * cols
+    rec["fused_add_rmsnorm"] = {"us": round(t * 1e6, 1), "gbs": round(byt / t / 1e9, 1),
+                                "frac_of_measured_hbm": round(byt / t / 1e9 / peaks["hbm_gbs"], 3), "max_abs_err": err}
+    q0 = qkv.clone()
+    t = timed(lambda: ops.rope_neox(qkv, pos, rotary))
+    q1 = q0.clone()
+    ops.rope_neox(q1, pos, rotary)
+    want = oracle.rope_neox(q0[rows_s].float().cpu().numpy(), pos[rows_s].cpu().numpy(), rotary)
+    err = float(np.abs(q1[rows_s].float().cpu().numpy() - want).max())
+    assert err <= 2e-2 * (1 + float(np.abs(want).max())), f"rope off by {err}"
+    byt = 4 * rows * heads * rotary   # only the rotated part of every head is read and written
+    rec["rope_neox"] = {"us": round(t * 1e6, 1), "gbs": round(byt / t / 1e9, 1),
+                        "frac_of_measured_hbm": round(byt / t / 1e9 / peaks["hbm_gbs"], 3), "max_abs_err": err,
+                        "shape": [rows, heads, head_dim], "rotary_dim": rotary}
+    rec["shape"] = [rows, cols]
+    rec["dtype"] = "bf16"
+    return rec
+
+
 def shape_sweep(peaks):
     """Decode (HBM-bound) and prefill (tensor-bound) shapes of the benchmark configs, quant + GEMM,
     device-timed.  Small shapes are replayed from a CUDA graph of 10 steps so that host launch cost
@@ -1065,7 +1128,7 @@ def run_ours(args):
         torch.cuda.empty_cache()
         line["moe"] = moe_config(peaks, experts=args.moe_experts, tokens=args.moe_tokens)
         torch.cuda.empty_cache()
-        line["extra"] = {"reference_cuda": reference_cuda_baseline()}
+        line["extra"] = {"reference_cuda": reference_cuda_baseline(), "block_ops": block_ops(peaks)}
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         smp = sized_cpu_sample(k, threads, args.cpu_seconds)
@@ -1096,6 +1159,8 @@ def main():
             run_reference(args)
         elif args.refcuda_only:
             print_result(json.dumps({"reference_cuda": reference_cuda_baseline()}))
+        elif args.block_ops_only:
+            print_result(json.dumps({"block_ops": block_ops(measured_peaks())}))
         elif args.moe_only or args.sweep_only:
             from inference_b200 import ops
             for kv in args.set:

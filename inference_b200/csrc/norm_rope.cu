@@ -7,12 +7,13 @@
 //     it (16-byte loads, up to eight vectors per thread), so it is read from memory once; 32 to 256
 //     threads per row depending on its length, several rows per CTA when rows are short.
 //   * rope_kernel: the angle of (position, i) does not depend on the head, so a CTA computes the
-//     cos / sin table of its token once (frequencies in double precision, which reproduces the
-//     CPU golden's powf bit for bit; at position 100 000 two units in the last place of a
-//     single-precision powf are 0.02 rad) and applies it to a block of heads with 16-byte accesses.
+//     cos / sin table of its token once and applies it to a block of heads with 16-byte accesses.
+//     The frequencies come from the host (the C library's powf, as in the CPU golden: at position
+//     100 000 two units in the last place of a device powf would be 0.02 rad).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 
 #include "internal.h"
@@ -62,8 +63,9 @@ __device__ __forceinline__ uint4 pack(const float (&f)[VecOf<T>::N]) {
 
 // kAdd: residual[r, :] += x[r, :] first (stored in T), then the norm of the sum.  As in the
 // reference's kernel the sum of squares uses the unrounded sums and the output the stored ones.
-// tpr = threads per row (a power of two, 32 .. 256); rows per CTA = 256 / tpr.
-template <typename T, bool kAdd>
+// tpr = threads per row (a power of two, 32 .. 256); rows per CTA = 256 / tpr; NV = 16-byte
+// vectors of the row per thread, kept packed in registers between the two passes.
+template <typename T, bool kAdd, int NV>
 __global__ void __launch_bounds__(kThreads)
 rmsnorm_vec_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __restrict__ in,
                    const T* __restrict__ weight, float eps, int64_t rows, int cols, int tpr) {
@@ -76,27 +78,32 @@ rmsnorm_vec_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __res
   const uint4* src = reinterpret_cast<const uint4*>(in + (live ? row : 0) * cols);
   uint4* res = kAdd ? reinterpret_cast<uint4*>(residual + (live ? row : 0) * cols) : nullptr;
 
-  float v[kMaxVec][V];
+  uint4 raw[NV], rraw[kAdd ? NV : 1];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int j = lane_in_row + k * tpr;
+    const bool have = live && j < nvec;
+    raw[k] = have ? __ldg(src + j) : make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (kAdd) rraw[k] = have ? res[j] : make_uint4(0u, 0u, 0u, 0u);
+  }
   float partial = 0.0f;
 #pragma unroll
-  for (int k = 0; k < kMaxVec; ++k) {
-    const int j = lane_in_row + k * tpr;
-    if (live && j < nvec) {
-      unpack<T>(__ldg(src + j), v[k]);
-      if constexpr (kAdd) {
-        float r[V];
-        unpack<T>(res[j], r);
+  for (int k = 0; k < NV; ++k) {
+    float v[V];
+    unpack<T>(raw[k], v);
+    if constexpr (kAdd) {
+      float r[V];
+      unpack<T>(rraw[k], r);
 #pragma unroll
-        for (int i = 0; i < V; ++i) r[i] = __fadd_rn(r[i], v[k][i]);
+      for (int i = 0; i < V; ++i) r[i] = __fadd_rn(r[i], v[i]);
 #pragma unroll
-        for (int i = 0; i < V; ++i) partial = fmaf(r[i], r[i], partial);
-        const uint4 stored = pack<T>(r);
-        res[j] = stored;
-        unpack<T>(stored, v[k]);   // the output is computed from what was stored
-      } else {
+      for (int i = 0; i < V; ++i) partial = fmaf(r[i], r[i], partial);
+      raw[k] = pack<T>(r);   // what is stored; the output is computed from it
+      const int j = lane_in_row + k * tpr;
+      if (live && j < nvec) res[j] = raw[k];
+    } else {
 #pragma unroll
-        for (int i = 0; i < V; ++i) partial = fmaf(v[k][i], v[k][i], partial);
-      }
+      for (int i = 0; i < V; ++i) partial = fmaf(v[i], v[i], partial);
     }
   }
 #pragma unroll
@@ -112,13 +119,14 @@ rmsnorm_vec_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __res
   uint4* dst = reinterpret_cast<uint4*>(out + (live ? row : 0) * cols);
   const uint4* wv = reinterpret_cast<const uint4*>(weight);
 #pragma unroll
-  for (int k = 0; k < kMaxVec; ++k) {
+  for (int k = 0; k < NV; ++k) {
     const int j = lane_in_row + k * tpr;
     if (live && j < nvec) {
-      float w[V], y[V];
+      float v[V], w[V], y[V];
+      unpack<T>(raw[k], v);
       unpack<T>(__ldg(wv + j), w);
 #pragma unroll
-      for (int i = 0; i < V; ++i) y[i] = __fmul_rn(__fmul_rn(v[k][i], inv), w[i]);
+      for (int i = 0; i < V; ++i) y[i] = __fmul_rn(__fmul_rn(v[i], inv), w[i]);
       dst[j] = pack<T>(y);
     }
   }
@@ -166,13 +174,20 @@ int launch_rmsnorm_t(void* out, void* residual, const void* in, const void* weig
   if (aligned && cols % V == 0 && nvec <= static_cast<int64_t>(kThreads) * kMaxVec) {
     int tpr = 32;
     while (tpr < kThreads && static_cast<int64_t>(tpr) * 4 < nvec) tpr <<= 1;   // about four vectors per thread
-    while (static_cast<int64_t>(tpr) * kMaxVec < nvec) tpr <<= 1;
+    const int per_thread = static_cast<int>((nvec + tpr - 1) / tpr);
     const int rows_per_cta = kThreads / tpr;
     const int64_t grid = (rows + rows_per_cta - 1) / rows_per_cta;
     if (grid > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
-    rmsnorm_vec_kernel<T, kAdd><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-        static_cast<T*>(out), static_cast<T*>(residual), static_cast<const T*>(in), static_cast<const T*>(weight),
-        eps, rows, static_cast<int>(cols), tpr);
+    T* o = static_cast<T*>(out);
+    T* r = static_cast<T*>(residual);
+    const T* i = static_cast<const T*>(in);
+    const T* w = static_cast<const T*>(weight);
+    const unsigned g = static_cast<unsigned>(grid);
+    const int c = static_cast<int>(cols);
+    if (per_thread <= 1) rmsnorm_vec_kernel<T, kAdd, 1><<<g, kThreads, 0, stream>>>(o, r, i, w, eps, rows, c, tpr);
+    else if (per_thread <= 2) rmsnorm_vec_kernel<T, kAdd, 2><<<g, kThreads, 0, stream>>>(o, r, i, w, eps, rows, c, tpr);
+    else if (per_thread <= 4) rmsnorm_vec_kernel<T, kAdd, 4><<<g, kThreads, 0, stream>>>(o, r, i, w, eps, rows, c, tpr);
+    else rmsnorm_vec_kernel<T, kAdd, kMaxVec><<<g, kThreads, 0, stream>>>(o, r, i, w, eps, rows, c, tpr);
   } else {
     if (rows > 0x7FFFFFFFLL || cols > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
     rmsnorm_any_kernel<T, kAdd><<<static_cast<unsigned>(rows), kThreads, 0, stream>>>(
@@ -184,52 +199,71 @@ int launch_rmsnorm_t(void* out, void* residual, const void* in, const void* weig
 
 // ------------------------------------------------------------------------------------- rotary embedding
 constexpr int kRopeThreads = 128;
-constexpr int kRopeHeadsPerCta = 8;
 constexpr int kRopeMaxHalf = 512;   // rotary_dim up to 1024
 
-// grid (tokens, ceil(heads / kRopeHeadsPerCta)).  kVec: 16-byte accesses (rotary_dim / 2 a multiple
-// of the vector length, rows 16-byte aligned); otherwise element by element.
+// The frequencies base^(-2 i / rotary_dim) * yarn depend on i only: the launcher computes them on the
+// host with the C library's powf, the very function the CPU golden calls, and passes them in the
+// kernel's parameter block.
+struct RopeFreq {
+  float f[kRopeMaxHalf];
+};
+
+// grid (tokens, ceil(heads / heads_per_cta)).  kVec: 16-byte accesses (rotary_dim / 2 a multiple of the
+// vector length, rows 16-byte aligned); otherwise element by element.
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kRopeThreads)
 rope_kernel(T* __restrict__ qkv, const int64_t* __restrict__ positions, int heads, int head_dim, int rotary_dim,
-            float base, float yarn) {
+            int heads_per_cta, const __grid_constant__ RopeFreq freq) {
   constexpr int V = VecOf<T>::N;
+  constexpr int kItems = 4;             // vector pairs a thread handles per CTA (the launcher sizes the head block so)
   __shared__ float2 cs[kRopeMaxHalf];   // (cos, sin) of this token's angles
   const int half = rotary_dim >> 1;
   const int64_t t = blockIdx.x;
-  const float pos = static_cast<float>(__ldg(positions + t));
-  for (int i = threadIdx.x; i < half; i += kRopeThreads) {
-    // the golden code: freq = powf(base, -2 i / rotary_dim) * yarn in fp32; the power itself in
-    // double precision and rounded once, which is what a correctly rounded powf returns
-    const float e = __fdiv_rn(__fmul_rn(-2.0f, static_cast<float>(i)), static_cast<float>(rotary_dim));
-    const float pw = static_cast<float>(pow(static_cast<double>(base), static_cast<double>(e)));
-    const float theta = __fmul_rn(pos, __fmul_rn(pw, yarn));
-    double s, c;
-    sincos(static_cast<double>(theta), &s, &c);
-    cs[i] = make_float2(static_cast<float>(c), static_cast<float>(s));
-  }
-  __syncthreads();
-  const int h0 = blockIdx.y * kRopeHeadsPerCta;
-  const int h1 = min(heads, h0 + kRopeHeadsPerCta);
+  const int h0 = blockIdx.y * heads_per_cta;
+  const int h1 = min(heads, h0 + heads_per_cta);
   T* tok = qkv + t * heads * head_dim;
+  // the operands are requested before the table is computed, so that the two latencies overlap
+  uint4 r0[kVec ? kItems : 1], r1[kVec ? kItems : 1];
   if constexpr (kVec) {
     const int vec_per_head = half / V;
     const int work = (h1 - h0) * vec_per_head;
-    for (int wi = threadIdx.x; wi < work; wi += kRopeThreads) {
-      const int h = h0 + wi / vec_per_head, j = wi % vec_per_head;
-      uint4* p0 = reinterpret_cast<uint4*>(tok + h * head_dim) + j;
-      uint4* p1 = reinterpret_cast<uint4*>(tok + h * head_dim + half) + j;
-      float x0[V], x1[V], y0[V], y1[V];
-      unpack<T>(*p0, x0);
-      unpack<T>(*p1, x1);
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        const float2 a = cs[j * V + i];
-        y0[i] = __fsub_rn(__fmul_rn(x0[i], a.x), __fmul_rn(x1[i], a.y));
-        y1[i] = __fadd_rn(__fmul_rn(x1[i], a.x), __fmul_rn(x0[i], a.y));
+    for (int k = 0; k < kItems; ++k) {
+      const int wi = threadIdx.x + k * kRopeThreads;
+      if (wi < work) {
+        const int h = h0 + wi / vec_per_head, j = wi % vec_per_head;
+        r0[k] = *(reinterpret_cast<const uint4*>(tok + h * head_dim) + j);
+        r1[k] = *(reinterpret_cast<const uint4*>(tok + h * head_dim + half) + j);
       }
-      *p0 = pack<T>(y0);
-      *p1 = pack<T>(y1);
+    }
+  }
+  const float pos = static_cast<float>(__ldg(positions + t));
+  for (int i = threadIdx.x; i < half; i += kRopeThreads) {
+    float sn, c;
+    sincosf(__fmul_rn(pos, freq.f[i]), &sn, &c);   // the accurate version: angles reach 1e5 rad
+    cs[i] = make_float2(c, sn);
+  }
+  __syncthreads();
+  if constexpr (kVec) {
+    const int vec_per_head = half / V;
+    const int work = (h1 - h0) * vec_per_head;
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const int wi = threadIdx.x + k * kRopeThreads;
+      if (wi < work) {
+        const int h = h0 + wi / vec_per_head, j = wi % vec_per_head;
+        float x0[V], x1[V], y0[V], y1[V];
+        unpack<T>(r0[k], x0);
+        unpack<T>(r1[k], x1);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const float2 a = cs[j * V + i];
+          y0[i] = __fsub_rn(__fmul_rn(x0[i], a.x), __fmul_rn(x1[i], a.y));
+          y1[i] = __fadd_rn(__fmul_rn(x1[i], a.x), __fmul_rn(x0[i], a.y));
+        }
+        *(reinterpret_cast<uint4*>(tok + h * head_dim) + j) = pack<T>(y0);
+        *(reinterpret_cast<uint4*>(tok + h * head_dim + half) + j) = pack<T>(y1);
+      }
     }
   } else {
     const int work = (h1 - h0) * half;
@@ -249,15 +283,31 @@ int launch_rope_t(void* qkv, const int64_t* positions, int64_t tokens, int heads
                   float base, float yarn, cudaStream_t stream) {
   constexpr int V = VecOf<T>::N;
   const int half = rotary_dim / 2;
+  RopeFreq freq;
+  for (int i = 0; i < half; ++i) {
+    // reference/reference.cpp:44: std::pow(base, -2.0f * float(i) / float(rotary_dim)) * yarn_factor
+    volatile float e = -2.0f * static_cast<float>(i) / static_cast<float>(rotary_dim);
+    volatile float pw = powf(base, e);
+    freq.f[i] = pw * yarn;
+  }
+  for (int i = half; i < kRopeMaxHalf; ++i) freq.f[i] = 0.0f;
   const bool vec = (reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 && half % V == 0 &&
                    (static_cast<int64_t>(head_dim) * sizeof(T)) % 16 == 0;
-  const dim3 grid(static_cast<unsigned>(tokens), static_cast<unsigned>((heads + kRopeHeadsPerCta - 1) / kRopeHeadsPerCta));
+  // at most four work items per thread and CTA (the vector kernel holds that many in registers);
+  // a token's table is computed once per CTA
+  const int items_per_head = vec ? half / V : half;
+  int hpc = 4 * kRopeThreads / items_per_head;
+  if (hpc > heads) hpc = heads;
+  if (hpc < 1) hpc = 1;
+  const int chunks = (heads + hpc - 1) / hpc;
+  if (chunks > 65535) return INFEROP_ERR_LIMIT;
+  const dim3 grid(static_cast<unsigned>(tokens), static_cast<unsigned>(chunks));
   if (vec) {
     rope_kernel<T, true><<<grid, kRopeThreads, 0, stream>>>(static_cast<T*>(qkv), positions, heads, head_dim,
-                                                            rotary_dim, base, yarn);
+                                                            rotary_dim, hpc, freq);
   } else {
     rope_kernel<T, false><<<grid, kRopeThreads, 0, stream>>>(static_cast<T*>(qkv), positions, heads, head_dim,
-                                                             rotary_dim, base, yarn);
+                                                             rotary_dim, hpc, freq);
   }
   return check_launch();
 }
@@ -281,7 +331,7 @@ int launch_rmsnorm(void* out, void* residual, const void* in, const void* weight
 int launch_rope_neox(void* qkv, const int64_t* positions, int32_t dt, int64_t tokens, int heads, int head_dim,
                      int rotary_dim, float base, float yarn, cudaStream_t stream) {
   if (rotary_dim / 2 > kRopeMaxHalf) return INFEROP_ERR_LIMIT;
-  if (tokens > 0x7FFFFFFFLL || (heads + kRopeHeadsPerCta - 1) / kRopeHeadsPerCta > 65535) return INFEROP_ERR_LIMIT;
+  if (tokens > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
   switch (dt) {
     case 0: return launch_rope_t<float>(qkv, positions, tokens, heads, head_dim, rotary_dim, base, yarn, stream);
     case 1: return launch_rope_t<__half>(qkv, positions, tokens, heads, head_dim, rotary_dim, base, yarn, stream);
