@@ -76,6 +76,16 @@ INFEROP_EXPORT void rope_neox(void* qkv, const int64_t* positions, dtype dt, int
 INFEROP_EXPORT void silu_and_mul(void* out, const void* gate_up, dtype dt, int64_t tokens, int64_t d,
                   void* stream = nullptr);
 
+// Paged attention (single-token decode, GQA):
+//   q / out [batch, num_heads, head_dim], k_cache / v_cache [num_blocks, block_size, num_kv_heads, head_dim] (dt),
+//   block_tables int32 [batch, max_blocks_per_seq], seq_lens int32 [batch].
+// head_dim in {64, 128, 256}; num_heads % num_kv_heads == 0; anything else is a silent no-op.
+INFEROP_EXPORT void paged_attn_decode(void* out, const void* q, const void* k_cache, const void* v_cache,
+                       const int32_t* block_tables, const int32_t* seq_lens, dtype dt,
+                       int batch, int num_heads, int num_kv_heads, int head_dim,
+                       int block_size, int max_blocks_per_seq, float scale,
+                       void* stream = nullptr);
+
 // MoE routing: softmax over logits [tokens, num_experts] (fp32) + top-k.
 //   topk_weights fp32 [tokens, topk] (softmax probability, renormalised over the k when asked)
 //   topk_ids     int32 [tokens, topk]; equal probabilities: the lower expert index first

@@ -229,6 +229,20 @@ INFEROP_API int inferop_fused_add_rmsnorm(void* residual, void* out, const void*
 INFEROP_API int inferop_rope_neox(void* qkv, const int64_t* positions, int32_t dt, int64_t tokens, int32_t heads,
                       int32_t head_dim, int32_t rotary_dim, float base, float yarn_factor, void* stream);
 
+/* Paged attention, single-token decode with grouped-query heads (reference ops.h:96-100,
+ * kernels/attention/paged_attn_decode.cu:26-118, CPU reference.cpp:112-150):
+ *   q / out [batch, num_heads, head_dim] in dt; k_cache / v_cache [blocks, block_size, num_kv_heads,
+ *   head_dim] in dt (16-byte aligned); block_tables int32 [batch, max_blocks_per_seq]; seq_lens int32
+ *   [batch] (clamped to max_blocks_per_seq * block_size); out = softmax(q k^T * scale) v per head, an
+ *   empty sequence gives zeros.  head_dim in {64, 128, 256} (the reference's list; anything else is
+ *   INFEROP_ERR_SHAPE where the reference does nothing), num_heads % num_kv_heads == 0, batch <= 65535.
+ * Long sequences are processed as several token ranges whose partial results live in scratch of the
+ * stream (allocated by the first call that needs it: make one call before capturing a CUDA graph). */
+INFEROP_API int inferop_paged_attn_decode(void* out, const void* q, const void* k_cache, const void* v_cache,
+                              const int32_t* block_tables, const int32_t* seq_lens, int32_t dt, int32_t batch,
+                              int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, int32_t block_size,
+                              int32_t max_blocks_per_seq, float scale, void* stream);
+
 /* SwiGLU (reference include/inferop/ops.h:54-55, kernels/silu_mul.cu:16-28, CPU
  * reference/reference.cpp:55-63): out[t, i] = silu(gate_up[t, i]) * gate_up[t, d + i] for
  * gate_up [tokens, 2d] and out [tokens, d] in dt (0 fp32, 1 fp16, 2 bf16), computed in fp32. */

@@ -42,6 +42,8 @@ SIGNATURES = {
     "inferop_rmsnorm": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _i64, C.c_float, _vp]),
     "inferop_fused_add_rmsnorm": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i64, _i64, C.c_float, _vp]),
     "inferop_rope_neox": (C.c_int, [_vp, _vp, _i32, _i64, _i32, _i32, _i32, C.c_float, C.c_float, _vp]),
+    "inferop_paged_attn_decode": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+                                            C.c_float, _vp]),
     "inferop_silu_and_mul": (C.c_int, [_vp, _vp, _i32, _i64, _i64, _vp]),
     "inferop_silu_and_mul_quant": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _i64, _i32, _vp]),
     "inferop_moe_max_mtiles": (_i64, [_i64, _i32, _i32]),

@@ -17,7 +17,7 @@ CSRC = os.path.join(_PKG, "csrc")
 LIB_DIR = os.path.join(_PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libinferop_b200.so")
 
-SOURCES = ["api.cu", "tensormap.cu", "quant.cu", "gemm_sm100.cu", "gemm_pair_sm100.cu", "gemm_decode_sm100.cu", "moe.cu", "reduce.cu", "norm_rope.cu"]
+SOURCES = ["api.cu", "tensormap.cu", "quant.cu", "gemm_sm100.cu", "gemm_pair_sm100.cu", "gemm_decode_sm100.cu", "moe.cu", "reduce.cu", "norm_rope.cu", "attention.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

@@ -541,6 +541,36 @@ int inferop_rope_neox(void* qkv, const int64_t* positions, int32_t dt, int64_t t
                           static_cast<cudaStream_t>(stream));
 }
 
+int inferop_paged_attn_decode(void* out, const void* q, const void* k_cache, const void* v_cache,
+                              const int32_t* block_tables, const int32_t* seq_lens, int32_t dt, int32_t batch,
+                              int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, int32_t block_size,
+                              int32_t max_blocks_per_seq, float scale, void* stream) {
+  if (batch <= 0 || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || block_size <= 0 ||
+      max_blocks_per_seq <= 0 || (head_dim != 64 && head_dim != 128 && head_dim != 256)) {
+    return INFEROP_ERR_SHAPE;
+  }
+  if (dt < 0 || dt > 2) return INFEROP_ERR_DTYPE;
+  if (batch > 65535 || static_cast<int64_t>(max_blocks_per_seq) * block_size > 0x7FFFFF00LL) return INFEROP_ERR_LIMIT;
+  if (!out || !q || !k_cache || !v_cache || !block_tables || !seq_lens) return INFEROP_ERR_POINTER;
+  if ((reinterpret_cast<uintptr_t>(k_cache) & 15u) || (reinterpret_cast<uintptr_t>(v_cache) & 15u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int splits = paged_attn_splits(ctx->sm_count, batch, num_heads, num_kv_heads, block_size, max_blocks_per_seq);
+  void *ws = nullptr, *unused = nullptr;
+  if (splits > 1) {
+    // partial states of the token ranges: scratch of this stream, grown on demand (a cudaMalloc when a
+    // call needs more than any before it on the stream)
+    const int rc = quant_scratch(ctx, s, paged_attn_workspace_bytes(splits, batch, num_heads, head_dim), 16, &ws, &unused);
+    if (rc != INFEROP_OK) return rc;
+  }
+  return launch_paged_attn_decode(out, q, k_cache, v_cache, block_tables, seq_lens, dt, batch, num_heads, num_kv_heads,
+                                  head_dim, block_size, max_blocks_per_seq, scale, splits, static_cast<float*>(ws), s);
+}
+
 int inferop_silu_and_mul(void* out, const void* gate_up, int32_t dt, int64_t tokens, int64_t d,
                          void* stream) {
   if (tokens <= 0 || d <= 0) return INFEROP_ERR_SHAPE;
@@ -852,6 +882,15 @@ void rope_neox(void* qkv, const int64_t* positions, dtype dt, int64_t tokens, in
                int rotary_dim, float base, float yarn_factor, void* stream) {
   report("rope_neox", inferop_rope_neox(qkv, positions, static_cast<int32_t>(dt), tokens, heads, head_dim,
                                         rotary_dim, base, yarn_factor, stream));
+}
+
+void paged_attn_decode(void* out, const void* q, const void* k_cache, const void* v_cache,
+                       const int32_t* block_tables, const int32_t* seq_lens, dtype dt, int batch, int num_heads,
+                       int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq, float scale,
+                       void* stream) {
+  report("paged_attn_decode",
+         inferop_paged_attn_decode(out, q, k_cache, v_cache, block_tables, seq_lens, static_cast<int32_t>(dt), batch,
+                                   num_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq, scale, stream));
 }
 
 void silu_and_mul(void* out, const void* gate_up, dtype dt, int64_t tokens, int64_t d, void* stream) {

@@ -136,6 +136,14 @@ int launch_rmsnorm(void* out, void* residual, const void* in, const void* weight
                    int64_t cols, float eps, cudaStream_t stream);
 int launch_rope_neox(void* qkv, const int64_t* positions, int32_t dt, int64_t tokens, int heads, int head_dim,
                      int rotary_dim, float base, float yarn, cudaStream_t stream);
+// attention.cu : paged attention decode.  `splits` token ranges per sequence (paged_attn_splits),
+// `workspace` of paged_attn_workspace_bytes for the partial states when splits > 1.
+int paged_attn_splits(int sm_count, int batch, int num_heads, int num_kv_heads, int block_size, int max_blocks_per_seq);
+size_t paged_attn_workspace_bytes(int splits, int batch, int num_heads, int head_dim);
+int launch_paged_attn_decode(void* out, const void* q, const void* k_cache, const void* v_cache,
+                             const int32_t* block_tables, const int32_t* seq_lens, int32_t dt, int batch,
+                             int num_heads, int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
+                             float scale, int splits, float* workspace, cudaStream_t stream);
 int launch_silu_and_mul(void* out, const void* gate_up, int32_t dt, int64_t rows, int64_t d,
                         cudaStream_t stream, int sms);
 int launch_silu_and_mul_quant(void* q, void* scales, const void* gate_up, int32_t dt, int64_t rows,

@@ -352,6 +352,31 @@ def rope_neox(qkv: torch.Tensor, positions: torch.Tensor, rotary_dim: int, base:
     return qkv
 
 
+def paged_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                      seq_lens: torch.Tensor, scale: float, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """q [batch, heads, dim]; k_cache / v_cache [blocks, block_size, kv_heads, dim] (q's dtype); block_tables
+    int32 [batch, max_blocks]; seq_lens int32 [batch] -> [batch, heads, dim]."""
+    for t, name in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache"), (block_tables, "block_tables"),
+                    (seq_lens, "seq_lens")):
+        _dev_tensor(t, name)
+    if q.dim() != 3 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape or q.dtype not in _TORCH2CODE or \
+            k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or k_cache.shape[3] != q.shape[2]:
+        raise ValueError("q must be [batch, heads, dim] and the caches [blocks, block_size, kv_heads, dim] of one dtype")
+    if block_tables.dtype != torch.int32 or seq_lens.dtype != torch.int32 or block_tables.dim() != 2 or \
+            block_tables.shape[0] != q.shape[0] or seq_lens.numel() != q.shape[0]:
+        raise ValueError("block_tables must be int32 [batch, max_blocks] and seq_lens int32 [batch]")
+    batch, heads, dim = q.shape
+    _, block_size, kv_heads, _ = k_cache.shape
+    with torch.cuda.device(q.device):
+        if out is None:
+            out = torch.empty_like(q)
+        check(lib.inferop_paged_attn_decode(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                            block_tables.data_ptr(), seq_lens.data_ptr(), int(_TORCH2CODE[q.dtype]),
+                                            batch, heads, kv_heads, dim, block_size, block_tables.shape[1],
+                                            float(scale), _stream_ptr(stream)), "paged_attn_decode")
+    return out
+
+
 def silu_and_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, d + i] (reference include/inferop/ops.h:54-55)."""
     _dev_tensor(gate_up, "gate_up")

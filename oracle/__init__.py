@@ -227,6 +227,27 @@ def rope_neox(qkv, positions, rotary_dim: int, base: float = 10000.0, yarn_facto
     return q
 
 
+def _attn_call(fn, q, k_cache, v_cache, block_tables, seq_lens, scale):
+    q, k_cache, v_cache = _f32(q), _f32(k_cache), _f32(v_cache)
+    bt = np.ascontiguousarray(block_tables, dtype=np.int32)
+    sl = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    batch, heads, dim = q.shape
+    _, block_size, kv_heads, _ = k_cache.shape
+    out = np.empty_like(q)
+    rc = fn(_ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(bt), _ptr(sl), _int(batch), _int(heads),
+            _int(kv_heads), _int(dim), _int(block_size), _int(bt.shape[1]), C.c_float(scale))
+    return out, rc
+
+
+def paged_attn_decode(q, k_cache, v_cache, block_tables, seq_lens, scale: float):
+    """q fp32 [batch, heads, dim], caches fp32 [blocks, block_size, kv_heads, dim], block_tables int32
+    [batch, max_blocks], seq_lens int32 [batch] -> fp32 [batch, heads, dim] (reference/reference.cpp:112-150)."""
+    out, rc = _attn_call(_lib.orc_paged_attn_decode, q, k_cache, v_cache, block_tables, seq_lens, scale)
+    if rc != 0:
+        raise ValueError("bad shape")
+    return out
+
+
 def moe_align(topk_ids, experts: int, tile_rows: int = 128):
     """Expert-sorted layout of a routing: the checker of the device kernel that has no reference
     counterpart (the reference loops over experts on the host).  Pairs (token, k) are sorted by
@@ -359,6 +380,10 @@ class _Reference:
         self.lib.ref_rope_neox(_ptr(q), _ptr(pos), _i64(t), _int(h), _int(d), _int(rotary_dim), C.c_float(base),
                                C.c_float(yarn_factor))
         return q
+
+    def paged_attn_decode(self, q, k_cache, v_cache, block_tables, seq_lens, scale):
+        self.lib.ref_paged_attn_decode.restype = None
+        return _attn_call(self.lib.ref_paged_attn_decode, q, k_cache, v_cache, block_tables, seq_lens, scale)[0]
 
     def silu_and_mul(self, gate_up):
         gate_up = _f32(gate_up)

@@ -332,3 +332,61 @@ int orc_rope_neox(float* qkv, const int64_t* positions, int64_t tokens, int head
   }
   return 0;
 }
+
+/* ---- paged attention, single-token decode, GQA (reference/reference.cpp:112-150) --------------
+ * q / out [batch, heads, head_dim]; k_cache / v_cache [blocks, block_size, kv_heads, head_dim];
+ * block_tables int32 [batch, max_blocks_per_seq]; seq_lens int32 [batch].  Per (sequence, head):
+ * scores = (q . k) * scale with the dot product accumulated left to right in fp32, m = max score,
+ * p = expf(score - m), l = sum p, out = (sum p * v) / l (0 for an empty sequence). */
+int orc_paged_attn_decode(float* out, const float* q, const float* k_cache, const float* v_cache,
+                          const int32_t* block_tables, const int32_t* seq_lens, int batch, int num_heads,
+                          int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq, float scale) {
+  if (batch < 0 || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || head_dim <= 0 ||
+      block_size <= 0)
+    return -1;
+  for (int b = 0; b < batch; ++b) {
+    const int len = seq_lens[b];
+    const int32_t* bt = block_tables + (int64_t)b * max_blocks_per_seq;
+    float* scores = (float*)malloc(sizeof(float) * (size_t)(len > 0 ? len : 1));
+    float* acc = (float*)malloc(sizeof(float) * (size_t)head_dim);
+    if (!scores || !acc) {
+      free(scores);
+      free(acc);
+      return -2;
+    }
+    for (int h = 0; h < num_heads; ++h) {
+      const int kvh = h / (num_heads / num_kv_heads);
+      const float* qv = q + ((int64_t)b * num_heads + h) * head_dim;
+      float m = -INFINITY;
+      for (int key = 0; key < len; ++key) {
+        const int blk = bt[key / block_size], off = key % block_size;
+        const float* krow = k_cache + (((int64_t)blk * block_size + off) * num_kv_heads + kvh) * head_dim;
+        volatile float dot = 0.0f;
+        for (int d = 0; d < head_dim; ++d) {
+          volatile float pr = qv[d] * krow[d];
+          dot = dot + pr;
+        }
+        scores[key] = dot * scale;
+        if (scores[key] > m) m = scores[key];
+      }
+      for (int d = 0; d < head_dim; ++d) acc[d] = 0.0f;
+      volatile float l = 0.0f;
+      for (int key = 0; key < len; ++key) {
+        const float p = expf(scores[key] - m);
+        l = l + p;
+        const int blk = bt[key / block_size], off = key % block_size;
+        const float* vrow = v_cache + (((int64_t)blk * block_size + off) * num_kv_heads + kvh) * head_dim;
+        for (int d = 0; d < head_dim; ++d) {
+          volatile float pr = p * vrow[d];
+          acc[d] = acc[d] + pr;
+        }
+      }
+      float* o = out + ((int64_t)b * num_heads + h) * head_dim;
+      const float inv = (l == 0.0f) ? 0.0f : 1.0f / l;
+      for (int d = 0; d < head_dim; ++d) o[d] = acc[d] * inv;
+    }
+    free(scores);
+    free(acc);
+  }
+  return 0;
+}

@@ -58,6 +58,12 @@ void ref_rope_neox(float* qkv, const int64_t* positions, int64_t tokens, int hea
                    float base, float yarn_factor) {
   r::rope_neox(qkv, positions, tokens, heads, head_dim, rotary_dim, base, yarn_factor);
 }
+void ref_paged_attn_decode(float* out, const float* q, const float* k_cache, const float* v_cache,
+                           const int32_t* block_tables, const int32_t* seq_lens, int batch, int num_heads,
+                           int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq, float scale) {
+  r::paged_attn_decode(out, q, k_cache, v_cache, block_tables, seq_lens, batch, num_heads, num_kv_heads, head_dim,
+                       block_size, max_blocks_per_seq, scale);
+}
 void ref_silu_and_mul(float* out, const float* gate_up, int64_t tokens, int64_t d) {
   r::silu_and_mul(out, gate_up, tokens, d);
 }

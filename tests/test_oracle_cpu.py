@@ -322,3 +322,46 @@ def test_rmsnorm_and_rope_golden_vectors():
     assert np.array_equal(oracle.rope_neox(g["q"], g["pos"], 64).view(np.uint32), g["rope"].view(np.uint32))
     assert np.array_equal(oracle.rope_neox(g["q2"], g["pos2"], 64, 500000.0, 0.25).view(np.uint32),
                           g["rope2"].view(np.uint32))
+
+
+# ------------------------------------------------------------------ paged attention decode
+def attn_case(batch, heads, kv_heads, dim, block_size, lens, seed=0, shuffle=False):
+    """The paged cache of the reference's test (tests/test_paged_attn.cpp:16-40): a shared first block,
+    then disjoint blocks per sequence; `shuffle` permutes the physical blocks."""
+    rng = np.random.default_rng(seed)
+    per_seq = max((l + block_size - 1) // block_size for l in lens)
+    blocks = 1 + batch * per_seq
+    k = rng.standard_normal((blocks, block_size, kv_heads, dim)).astype(np.float32)
+    v = rng.standard_normal((blocks, block_size, kv_heads, dim)).astype(np.float32)
+    q = rng.standard_normal((batch, heads, dim)).astype(np.float32)
+    tables = np.zeros((batch, per_seq), np.int32)
+    for b in range(batch):
+        for j in range(1, per_seq):
+            tables[b, j] = 1 + b * per_seq + (j - 1)
+    if shuffle:
+        perm = rng.permutation(blocks).astype(np.int32)
+        inv = np.argsort(perm)
+        k, v = k[inv], v[inv]          # logical block i now lives at physical block perm[i]
+        tables = perm[tables]
+    return q, k, v, tables, np.array(lens, np.int32)
+
+
+def test_paged_attention_properties_of_the_reference_test():
+    """tests/test_paged_attn.cpp:42-76: outputs inside the range of V, a length-1 sequence returns its V row."""
+    q, k, v, tables, lens = attn_case(3, 32, 8, 128, 16, [1, 17, 129])
+    out = oracle.paged_attn_decode(q, k, v, tables, lens, 1.0 / np.sqrt(128.0))
+    assert out.min() >= v.min() - 1e-3 and out.max() <= v.max() + 1e-3
+    np.testing.assert_allclose(out[0, 0], v[tables[0, 0], 0, 0], atol=1e-4)
+    empty = oracle.paged_attn_decode(q, k, v, tables, np.array([0, 17, 129], np.int32), 0.1)
+    assert np.array_equal(empty[0], np.zeros_like(empty[0]))
+
+
+@pytest.mark.skipif(not oracle.have_reference(), reason="reference tree not built here")
+def test_paged_attention_restatement_equals_the_reference_bit_for_bit():
+    R = oracle.reference
+    for (b, h, kvh, d, bs, lens, shuf) in ((3, 32, 8, 128, 16, [1, 17, 129], False), (2, 16, 4, 64, 16, [5, 64], True),
+                                           (2, 8, 8, 256, 16, [33, 200], True), (1, 4, 1, 128, 8, [77], True)):
+        q, k, v, tables, sl = attn_case(b, h, kvh, d, bs, lens, seed=b + d, shuffle=shuf)
+        scale = float(1.0 / np.sqrt(d))
+        assert np.array_equal(oracle.paged_attn_decode(q, k, v, tables, sl, scale).view(np.uint32),
+                              R.paged_attn_decode(q, k, v, tables, sl, scale).view(np.uint32))
