@@ -391,7 +391,57 @@ def block_ops(peaks, rows=16384, cols=7168, heads=32, head_dim=128, rotary=64):
                         "shape": [rows, heads, head_dim], "rotary_dim": rotary}
     rec["shape"] = [rows, cols]
     rec["dtype"] = "bf16"
+    rec["paged_attn_decode"] = attention_bench(peaks)
     return rec
+
+
+def attention_bench(peaks):
+    """Paged attention decode, bf16, 32 query heads over 8 KV heads of 128: a batch of 64 sequences of 4096
+    tokens and one sequence of 65536 tokens; bytes = the K and V rows of the sequences (read once)."""
+    import numpy as np
+    import torch
+    import oracle
+    from inference_b200 import ops
+    heads, kvh, dim, bs = 32, 8, 128, 16
+    out = []
+    for batch, length in ((64, 4096), (1, 65536), (8, 1024)):
+        per_seq = length // bs
+        blocks = batch * per_seq
+        g = torch.Generator(device="cuda")
+        g.manual_seed(batch)
+        k = torch.randn((blocks, bs, kvh, dim), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        v = torch.randn((blocks, bs, kvh, dim), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        q = torch.randn((batch, heads, dim), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        tables = torch.randperm(blocks, generator=g, device="cuda").to(torch.int32).view(batch, per_seq)
+        lens = torch.full((batch,), length, dtype=torch.int32, device="cuda")
+        o = torch.empty_like(q)
+        scale = float(1.0 / np.sqrt(dim))
+        for _ in range(2):
+            ops.paged_attn_decode(q, k, v, tables, lens, scale, out=o)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = 10
+        e0.record()
+        for _ in range(iters):
+            ops.paged_attn_decode(q, k, v, tables, lens, scale, out=o)
+        e1.record()
+        torch.cuda.synchronize()
+        t = e0.elapsed_time(e1) * 1e-3 / iters
+        # parity of one sequence against the oracle (its blocks only)
+        b0 = batch - 1
+        tb = tables[b0].long()
+        want = oracle.paged_attn_decode(q[b0:b0 + 1].float().cpu().numpy(), k[tb].float().cpu().numpy(),
+                                        v[tb].float().cpu().numpy(), np.arange(per_seq, dtype=np.int32)[None, :],
+                                        np.array([length], np.int32), scale)
+        err = float(np.abs(o[b0:b0 + 1].float().cpu().numpy() - want).max())
+        assert err <= 2e-2, f"paged attention off by {err}"
+        byt = 2 * batch * length * kvh * dim * 2
+        out.append({"batch": batch, "seq_len": length, "heads": heads, "kv_heads": kvh, "head_dim": dim,
+                    "us": round(t * 1e6, 1), "gbs": round(byt / t / 1e9, 1),
+                    "frac_of_measured_hbm": round(byt / t / 1e9 / peaks["hbm_gbs"], 3), "max_abs_err": err})
+        del k, v
+        torch.cuda.empty_cache()
+    return out
 
 
 def shape_sweep(peaks):

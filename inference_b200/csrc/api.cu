@@ -797,6 +797,10 @@ int inferop_set_option(const char* key, int64_t value) {
     o.pdl_trigger = value != 0;
   } else if (!strcmp(key, "fused_prologue")) {
     o.fused_prologue = value != 0;
+  } else if (!strcmp(key, "attn_heads_per_cta")) {
+    o.attn_heads_per_cta = static_cast<int>(value);
+  } else if (!strcmp(key, "attn_splits")) {
+    o.attn_splits = static_cast<int>(value);
   } else if (!strcmp(key, "quant_pdl")) {
     o.quant_pdl = value != 0;
   } else if (!strcmp(key, "gemm_pdl")) {

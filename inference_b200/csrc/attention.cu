@@ -29,7 +29,8 @@ namespace ib200 {
 namespace {
 
 constexpr int kThreads = 128;
-constexpr int kBatch = 4;   // tokens of a stream in flight per step
+constexpr int kBatch = 4;   // tokens of a stream per step
+constexpr int kDepth = 3;   // steps in flight (shared-memory ring)
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
@@ -47,6 +48,43 @@ template <>
 __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+
+// 2^x for x <= 0 by the special-function unit alone (results below the normal range flush to 0)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// the elements of one 16-byte vector as floats (16-bit types: pure bit operations / packed converts)
+template <typename T>
+__device__ __forceinline__ void unpack_vec(const uint4& raw, float* f);
+template <>
+__device__ __forceinline__ void unpack_vec<float>(const uint4& raw, float* f) {
+  f[0] = __uint_as_float(raw.x);
+  f[1] = __uint_as_float(raw.y);
+  f[2] = __uint_as_float(raw.z);
+  f[3] = __uint_as_float(raw.w);
+}
+template <>
+__device__ __forceinline__ void unpack_vec<__nv_bfloat16>(const uint4& raw, float* f) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void unpack_vec<__half>(const uint4& raw, float* f) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
 
 template <typename T, int D>
 struct ACfg {
@@ -67,7 +105,7 @@ struct AttnParams {
   const int32_t* block_tables;
   const int32_t* seq_lens;
   float* partial;   // [batch][heads][splits][D + 2]: accumulator, running maximum (base 2), denominator
-  int num_heads, num_kv_heads, block_size, max_blocks_per_seq, splits;
+  int num_heads, num_kv_heads, block_size, block_shift, max_blocks_per_seq, splits;   // block_shift: log2(block_size) or -1
   float scale_log2e;
 };
 
@@ -78,7 +116,7 @@ __device__ __forceinline__ int elem_index(int sub, int e) {
 }
 
 template <typename T, int D, int GT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 paged_attn_kernel(const AttnParams p) {
   using C = ACfg<T, D>;
   extern __shared__ float sm[];   // [NS][GT][D + 2] at the end: the streams' states
@@ -120,81 +158,155 @@ paged_attn_kernel(const AttnParams p) {
 
   const T* kc = static_cast<const T*>(p.k_cache);
   const T* vc = static_cast<const T*>(p.v_cache);
+  // K and V rows travel through a ring in shared memory by cp.async, kDepth steps ahead of the
+  // arithmetic: every lane copies the 16-byte pieces it will itself consume, so the only
+  // synchronisation is the lane's own wait for its copy groups, and the bytes in flight are not
+  // limited by registers.  Layout: [step % kDepth][token of the step][K, V][vector][thread].
+  constexpr int kSlotVecs = kBatch * 2 * C::VPL;           // 16-byte pieces per thread and step
+  uint4* ring = reinterpret_cast<uint4*>(sm);              // the streams' final states reuse this memory
+  auto issue = [&](int step_tb0, int slot) {
+#pragma unroll
+    for (int c = 0; c < kBatch; ++c) {
+      const int t = step_tb0 + stream + c * C::NS;
+      if (t < t1) {
+        // (a power-of-two block size, the usual case, needs no division)
+        const int bi = p.block_shift >= 0 ? t >> p.block_shift : t / p.block_size;
+        const int off = p.block_shift >= 0 ? t & (p.block_size - 1) : t - bi * p.block_size;
+        const int blk = __ldg(bt + bi);
+        const int64_t row = ((static_cast<int64_t>(blk) * p.block_size + off) * p.num_kv_heads + kvh) * D;
+#pragma unroll
+        for (int v = 0; v < C::VPL; ++v) {
+          uint4* dk = ring + (static_cast<size_t>(slot) * kSlotVecs + (c * 2 + 0) * C::VPL + v) * kThreads + threadIdx.x;
+          uint4* dv = ring + (static_cast<size_t>(slot) * kSlotVecs + (c * 2 + 1) * C::VPL + v) * kThreads + threadIdx.x;
+          const uint4* sk = reinterpret_cast<const uint4*>(kc + row) + v * C::LPT + sub;
+          const uint4* sv = reinterpret_cast<const uint4*>(vc + row) + v * C::LPT + sub;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dk)), "l"(sk) : "memory");
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dv)), "l"(sv) : "memory");
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // one group per step, empty or not
+  };
+  constexpr int kStep = C::NS * kBatch;                    // tokens of the CTA per step
+#pragma unroll
+  for (int j = 0; j < kDepth - 1; ++j) issue(t0 + j * kStep, j);
+
   // the trip count is the same for every lane of the CTA (the shuffles below need whole warps);
   // a stream whose tokens of a step all lie beyond the range skips the update
-  for (int tb0 = t0; tb0 < t1; tb0 += C::NS * kBatch) {
+  int slot = 0;
+  for (int tb0 = t0; tb0 < t1; tb0 += kStep) {
     const int tb = tb0 + stream;
-    // ---- request the K and V rows of up to kBatch tokens of this stream
+    {
+      int ahead = slot + kDepth - 1;
+      if (ahead >= kDepth) ahead -= kDepth;
+      issue(tb0 + (kDepth - 1) * kStep, ahead);
+    }
+    asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory");
     uint4 kr[kBatch][C::VPL], vr[kBatch][C::VPL];
     bool valid[kBatch];
 #pragma unroll
     for (int c = 0; c < kBatch; ++c) {
-      const int t = tb + c * C::NS;
-      valid[c] = t < t1;
-      if (valid[c]) {
-        const int blk = __ldg(bt + t / p.block_size);
-        const int64_t row = ((static_cast<int64_t>(blk) * p.block_size + t % p.block_size) * p.num_kv_heads + kvh) * D;
-#pragma unroll
-        for (int v = 0; v < C::VPL; ++v) {
-          kr[c][v] = __ldg(reinterpret_cast<const uint4*>(kc + row) + v * C::LPT + sub);
-          vr[c][v] = __ldg(reinterpret_cast<const uint4*>(vc + row) + v * C::LPT + sub);
-        }
-      }
-    }
-    // ---- scores of the batch for every head of the group (all lanes of a token end up with the sum)
-    float s2[GT][kBatch];
-#pragma unroll
-    for (int c = 0; c < kBatch; ++c) {
-      float kf[C::EPL];
+      valid[c] = tb + c * C::NS < t1;
 #pragma unroll
       for (int v = 0; v < C::VPL; ++v) {
-        const T* e8 = reinterpret_cast<const T*>(&kr[c][v]);
-#pragma unroll
-        for (int i = 0; i < C::EV; ++i) kf[v * C::EV + i] = valid[c] ? to_f32<T>(e8[i]) : 0.0f;
+        kr[c][v] = ring[(static_cast<size_t>(slot) * kSlotVecs + (c * 2 + 0) * C::VPL + v) * kThreads + threadIdx.x];
+        vr[c][v] = ring[(static_cast<size_t>(slot) * kSlotVecs + (c * 2 + 1) * C::VPL + v) * kThreads + threadIdx.x];
       }
+    }
+    if (++slot == kDepth) slot = 0;
+    // ---- scores of the batch for every head of the group: this lane's partial dot products ...
+    constexpr int NV = GT * kBatch;   // values to be summed over the LPT lanes of the token group
+    float val[NV];
+#pragma unroll
+    for (int c = 0; c < kBatch; ++c) {
+      // (the slot of a token beyond the range holds stale bytes: its scores are masked below)
+      float kf[C::EPL];
+#pragma unroll
+      for (int v = 0; v < C::VPL; ++v) unpack_vec<T>(kr[c][v], kf + v * C::EV);
 #pragma unroll
       for (int g = 0; g < GT; ++g) {
         float part = 0.0f;
 #pragma unroll
         for (int e = 0; e < C::EPL; ++e) part = fmaf(qf[g][e], kf[e], part);
+        val[g * kBatch + c] = part;
+      }
+    }
+    // ... summed by a reduce-scatter butterfly (every step halves the values a lane carries:
+    // NV - 1 shuffles instead of NV log2(LPT); the warp shuffle unit is the scarce resource here)
+    // and handed back to all lanes of the group from their owners
+    {
+      int cnt = NV;
 #pragma unroll
-        for (int o = C::LPT / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
-        s2[g][c] = valid[c] ? part : -INFINITY;
+      for (int o = C::LPT / 2; o > 0; o >>= 1) {
+        if (cnt > 1) {
+          const bool upper = (sub & o) != 0;
+          cnt >>= 1;
+#pragma unroll
+          for (int i = 0; i < NV / 2; ++i) {
+            if (i < cnt) {
+              const float keep = upper ? val[i + cnt] : val[i];
+              const float send = upper ? val[i] : val[i + cnt];
+              val[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, o);
+            }
+          }
+        } else {
+          val[0] += __shfl_xor_sync(0xFFFFFFFFu, val[0], o);
+        }
+      }
+    }
+    float s2[GT][kBatch];
+    {
+      constexpr int CF = NV >= C::LPT ? NV / C::LPT : 1;      // totals a lane owns after the butterfly
+      constexpr int LF = NV >= C::LPT ? 1 : C::LPT / NV;      // lanes that hold the same total
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const float tot = __shfl_sync(0xFFFFFFFFu, val[v % CF], (v / CF) * LF, C::LPT);
+        s2[v / kBatch][v % kBatch] = valid[v % kBatch] ? tot : -INFINITY;
       }
     }
     // ---- online softmax update (with valid[0] the maxima are finite)
     if (!valid[0]) continue;
+    float pr[GT][kBatch];
 #pragma unroll
     for (int g = 0; g < GT; ++g) {
       float m_new = m[g];
 #pragma unroll
       for (int c = 0; c < kBatch; ++c) m_new = fmaxf(m_new, s2[g][c]);
-      const float alpha = exp2f(m[g] - m_new);   // 0 for the first batch (m = -inf)
-      float pr[kBatch], ps = 0.0f;
+      if (m_new > m[g]) {
+        // a new maximum (always so in a stream's first step, where m = -inf and alpha = 0; rare
+        // later in a long sequence): the state is rescaled
+        const float alpha = ex2(m[g] - m_new);
+        l[g] *= alpha;
 #pragma unroll
-      for (int c = 0; c < kBatch; ++c) {
-        pr[c] = exp2f(s2[g][c] - m_new);         // 0 for a missing token
-        ps += pr[c];
+        for (int e = 0; e < C::EPL; ++e) acc[g][e] *= alpha;
+        m[g] = m_new;
       }
-      l[g] = fmaf(l[g], alpha, ps);
-      m[g] = m_new;
-#pragma unroll
-      for (int e = 0; e < C::EPL; ++e) acc[g][e] *= alpha;
+      float ps = 0.0f;
 #pragma unroll
       for (int c = 0; c < kBatch; ++c) {
-        if (valid[c]) {
+        pr[g][c] = ex2(s2[g][c] - m_new);        // 0 for a missing token
+        ps += pr[g][c];
+      }
+      l[g] += ps;
+    }
 #pragma unroll
-          for (int v = 0; v < C::VPL; ++v) {
-            const T* e8 = reinterpret_cast<const T*>(&vr[c][v]);
+    for (int c = 0; c < kBatch; ++c) {
+      if (valid[c]) {
+        float vf[C::EPL];
 #pragma unroll
-            for (int i = 0; i < C::EV; ++i) acc[g][v * C::EV + i] = fmaf(pr[c], to_f32<T>(e8[i]), acc[g][v * C::EV + i]);
-          }
+        for (int v = 0; v < C::VPL; ++v) unpack_vec<T>(vr[c][v], vf + v * C::EV);
+#pragma unroll
+        for (int g = 0; g < GT; ++g) {
+#pragma unroll
+          for (int e = 0; e < C::EPL; ++e) acc[g][e] = fmaf(pr[g][c], vf[e], acc[g][e]);
         }
       }
     }
   }
 
-  // ---- merge the CTA's streams: every stream leaves its state in shared memory
+  // ---- merge the CTA's streams: every stream leaves its state in shared memory (the ring's)
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
   constexpr int kRec = D + 2;
   float* mine = sm + (static_cast<size_t>(stream) * GT) * kRec;
 #pragma unroll
@@ -255,7 +367,9 @@ paged_attn_merge_kernel(const AttnParams p) {
 template <typename T, int D, int GT>
 int launch_attn_gt(const AttnParams& p, int batch, cudaStream_t stream) {
   using C = ACfg<T, D>;
-  const size_t smem = static_cast<size_t>(C::NS) * GT * (D + 2) * sizeof(float);
+  const size_t states = static_cast<size_t>(C::NS) * GT * (D + 2) * sizeof(float);
+  const size_t ring = static_cast<size_t>(kDepth) * kBatch * 2 * C::VPL * kThreads * 16;
+  const size_t smem = states > ring ? states : ring;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -274,12 +388,19 @@ int launch_attn_gt(const AttnParams& p, int batch, cudaStream_t stream) {
   return check_launch();
 }
 
+int heads_per_cta(int group) {
+  const int forced = options().attn_heads_per_cta;
+  if ((forced == 1 || forced == 2 || forced == 4) && group % forced == 0) return forced;
+  return group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+}
+
 template <typename T, int D>
 int launch_attn_d(const AttnParams& p, int batch, cudaStream_t stream) {
-  const int g = p.num_heads / p.num_kv_heads;
-  if (g % 4 == 0) return launch_attn_gt<T, D, 4>(p, batch, stream);
-  if (g % 2 == 0) return launch_attn_gt<T, D, 2>(p, batch, stream);
-  return launch_attn_gt<T, D, 1>(p, batch, stream);
+  switch (heads_per_cta(p.num_heads / p.num_kv_heads)) {
+    case 4: return launch_attn_gt<T, D, 4>(p, batch, stream);
+    case 2: return launch_attn_gt<T, D, 2>(p, batch, stream);
+    default: return launch_attn_gt<T, D, 1>(p, batch, stream);
+  }
 }
 
 template <typename T>
@@ -296,12 +417,13 @@ int launch_attn_t(const AttnParams& p, int batch, int head_dim, cudaStream_t str
 
 int paged_attn_splits(int sm_count, int batch, int num_heads, int num_kv_heads, int block_size, int max_blocks_per_seq) {
   const int g = num_heads / num_kv_heads;
-  const int gt = g % 4 == 0 ? 4 : (g % 2 == 0 ? 2 : 1);
+  const int gt = heads_per_cta(g);
   const int64_t base = static_cast<int64_t>(batch) * num_kv_heads * (g / gt);
-  int64_t splits = (4LL * sm_count + base - 1) / base;                       // about four CTAs per SM
+  if (options().attn_splits > 0) return options().attn_splits > 128 ? 128 : options().attn_splits;
+  int64_t splits = (4LL * sm_count + base - 1) / base;                       // about four CTAs per SM, as many as are resident
   const int64_t by_len = (static_cast<int64_t>(max_blocks_per_seq) * block_size + 255) / 256;   // 256 tokens per CTA at least
   if (splits > by_len) splits = by_len;
-  if (splits > 64) splits = 64;
+  if (splits > 64) splits = 64;   // (128 ranges of one 65536-token sequence measured 25 % slower than 64)
   if (splits < 1) splits = 1;
   return static_cast<int>(splits);
 }
@@ -325,6 +447,9 @@ int launch_paged_attn_decode(void* out, const void* q, const void* k_cache, cons
   p.num_heads = num_heads;
   p.num_kv_heads = num_kv_heads;
   p.block_size = block_size;
+  p.block_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1 << sh) == block_size) p.block_shift = sh;
   p.max_blocks_per_seq = max_blocks_per_seq;
   p.splits = splits;
   p.scale_log2e = scale * 1.4426950408889634f;

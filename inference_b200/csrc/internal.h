@@ -51,6 +51,8 @@ struct Options {
   int gemm_pair = -1;      // large-tile GEMM on CTA pairs (256 x 256 tiles): -1 auto, 0 never, 1 always
   int pdl_trigger = 1;     // small-M GEMM: a dependent launch (the next step's quantiser) may start under its tail
   int fused_prologue = 0;  // one-call quantise + GEMM, M <= 32: 1 = quantise inside the small-M kernel (one launch; slower than the chained pair except at M = 1)
+  int attn_heads_per_cta = 0;  // paged attention: query heads of a KV head per CTA (0 = auto: 4, 2 or 1)
+  int attn_splits = 0;     // paged attention: token ranges per sequence (0 = auto)
   int quant_pdl = 1;       // quantiser: launch with programmatic stream serialisation
   int gemm_pdl = 1;        // pair kernel: launch with programmatic stream serialisation
   int debug_no_loads = 0;  // test hook: the TMA producers of the GEMM kernels issue no load (every wait runs out)

@@ -49,6 +49,9 @@ def test_argument_validation_needs_no_gpu():
     assert lib.inferop_fused_add_rmsnorm(1, None, 1, 1, 2, 4, 128, 1e-6, None) == _capi.ERR_POINTER
     assert lib.inferop_rope_neox(1, 1, 2, 4, 8, 128, 130, 10000.0, 1.0, None) == _capi.ERR_SHAPE
     assert lib.inferop_rope_neox(1, 1, 2, 4, 8, 128, 63, 10000.0, 1.0, None) == _capi.ERR_SHAPE
+    assert lib.inferop_paged_attn_decode(16, 16, 16, 16, 16, 16, 2, 1, 8, 3, 128, 16, 4, 0.1, None) == _capi.ERR_SHAPE
+    assert lib.inferop_paged_attn_decode(16, 16, 16, 16, 16, 16, 2, 1, 8, 4, 100, 16, 4, 0.1, None) == _capi.ERR_SHAPE
+    assert lib.inferop_paged_attn_decode(16, 16, 24, 16, 16, 16, 2, 1, 8, 4, 128, 16, 4, 0.1, None) == _capi.ERR_POINTER
     assert lib.inferop_w8a8_block_fp8_gemm(1, 1, 1, 1, 1, 4, 4, 100, 128, 128, 2, None) == _capi.ERR_SHAPE
     assert lib.inferop_w8a8_block_fp8_gemm(1, 1, 1, 1, 1, 4, 4, 128, 64, 128, 2, None) == _capi.ERR_SHAPE
     assert lib.inferop_w8a8_block_fp8_gemm(1, 1, 1, 1, 1, 0, 4, 128, 128, 128, 2, None) == _capi.ERR_SHAPE

@@ -29,7 +29,7 @@ def _build(name, tmp_path):
 
 
 @pytest.mark.parametrize("name", ["test_fp8", "test_quant", "test_gemm", "test_topk", "test_silu_mul", "test_rmsnorm",
-                                  "test_rope"])
+                                  "test_rope", "test_paged_attn"])
 def test_reference_test_program_builds_and_its_cpu_half_passes(name, tmp_path):
     import torch
     exe = _build(name, tmp_path)
