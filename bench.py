@@ -378,6 +378,24 @@ def block_ops(peaks, rows=16384, cols=7168, heads=32, head_dim=128, rotary=64):
     byt = 8 * rows * cols
     rec["fused_add_rmsnorm"] = {"us": round(t * 1e6, 1), "gbs": round(byt / t / 1e9, 1),
                                 "frac_of_measured_hbm": round(byt / t / 1e9 / peaks["hbm_gbs"], 3), "max_abs_err": err}
+    # RMSNorm + 1x128 FP8 quantisation in one pass against the two kernels (same bytes and scales)
+    qq = torch.empty((rows, cols), dtype=torch.uint8, device="cuda")
+    qs = torch.empty((rows, cols // 128), dtype=torch.float32, device="cuda")
+    t1 = timed(lambda: ops.rmsnorm_quant(x, w, 1e-6, q=qq, scales=qs))
+    q2 = torch.empty_like(qq)
+    s2 = torch.empty_like(qs)
+
+    def two_calls():
+        ops.rmsnorm(x, w, 1e-6, out=out)
+        ops.quant_fp8_per_token_group(out, 128, q2, s2)
+
+    t2 = timed(two_calls)
+    byt = 3 * rows * cols + 4 * rows * (cols // 128)
+    rec["rmsnorm_quant"] = {"us": round(t1 * 1e6, 1), "gbs": round(byt / t1 / 1e9, 1),
+                            "frac_of_measured_hbm": round(byt / t1 / 1e9 / peaks["hbm_gbs"], 3),
+                            "two_kernels_us": round(t2 * 1e6, 1),
+                            "same_bits": bool(torch.equal(qq, q2) and torch.equal(qs, s2))}
+    assert rec["rmsnorm_quant"]["same_bits"]
     q0 = qkv.clone()
     t = timed(lambda: ops.rope_neox(qkv, pos, rotary))
     q1 = q0.clone()

@@ -220,6 +220,16 @@ INFEROP_API int inferop_rmsnorm(void* out, const void* in, const void* weight, i
 INFEROP_API int inferop_fused_add_rmsnorm(void* residual, void* out, const void* x, const void* weight, int32_t dt,
                               int64_t rows, int64_t cols, float eps, void* stream);
 
+/* RMSNorm (residual == NULL) or residual add + RMSNorm (residual[r, :] += in[r, :] in place) with the
+ * 1 x 128 FP8 quantisation of the result in the same pass: q [rows, cols] E4M3 and scales
+ * [rows, cols / 128] are, bit for bit, what inferop_quant_fp8_per_token_group gives on the output of
+ * inferop_rmsnorm / inferop_fused_add_rmsnorm (reference ops.h:30-37 then :64-65), and the 16-bit matrix
+ * between the two never exists (3 bytes per element instead of 7).  dt 1 fp16 / 2 bf16 (the type of in,
+ * weight, residual and of the intermediate rounding); group_size == 128; cols % 128 == 0, cols <= 16384;
+ * in / weight / residual 16-byte aligned, q 8-byte aligned.  No counterpart in the reference. */
+INFEROP_API int inferop_rmsnorm_quant(void* q, void* scales, void* residual, const void* in, const void* weight,
+                          int32_t dt, int64_t rows, int64_t cols, int32_t group_size, float eps, void* stream);
+
 /* Rotary position embedding, GPT-NeoX layout, in place (reference ops.h:46-48, kernels/rope.cu:19-41,
  * CPU reference.cpp:37-53): qkv [tokens, heads, head_dim] in dt, positions int64 [tokens] (device);
  * for i < rotary_dim / 2: theta = position * base^(-2 i / rotary_dim) * yarn_factor and

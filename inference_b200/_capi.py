@@ -41,6 +41,7 @@ SIGNATURES = {
     "inferop_topk_softmax": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "inferop_rmsnorm": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _i64, C.c_float, _vp]),
     "inferop_fused_add_rmsnorm": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i64, _i64, C.c_float, _vp]),
+    "inferop_rmsnorm_quant": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i32, C.c_float, _vp]),
     "inferop_rope_neox": (C.c_int, [_vp, _vp, _i32, _i64, _i32, _i32, _i32, C.c_float, C.c_float, _vp]),
     "inferop_paged_attn_decode": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
                                             C.c_float, _vp]),

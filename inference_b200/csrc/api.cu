@@ -526,6 +526,21 @@ int inferop_fused_add_rmsnorm(void* residual, void* out, const void* x, const vo
   return launch_rmsnorm(out, residual, x, weight, dt, rows, cols, eps, static_cast<cudaStream_t>(stream));
 }
 
+int inferop_rmsnorm_quant(void* q, void* scales, void* residual, const void* in, const void* weight, int32_t dt,
+                          int64_t rows, int64_t cols, int32_t group_size, float eps, void* stream) {
+  if (rows <= 0 || cols <= 0 || group_size != 128 || cols % 128 != 0 || cols > 16384) return INFEROP_ERR_SHAPE;
+  if (dt != 1 && dt != 2) return INFEROP_ERR_DTYPE;
+  if (!q || !scales || !in || !weight) return INFEROP_ERR_POINTER;
+  if (((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(residual)) & 15u) ||
+      (reinterpret_cast<uintptr_t>(q) & 7u) || (reinterpret_cast<uintptr_t>(scales) & 3u)) {
+    return INFEROP_ERR_POINTER;
+  }
+  int err;
+  DeviceCtx* ctx = current_ctx(&err);
+  if (!ctx) return err;
+  return launch_rmsnorm_quant(q, scales, residual, in, weight, dt, rows, cols, eps, static_cast<cudaStream_t>(stream));
+}
+
 int inferop_rope_neox(void* qkv, const int64_t* positions, int32_t dt, int64_t tokens, int32_t heads,
                       int32_t head_dim, int32_t rotary_dim, float base, float yarn_factor, void* stream) {
   if (tokens <= 0 || heads <= 0 || head_dim <= 0 || rotary_dim <= 0 || rotary_dim > head_dim ||

@@ -136,6 +136,9 @@ int launch_topk_softmax(int32_t* ids, float* weights, const float* logits, int32
 // and the NeoX rotary embedding in place.
 int launch_rmsnorm(void* out, void* residual, const void* in, const void* weight, int32_t dt, int64_t rows,
                    int64_t cols, float eps, cudaStream_t stream);
+// the same followed by the 1 x 128 FP8 quantisation of the (16-bit) result, in one pass
+int launch_rmsnorm_quant(void* q, void* scales, void* residual, const void* in, const void* weight, int32_t dt,
+                         int64_t rows, int64_t cols, float eps, cudaStream_t stream);
 int launch_rope_neox(void* qkv, const int64_t* positions, int32_t dt, int64_t tokens, int heads, int head_dim,
                      int rotary_dim, float base, float yarn, cudaStream_t stream);
 // attention.cu : paged attention decode.  `splits` token ranges per sequence (paged_attn_splits),

@@ -17,6 +17,7 @@
 #include <stdint.h>
 
 #include "internal.h"
+#include "quant_math.cuh"
 
 namespace ib200 {
 namespace {
@@ -132,6 +133,92 @@ rmsnorm_vec_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __res
   }
 }
 
+// RMSNorm (or residual add + RMSNorm) with the 1 x 128 FP8 quantisation of the result in the same
+// pass: q / scales are what quant_fp8_per_token_group gives on the 16-bit output of the norm, bit
+// for bit (the normalised value is rounded to T first, then quantised by the quantiser's own
+// functions), and the 16-bit matrix between the two never exists.  A group of 128 elements is 16
+// consecutive vectors, i.e. the 16 lanes of a half warp.  16-bit T, cols % 128 == 0.
+template <typename T, bool kAdd, int NV>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_quant_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, T* __restrict__ residual,
+                     const T* __restrict__ in, const T* __restrict__ weight, float eps, int64_t rows, int cols,
+                     int tpr) {
+  constexpr int V = 8;
+  using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+  __shared__ float red[kThreads / 32];
+  const int lane_in_row = threadIdx.x & (tpr - 1);
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (kThreads / tpr) + (threadIdx.x / tpr);
+  const bool live = row < rows;
+  const int nvec = cols / V;
+  const uint4* src = reinterpret_cast<const uint4*>(in + (live ? row : 0) * cols);
+  uint4* res = kAdd ? reinterpret_cast<uint4*>(residual + (live ? row : 0) * cols) : nullptr;
+
+  uint4 raw[NV], rraw[kAdd ? NV : 1];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int j = lane_in_row + k * tpr;
+    const bool have = live && j < nvec;
+    raw[k] = have ? __ldg(src + j) : make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (kAdd) rraw[k] = have ? res[j] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float partial = 0.0f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    float v[V];
+    unpack<T>(raw[k], v);
+    if constexpr (kAdd) {
+      float r[V];
+      unpack<T>(rraw[k], r);
+#pragma unroll
+      for (int i = 0; i < V; ++i) r[i] = __fadd_rn(r[i], v[i]);
+#pragma unroll
+      for (int i = 0; i < V; ++i) partial = fmaf(r[i], r[i], partial);
+      raw[k] = pack<T>(r);
+      const int j = lane_in_row + k * tpr;
+      if (live && j < nvec) res[j] = raw[k];
+    } else {
+#pragma unroll
+      for (int i = 0; i < V; ++i) partial = fmaf(v[i], v[i], partial);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) partial += __shfl_xor_sync(0xFFFFFFFFu, partial, o);
+  if (tpr > 32) {
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = partial;
+    __syncthreads();
+    const int w0 = (threadIdx.x / tpr) * (tpr >> 5);
+    partial = 0.0f;
+    for (int w = 0; w < (tpr >> 5); ++w) partial += red[w0 + w];
+  }
+  const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(partial, static_cast<float>(cols)), eps)));
+  const uint4* wv = reinterpret_cast<const uint4*>(weight);
+  uint8_t* qrow = q + (live ? row : 0) * cols;
+  float* srow = scales + (live ? row : 0) * (cols >> 7);
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int j = lane_in_row + k * tpr;
+    const bool have = live && j < nvec;   // the same for the 16 lanes of a group (nvec % 16 == 0)
+    float v[V], w[V], y[V];
+    unpack<T>(raw[k], v);
+    unpack<T>(have ? __ldg(wv + j) : make_uint4(0u, 0u, 0u, 0u), w);
+#pragma unroll
+    for (int i = 0; i < V; ++i) y[i] = __fmul_rn(__fmul_rn(v[i], inv), w[i]);
+    const uint4 yraw = pack<T>(y);        // the norm's output as it would have been stored
+    float f[V];
+    unpack<T>(yraw, f);
+    float amax = absmax8_packed<T2>(yraw);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    const float scale = group_scale(amax);
+    if (have) {
+      const uint2 bytes = fast_div_ok(amax) ? quantise8_fast16(yraw, f, scale, __frcp_rn(scale))
+                                            : quantise8<false>(f, scale, 0.0f);
+      *reinterpret_cast<uint2*>(qrow + j * V) = bytes;
+      if ((lane_in_row & 15) == 0) srow[j >> 4] = scale;
+    }
+  }
+}
+
 // Any shape and alignment: one CTA per row, two strided passes (the reference's own scheme).
 template <typename T, bool kAdd>
 __global__ void __launch_bounds__(kThreads)
@@ -194,6 +281,30 @@ int launch_rmsnorm_t(void* out, void* residual, const void* in, const void* weig
         static_cast<T*>(out), static_cast<T*>(residual), static_cast<const T*>(in), static_cast<const T*>(weight),
         eps, static_cast<int>(cols));
   }
+  return check_launch();
+}
+
+template <typename T, bool kAdd>
+int launch_rmsnorm_quant_t(void* q, void* scales, void* residual, const void* in, const void* weight, int64_t rows,
+                           int64_t cols, float eps, cudaStream_t stream) {
+  const int64_t nvec = cols / 8;
+  int tpr = 32;
+  while (tpr < kThreads && static_cast<int64_t>(tpr) * 4 < nvec) tpr <<= 1;
+  const int per_thread = static_cast<int>((nvec + tpr - 1) / tpr);
+  const int rows_per_cta = kThreads / tpr;
+  const int64_t grid = (rows + rows_per_cta - 1) / rows_per_cta;
+  if (grid > 0x7FFFFFFFLL) return INFEROP_ERR_LIMIT;
+  uint8_t* qp = static_cast<uint8_t*>(q);
+  float* sp = static_cast<float*>(scales);
+  T* r = static_cast<T*>(residual);
+  const T* i = static_cast<const T*>(in);
+  const T* w = static_cast<const T*>(weight);
+  const unsigned g = static_cast<unsigned>(grid);
+  const int c = static_cast<int>(cols);
+  if (per_thread <= 1) rmsnorm_quant_kernel<T, kAdd, 1><<<g, kThreads, 0, stream>>>(qp, sp, r, i, w, eps, rows, c, tpr);
+  else if (per_thread <= 2) rmsnorm_quant_kernel<T, kAdd, 2><<<g, kThreads, 0, stream>>>(qp, sp, r, i, w, eps, rows, c, tpr);
+  else if (per_thread <= 4) rmsnorm_quant_kernel<T, kAdd, 4><<<g, kThreads, 0, stream>>>(qp, sp, r, i, w, eps, rows, c, tpr);
+  else rmsnorm_quant_kernel<T, kAdd, kMaxVec><<<g, kThreads, 0, stream>>>(qp, sp, r, i, w, eps, rows, c, tpr);
   return check_launch();
 }
 
@@ -324,6 +435,19 @@ int launch_rmsnorm(void* out, void* residual, const void* in, const void* weight
                        : launch_rmsnorm_t<__half, false>(out, nullptr, in, weight, rows, cols, eps, stream);
     case 2: return add ? launch_rmsnorm_t<__nv_bfloat16, true>(out, residual, in, weight, rows, cols, eps, stream)
                        : launch_rmsnorm_t<__nv_bfloat16, false>(out, nullptr, in, weight, rows, cols, eps, stream);
+    default: return INFEROP_ERR_DTYPE;
+  }
+}
+
+int launch_rmsnorm_quant(void* q, void* scales, void* residual, const void* in, const void* weight, int32_t dt,
+                         int64_t rows, int64_t cols, float eps, cudaStream_t stream) {
+  if (cols % 128 != 0 || cols / 8 > static_cast<int64_t>(kThreads) * kMaxVec) return INFEROP_ERR_SHAPE;
+  const bool add = residual != nullptr;
+  switch (dt) {
+    case 1: return add ? launch_rmsnorm_quant_t<__half, true>(q, scales, residual, in, weight, rows, cols, eps, stream)
+                       : launch_rmsnorm_quant_t<__half, false>(q, scales, nullptr, in, weight, rows, cols, eps, stream);
+    case 2: return add ? launch_rmsnorm_quant_t<__nv_bfloat16, true>(q, scales, residual, in, weight, rows, cols, eps, stream)
+                       : launch_rmsnorm_quant_t<__nv_bfloat16, false>(q, scales, nullptr, in, weight, rows, cols, eps, stream);
     default: return INFEROP_ERR_DTYPE;
   }
 }

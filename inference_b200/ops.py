@@ -336,6 +336,31 @@ def fused_add_rmsnorm(residual: torch.Tensor, x: torch.Tensor, weight: torch.Ten
     return out
 
 
+def rmsnorm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: torch.Tensor | None = None,
+                  q: torch.Tensor | None = None, scales: torch.Tensor | None = None, stream=None):
+    """quant_fp8_per_token_group(rmsnorm(x, weight)) in one pass (with `residual`: residual += x first, in
+    place, then the norm of the sum).  x fp16 / bf16 [rows, cols], cols % 128 == 0 -> (q uint8, scales fp32)."""
+    _dev_tensor(x, "x")
+    _dev_tensor(weight, "weight")
+    if x.dim() != 2 or x.dtype not in (torch.float16, torch.bfloat16) or weight.dtype != x.dtype or \
+            tuple(weight.shape) != (x.shape[1],):
+        raise ValueError("x must be fp16 / bf16 [rows, cols] and weight [cols] of the same dtype")
+    if residual is not None:
+        _dev_tensor(residual, "residual")
+        if residual.shape != x.shape or residual.dtype != x.dtype:
+            raise ValueError("residual must match x")
+    rows, cols = x.shape
+    with torch.cuda.device(x.device):
+        if q is None:
+            q = torch.empty((rows, cols), dtype=torch.uint8, device=x.device)
+        if scales is None:
+            scales = torch.empty((rows, cols // 128), dtype=torch.float32, device=x.device)
+        check(lib.inferop_rmsnorm_quant(q.data_ptr(), scales.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                        x.data_ptr(), weight.data_ptr(), int(_TORCH2CODE[x.dtype]), rows, cols, 128,
+                                        float(eps), _stream_ptr(stream)), "rmsnorm_quant")
+    return q, scales
+
+
 def rope_neox(qkv: torch.Tensor, positions: torch.Tensor, rotary_dim: int, base: float = 10000.0,
               yarn_factor: float = 1.0, stream=None) -> torch.Tensor:
     """NeoX rotary embedding in place on qkv [tokens, heads, head_dim]; positions int64 [tokens]."""

@@ -149,3 +149,47 @@ def test_norm_and_rope_reject_bad_arguments(ops):
     assert lib.inferop_rope_neox(p, None, 0, 4, 2, 16, 8, 10000.0, 1.0, None) == _capi.ERR_POINTER
     torch.cuda.synchronize()
     assert bool((t == 0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(33, 1024), (1, 7168), (300, 128), (7, 16384), (64, 2048), (5, 4096)])
+@pytest.mark.parametrize("with_residual", [False, True])
+def test_rmsnorm_with_quantisation_equals_the_two_calls(ops, dtype, rows, cols, with_residual):
+    """The one-pass form gives the bytes and scales of rmsnorm (or fused_add_rmsnorm) followed by
+    quant_fp8_per_token_group, bit for bit, and the same updated residual."""
+    rng = np.random.default_rng(rows + cols)
+    x = torch.from_numpy(rng.standard_normal((rows, cols)).astype(np.float32)).cuda().to(dtype)
+    x[0, :128] = 0                                   # a group that normalises to zeros
+    w = torch.from_numpy(rng.uniform(0.5, 1.5, cols).astype(np.float32)).cuda().to(dtype)
+    if with_residual:
+        res = torch.from_numpy(rng.standard_normal((rows, cols)).astype(np.float32)).cuda().to(dtype)
+        res[0, :128] = 0
+        r1, r2 = res.clone(), res.clone()
+        y = ops.fused_add_rmsnorm(r1, x, w, 1e-6)
+        q, s = ops.rmsnorm_quant(x, w, 1e-6, residual=r2)
+        assert torch.equal(r1.view(torch.int16), r2.view(torch.int16))
+    else:
+        y = ops.rmsnorm(x, w, 1e-6)
+        q, s = ops.rmsnorm_quant(x, w, 1e-6)
+    q_want, s_want = ops.quant_fp8_per_token_group(y)
+    assert torch.equal(s, s_want)
+    assert torch.equal(q, q_want)
+    # and the chain against the oracle: quantising the oracle's rounded norm gives the same scales up to the
+    # rare element that rounds differently (the row sum is added in another order)
+    got_s = s.cpu().numpy()
+    xin = (x.float() + (res.float() if with_residual else 0)).to(dtype).float().cpu().numpy() if with_residual else x.float().cpu().numpy()
+    gold = oracle.rmsnorm(xin, w.float().cpu().numpy(), 1e-6)
+    _, s_gold = oracle.quant_fp8_per_token_group(rounded(gold, dtype))
+    np.testing.assert_allclose(got_s, s_gold, rtol=2e-2, atol=1e-8)
+
+
+def test_rmsnorm_with_quantisation_rejects_what_it_cannot_do(ops):
+    from inference_b200 import _capi
+    lib = _capi.lib
+    t = torch.zeros(1 << 16, dtype=torch.bfloat16, device="cuda")
+    p = t.data_ptr()
+    assert lib.inferop_rmsnorm_quant(p, p, None, p, p, 2, 4, 1000, 128, 1e-6, None) == _capi.ERR_SHAPE     # cols % 128
+    assert lib.inferop_rmsnorm_quant(p, p, None, p, p, 2, 4, 32768, 128, 1e-6, None) == _capi.ERR_SHAPE    # too wide
+    assert lib.inferop_rmsnorm_quant(p, p, None, p, p, 0, 4, 1024, 128, 1e-6, None) == _capi.ERR_DTYPE     # fp32
+    assert lib.inferop_rmsnorm_quant(p, p, None, p + 2, p, 2, 4, 1024, 128, 1e-6, None) == _capi.ERR_POINTER
+    assert lib.inferop_rmsnorm_quant(p, p, None, p, p, 2, 4, 1024, 64, 1e-6, None) == _capi.ERR_SHAPE      # group size
