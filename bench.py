@@ -332,6 +332,25 @@ def reference_cuda_baseline(m=4096, n=18432, k=7168, iters=3):
 
 
 # ----------------------------------------------------------------------------- shape sweep
+def reference_cuda_lib():
+    """oracle/_ref/libinferop_ref_cuda.so (the reference's own CUDA kernels built for sm_100) or None."""
+    import ctypes as C
+    path = os.path.join(ROOT, "oracle", "_ref", "libinferop_ref_cuda.so")
+    if not os.path.exists(path):
+        return None
+    ref = C.CDLL(path)
+    vp, i64, i32, f32 = C.c_void_p, C.c_int64, C.c_int32, C.c_float
+    try:
+        ref.refcuda_rmsnorm.argtypes = [vp, vp, vp, i32, i64, i64, f32, vp]
+        ref.refcuda_rope_neox.argtypes = [vp, vp, i32, i64, i32, i32, i32, f32, f32, vp]
+        ref.refcuda_paged_attn_decode.argtypes = [vp] * 6 + [i32] * 7 + [f32, vp]
+        for fn in (ref.refcuda_rmsnorm, ref.refcuda_rope_neox, ref.refcuda_paged_attn_decode):
+            fn.restype = None
+    except AttributeError:
+        return None          # an older build of the baseline library without these operators
+    return ref
+
+
 def block_ops(peaks, rows=16384, cols=7168, heads=32, head_dim=128, rotary=64):
     """The operators in front of the quantise + GEMM path in a transformer block (RMSNorm, residual add +
     RMSNorm, NeoX rotary embedding), bf16, device-timed on tensors larger than L2, each checked against
@@ -359,6 +378,8 @@ def block_ops(peaks, rows=16384, cols=7168, heads=32, head_dim=128, rotary=64):
         return e0.elapsed_time(e1) * 1e-3 / iters
 
     rec = {}
+    ref = reference_cuda_lib()
+    cur = torch.cuda.current_stream().cuda_stream
     rows_s = np.array([0, 1, rows // 2, rows - 1])
     t = timed(lambda: ops.rmsnorm(x, w, 1e-6, out=out))
     want = oracle.rmsnorm(x[rows_s].float().cpu().numpy(), w.float().cpu().numpy())
@@ -367,6 +388,13 @@ def block_ops(peaks, rows=16384, cols=7168, heads=32, head_dim=128, rotary=64):
     byt = 4 * rows * cols
     rec["rmsnorm"] = {"us": round(t * 1e6, 1), "gbs": round(byt / t / 1e9, 1),
                       "frac_of_measured_hbm": round(byt / t / 1e9 / peaks["hbm_gbs"], 3), "max_abs_err": err}
+    if ref is not None:
+        # the reference's own kernel (one block per row, two passes over memory) on the same tensors
+        out_r = torch.empty_like(out)
+        tr = timed(lambda: ref.refcuda_rmsnorm(out_r.data_ptr(), x.data_ptr(), w.data_ptr(), 2, rows, cols, 1e-6, cur), iters=5)
+        rec["rmsnorm"]["reference_cuda_us"] = round(tr * 1e6, 1)
+        rec["rmsnorm"]["max_abs_diff_vs_reference_cuda"] = float((out.float() - out_r.float()).abs().max().item())
+        del out_r
     res0 = res.clone()
     t = timed(lambda: ops.fused_add_rmsnorm(res, x, w, 1e-6, out=out))
     r1 = res0.clone()
@@ -407,13 +435,22 @@ def block_ops(peaks, rows=16384, cols=7168, heads=32, head_dim=128, rotary=64):
     rec["rope_neox"] = {"us": round(t * 1e6, 1), "gbs": round(byt / t / 1e9, 1),
                         "frac_of_measured_hbm": round(byt / t / 1e9 / peaks["hbm_gbs"], 3), "max_abs_err": err,
                         "shape": [rows, heads, head_dim], "rotary_dim": rotary}
+    if ref is not None:
+        q2 = q0.clone()
+        tr = timed(lambda: ref.refcuda_rope_neox(q2.data_ptr(), pos.data_ptr(), 2, rows, heads, head_dim, rotary,
+                                                 10000.0, 1.0, cur), iters=5)
+        rec["rope_neox"]["reference_cuda_us"] = round(tr * 1e6, 1)
+        q2.copy_(q0)
+        ref.refcuda_rope_neox(q2.data_ptr(), pos.data_ptr(), 2, rows, heads, head_dim, rotary, 10000.0, 1.0, cur)
+        rec["rope_neox"]["max_abs_diff_vs_reference_cuda"] = float((q1.float() - q2.float()).abs().max().item())
+        del q2
     rec["shape"] = [rows, cols]
     rec["dtype"] = "bf16"
-    rec["paged_attn_decode"] = attention_bench(peaks)
+    rec["paged_attn_decode"] = attention_bench(peaks, ref)
     return rec
 
 
-def attention_bench(peaks):
+def attention_bench(peaks, ref=None):
     """Paged attention decode, bf16, 32 query heads over 8 KV heads of 128: a batch of 64 sequences of 4096
     tokens and one sequence of 65536 tokens; bytes = the K and V rows of the sequences (read once)."""
     import numpy as np
@@ -454,9 +491,28 @@ def attention_bench(peaks):
         err = float(np.abs(o[b0:b0 + 1].float().cpu().numpy() - want).max())
         assert err <= 2e-2, f"paged attention off by {err}"
         byt = 2 * batch * length * kvh * dim * 2
-        out.append({"batch": batch, "seq_len": length, "heads": heads, "kv_heads": kvh, "head_dim": dim,
-                    "us": round(t * 1e6, 1), "gbs": round(byt / t / 1e9, 1),
-                    "frac_of_measured_hbm": round(byt / t / 1e9 / peaks["hbm_gbs"], 3), "max_abs_err": err})
+        one = {"batch": batch, "seq_len": length, "heads": heads, "kv_heads": kvh, "head_dim": dim,
+               "us": round(t * 1e6, 1), "gbs": round(byt / t / 1e9, 1),
+               "frac_of_measured_hbm": round(byt / t / 1e9 / peaks["hbm_gbs"], 3), "max_abs_err": err}
+        if ref is not None:
+            # the reference's own kernel: one block per (sequence, query head), the cache read once per query head
+            o_r = torch.empty_like(o)
+            cur = torch.cuda.current_stream().cuda_stream
+
+            def ref_call():
+                ref.refcuda_paged_attn_decode(o_r.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), tables.data_ptr(),
+                                              lens.data_ptr(), 2, batch, heads, kvh, dim, bs, per_seq, scale, cur)
+
+            ref_call()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(3):
+                ref_call()
+            e1.record()
+            torch.cuda.synchronize()
+            one["reference_cuda_us"] = round(e0.elapsed_time(e1) * 1e3 / 3, 1)
+            one["max_abs_diff_vs_reference_cuda"] = float((o.float() - o_r.float()).abs().max().item())
+        out.append(one)
         del k, v
         torch.cuda.empty_cache()
     return out
