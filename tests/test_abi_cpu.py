@@ -129,7 +129,9 @@ def test_reference_cuda_baseline_library_exports_its_two_entry_points():
     if not os.path.exists(path):
         pytest.skip("not built here (needs the reference tree)")
     lib = ctypes.CDLL(path)
-    assert hasattr(lib, "refcuda_quant_fp8_per_token_group") and hasattr(lib, "refcuda_w8a8_block_fp8_gemm")
+    for name in ("refcuda_quant_fp8_per_token_group", "refcuda_w8a8_block_fp8_gemm", "refcuda_rmsnorm",
+                 "refcuda_rope_neox", "refcuda_paged_attn_decode"):
+        assert hasattr(lib, name), name
 
 
 def test_python_wrappers_reject_mistyped_or_misshaped_operands_before_the_c_call():
