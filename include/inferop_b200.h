@@ -280,7 +280,7 @@ INFEROP_API int64_t inferop_moe_max_mtiles(int64_t tokens, int32_t topk, int32_t
  *   tile_row0 / tile_meta [inferop_moe_max_mtiles]  M-tiles of up to 128 rows that never span
  *                              two experts: first row, and (expert << 8) | (rows - 1)
  *   num_mtiles [1]             how many tiles were written
- * all int32 device arrays.  One CTA; num_experts <= 1024. */
+ * all int32 device arrays.  One launch (a cluster of up to 8 CTAs); num_experts <= 1024. */
 INFEROP_API int inferop_moe_align(const int32_t* topk_ids, int64_t tokens, int32_t topk, int32_t num_experts,
                       int32_t* counts, int32_t* offsets, int32_t* pos, int32_t* src_token,
                       int32_t* tile_row0, int32_t* tile_meta, int32_t* num_mtiles, void* stream);
@@ -391,7 +391,8 @@ INFEROP_API int inferop_selftest_quant_div(int32_t dt, uint64_t* out3);
  * key: "gemm_tma_store" (-1 auto, 0, 1), "gemm_ctas" (0 = one per SM), "gemm_path" (0 auto,
  *      1 always the large-tile kernel, 2 the small-M kernel whenever M <= 128), "gemm_block_n"
  *      (0 auto, 128 or 256: tile width of the large-tile kernel; results do not depend on it),
- *      "gemm_group_m", "decode_splits", "decode_pdl".  Returns INFEROP_ERR_SHAPE for an unknown
+ *      "gemm_group_m", "decode_splits", "decode_pdl", "align_ctas" (CTAs of the moe_align cluster:
+ *      0 auto, 1..8; the layout does not depend on it).  Returns INFEROP_ERR_SHAPE for an unknown
  *      key/value. */
 INFEROP_API int inferop_set_option(const char* key, int64_t value);
 

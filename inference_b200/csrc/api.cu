@@ -816,6 +816,11 @@ int inferop_set_option(const char* key, int64_t value) {
     o.attn_heads_per_cta = static_cast<int>(value);
   } else if (!strcmp(key, "attn_splits")) {
     o.attn_splits = static_cast<int>(value);
+  } else if (!strcmp(key, "grouped_rep")) {
+    o.grouped_rep = value != 0;
+  } else if (!strcmp(key, "align_ctas")) {
+    if (value < 0 || value > 8) return INFEROP_ERR_SHAPE;
+    o.align_ctas = static_cast<int>(value);
   } else if (!strcmp(key, "quant_pdl")) {
     o.quant_pdl = value != 0;
   } else if (!strcmp(key, "gemm_pdl")) {

@@ -95,6 +95,7 @@ struct GemmParams {
   int group_m;   // M-tiles per rasterisation band: a band's A panel stays in L2 while W streams past once
   int tma_store; // 1: epilogue goes through shared memory + TMA store
   int no_loads;  // test hook: the producer issues no load
+  int rep = 0;   // grouped launches: M-tiles of at most 32 rows run in the replicated form (gemm_body)
   // SwiGLU launches only: c receives E4M3 bytes [rows, n / 2], c_scales one fp32 per 128 of them
   float* c_scales;
   DeviceStatus* status;
@@ -158,6 +159,7 @@ struct TileInfo {
   int sb_step;   // rows of b_scales between the left and the right column half
   int sb_rows;   // one past the last valid b_scales row for this tile's group
   int col;       // first output column
+  int rep;       // 1: the tile has at most 32 rows and runs in the replicated form
 };
 
 // The tile list of a grouped launch as the kernel sees it: either the by-value GroupTable or
@@ -182,6 +184,7 @@ __device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p, const 
   TileInfo ti;
   ti.sb_step = (BN / 2) / 128;
   ti.b_row_hi = 0;
+  ti.rep = 0;
   if (kSwiglu) {
     // p.n = 2 I weight rows per group, p.tiles_n = I / 128 tiles, 128 output columns per tile
     const int mt = t / p.tiles_n, tn = t - mt * p.tiles_n;
@@ -196,6 +199,7 @@ __device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p, const 
     ti.sb_step = inter >> 7;
     ti.sb_rows = (group + 1) * p.nb;
     ti.col = tn * 128;
+    ti.rep = (p.rep && (meta & 0xFF) < 32) ? 1 : 0;
   } else if (kGrouped) {
     const int mt = t / p.tiles_n, tn = t - mt * p.tiles_n;
     const int meta = tab.meta[mt];
@@ -206,6 +210,7 @@ __device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p, const 
     ti.sb_row = group * p.nb + tn * (BN / 128);
     ti.sb_rows = (group + 1) * p.nb;
     ti.col = tn * BN;
+    ti.rep = (BN == 256 && p.rep && (meta & 0xFF) < 32) ? 1 : 0;
   } else {
     int tm, tn;
     tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
@@ -272,7 +277,7 @@ template <typename OutT, int kMode, int TBN>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtensorMap* map_b,
                                           const CUtensorMap* map_c, const GemmParams& p,
                                           const TileList tab, const PeerMaps* peers,
-                                          const int* num_mtiles_dev) {
+                                          const int* num_mtiles_dev, const CUtensorMap* map_a32 = nullptr) {
   constexpr bool kSwiglu = kMode == kModeSwiglu;
   constexpr bool kGrouped = kMode == kModeGrouped || kSwiglu;
   constexpr bool kGather = kMode == kModeGather;
@@ -354,7 +359,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           }
           uint8_t* sa = smem + stage * kStageBytes;
           mbar_arrive_expect_tx(&full[stage], kStageBytes);
-          tma_load_2d(sa, map_a, &full[stage], kb * BK, ti.a_row);
+          if (kGrouped && ti.rep) {
+            // the tile's (at most) 32 rows four times over: every quarter of the 128 accumulator
+            // lanes then holds the same rows, and each quarter's warps promote other columns
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tma_load_2d(sa + q * 32 * BK, map_a32, &full[stage], kb * BK, ti.a_row);
+          } else {
+            tma_load_2d(sa, map_a, &full[stage], kb * BK, ti.a_row);
+          }
           if constexpr (kSwiglu) {
             // two 128-row boxes of the weights: the gate rows, then the up rows of the same block
             tma_load_2d(sa + kBytesA, map_b, &full[stage], kb * BK, ti.b_row);
@@ -446,7 +458,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       bool ok = true;
       const TileInfo ti = tile_info<kGrouped, BN, kSwiglu>(t, p, tab);
-      const int gm = ti.a_row + row;
+      // Replicated form of a tile with at most 32 rows (grouped launches, 256-column tiles): the
+      // producer loaded the same 32 rows into all four row quarters of the A tile, so the four
+      // lane quarters of the accumulator hold the same 32 x 256 block.  Lane l of every warp owns
+      // tile row l, and the warp of quarter q promotes columns [32 q, 32 q + 32) of its column
+      // half: a quarter of the work per warp, with the same arithmetic per element.  Without it a
+      // small tile costs the promotion warps as much as a full one (two of the eight do it all).
+      const bool rep = kGrouped && CT == 128 && ti.rep;
+      const int gm = ti.a_row + (rep ? lane : row);
       const int nbi = ti.sb_row + half * ti.sb_step;
       const bool have = gm < ti.row_end && nbi < ti.sb_rows;
       // a TMA store writes whole 128-row boxes (clipped only at the end of C): a grouped tile
@@ -480,6 +499,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
         tc_fence_after_sync();
         const uint32_t taddr = lane_base + buf * BN;
         uint32_t v0[32], v1[32];
+        if (rep) {
+          tmem_ld_32x32(taddr + quarter * 32, v0);
+          tmem_ld_wait_pin(v0);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          promote32(acc, v0, s);
+          continue;
+        }
         tmem_ld_32x32(taddr, v0);
         tmem_ld_32x32(taddr + 32, v1);
         tmem_ld_wait_pin(v0);
@@ -521,6 +549,63 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
         // (gate) then owns one whole 128-wide output group per thread.
         named_bar_sync(3, 256);   // the previous tile's readers are done with the staging memory
         const float* accf = reinterpret_cast<const float*>(acc);
+        if (rep) {
+          // replicated form: this thread holds 32 columns (four 16-byte chunks) of tile row `lane`;
+          // the 128-wide output group of a row is spread over the four quarters' warps, which
+          // exchange their partial maxima through shared memory
+          using T2 = typename std::conditional<std::is_same<OutT, __half>::value, __half2, __nv_bfloat162>::type;
+          uint8_t* exr = store_buf + lane * 256;
+          float* amax_sh = reinterpret_cast<float*>(store_buf + 32 * 256);   // [4][32]
+          if (half == 1) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 w;
+              const float* a8 = accf + j * 8;
+              w.x = pack2<OutT>(a8[0], a8[1]);
+              w.y = pack2<OutT>(a8[2], a8[3]);
+              w.z = pack2<OutT>(a8[4], a8[5]);
+              w.w = pack2<OutT>(a8[6], a8[7]);
+              *reinterpret_cast<uint4*>(exr + (((quarter * 4 + j) ^ (lane & 15)) << 4)) = w;
+            }
+          }
+          named_bar_sync(3, 256);
+          uint4 h[4];
+          float amax = 0.0f;
+          if (half == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 g;
+              const float* a8 = accf + j * 8;
+              g.x = pack2<OutT>(a8[0], a8[1]);
+              g.y = pack2<OutT>(a8[2], a8[3]);
+              g.z = pack2<OutT>(a8[4], a8[5]);
+              g.w = pack2<OutT>(a8[6], a8[7]);
+              const uint4 u = *reinterpret_cast<const uint4*>(exr + (((quarter * 4 + j) ^ (lane & 15)) << 4));
+              h[j] = swiglu::silu_mul8<OutT>(g, u);
+              amax = fmaxf(amax, absmax8_packed<T2>(h[j]));
+            }
+            amax_sh[quarter * 32 + lane] = amax;
+          }
+          named_bar_sync(3, 256);
+          if (half == 0 && gm < ti.row_end) {
+            amax = fmaxf(fmaxf(amax_sh[lane], amax_sh[32 + lane]), fmaxf(amax_sh[64 + lane], amax_sh[96 + lane]));
+            const float scale = group_scale(amax);
+            const bool fast = fast_div_ok(amax);
+            const float rcp = __frcp_rn(scale);
+            uint8_t* qrow = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(gm) * (p.n >> 1) + ti.col + quarter * 32;
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+              float f0[8], f1[8];
+              swiglu::unpack8<OutT>(h[j], f0);
+              swiglu::unpack8<OutT>(h[j + 1], f1);
+              const uint2 b0 = fast ? quantise8_fast16(h[j], f0, scale, rcp) : quantise8<false>(f0, scale, 0.0f);
+              const uint2 b1 = fast ? quantise8_fast16(h[j + 1], f1, scale, rcp) : quantise8<false>(f1, scale, 0.0f);
+              *reinterpret_cast<uint4*>(qrow + j * 8) = make_uint4(b0.x, b0.y, b1.x, b1.y);
+            }
+            if (quarter == 0) p.c_scales[static_cast<int64_t>(gm) * (p.n >> 8) + (ti.col >> 7)] = scale;
+          }
+          continue;
+        }
         uint8_t* ex = store_buf + row * 256;
         if (half == 1) {
 #pragma unroll
@@ -594,6 +679,32 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           }
         }
         continue;
+      }
+      if constexpr (kGrouped) {
+        if (rep) {
+          // replicated form: 32 columns of tile row `lane`, stored straight from the registers
+          if (gm < ti.row_end) {
+            const float* accf = reinterpret_cast<const float*>(acc);
+            const int col0 = ti.col + half * CT + quarter * 32;
+            OutT* crow = static_cast<OutT*>(p.c) + static_cast<int64_t>(gm) * p.n;
+            constexpr int kVec = 16 / sizeof(OutT);
+#pragma unroll
+            for (int j = 0; j < 32; j += kVec) {
+              const int col = col0 + j;
+              alignas(16) OutT tmp[kVec];
+#pragma unroll
+              for (int e = 0; e < kVec; ++e) tmp[e] = to_out<OutT>(accf[j + e]);
+              if (col + kVec <= p.n && (reinterpret_cast<uintptr_t>(crow + col) & 15u) == 0) {
+                *reinterpret_cast<uint4*>(crow + col) = *reinterpret_cast<const uint4*>(tmp);
+              } else {
+#pragma unroll
+                for (int e = 0; e < kVec; ++e)
+                  if (col + e < p.n) crow[col + e] = tmp[e];
+              }
+            }
+          }
+          continue;
+        }
       }
 #pragma unroll
       for (int ch = 0; ch < CT / 64; ++ch) {
@@ -720,8 +831,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 w8a8_grouped_dev_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                              const __grid_constant__ CUtensorMap map_c, const GemmParams p,
                              const int* __restrict__ row0, const int* __restrict__ meta,
-                             const int* __restrict__ num_mtiles) {
-  gemm_body<OutT, kModeGrouped, TBN>(&map_a, &map_b, &map_c, p, TileList{row0, meta}, nullptr, num_mtiles);
+                             const int* __restrict__ num_mtiles, const __grid_constant__ CUtensorMap map_a32) {
+  gemm_body<OutT, kModeGrouped, TBN>(&map_a, &map_b, &map_c, p, TileList{row0, meta}, nullptr, num_mtiles,
+                                     &map_a32);
 }
 
 // SwiGLU launch: grouped tile list from device memory, output = E4M3 bytes + scales
@@ -729,13 +841,13 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_swiglu_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const GemmParams p, const int* __restrict__ row0, const int* __restrict__ meta,
-                        const int* __restrict__ num_mtiles) {
-  gemm_body<T, kModeSwiglu, 256>(&map_a, &map_b, nullptr, p, TileList{row0, meta}, nullptr, num_mtiles);
+                        const int* __restrict__ num_mtiles, const __grid_constant__ CUtensorMap map_a32) {
+  gemm_body<T, kModeSwiglu, 256>(&map_a, &map_b, nullptr, p, TileList{row0, meta}, nullptr, num_mtiles, &map_a32);
 }
 
 template <typename T>
-int launch_swiglu_t(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, const int* row0,
-                    const int* meta, const int* num_mtiles, int ctas, cudaStream_t stream) {
+int launch_swiglu_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma32, const GemmParams& p,
+                    const int* row0, const int* meta, const int* num_mtiles, int ctas, cudaStream_t stream) {
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -745,13 +857,13 @@ int launch_swiglu_t(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPara
     if (e != cudaSuccess) return note_cuda_error(e);
     attr_done[dev] = true;
   }
-  w8a8_swiglu_gemm_kernel<T><<<ctas, kThreads, kSmemBytes, stream>>>(ma, mb, p, row0, meta, num_mtiles);
+  w8a8_swiglu_gemm_kernel<T><<<ctas, kThreads, kSmemBytes, stream>>>(ma, mb, p, row0, meta, num_mtiles, ma32);
   return check_launch();
 }
 
 template <typename OutT, int TBN>
 int launch_grouped_dev_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
-                         const GemmParams& p, const int* row0, const int* meta, const int* num_mtiles,
+                         const CUtensorMap& ma32, const GemmParams& p, const int* row0, const int* meta, const int* num_mtiles,
                          int ctas, cudaStream_t stream) {
   static bool attr_done[64] = {};
   int dev = 0;
@@ -763,7 +875,7 @@ int launch_grouped_dev_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUt
     attr_done[dev] = true;
   }
   w8a8_grouped_dev_gemm_kernel<OutT, TBN><<<ctas, kThreads, kSmemBytes, stream>>>(ma, mb, mc, p, row0, meta,
-                                                                             num_mtiles);
+                                                                             num_mtiles, ma32);
   return check_launch();
 }
 
@@ -1083,8 +1195,11 @@ int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void
   p.c_scales = nullptr;
   p.status = ctx->status;
 
-  CUtensorMap ma, mb, mc;
+  p.rep = (opt.grouped_rep && BN == 256) ? 1 : 0;
+  CUtensorMap ma, mb, mc, ma32;
   int rc = make_tensor_map_2d(&ma, a_q, 1, m_total, k, k, BM, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  rc = make_tensor_map_2d(&ma32, a_q, 1, m_total, k, k, 32, BK, true);
   if (rc != INFEROP_OK) return rc;
   rc = make_tensor_map_2d(&mb, b_q, 1, groups * n, k, k, BN, BK, true);
   if (rc != INFEROP_OK) return rc;
@@ -1097,12 +1212,12 @@ int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void
   int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
   if (ctas > p.num_tiles) ctas = p.num_tiles;
   switch (out_dt) {
-    case 0: return BN == 128 ? launch_grouped_dev_t<float, 128>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
-                             : launch_grouped_dev_t<float, 256>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
-    case 1: return BN == 128 ? launch_grouped_dev_t<__half, 128>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
-                             : launch_grouped_dev_t<__half, 256>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
-    case 2: return BN == 128 ? launch_grouped_dev_t<__nv_bfloat16, 128>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
-                             : launch_grouped_dev_t<__nv_bfloat16, 256>(ma, mb, mc, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
+    case 0: return BN == 128 ? launch_grouped_dev_t<float, 128>(ma, mb, mc, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
+                             : launch_grouped_dev_t<float, 256>(ma, mb, mc, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
+    case 1: return BN == 128 ? launch_grouped_dev_t<__half, 128>(ma, mb, mc, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
+                             : launch_grouped_dev_t<__half, 256>(ma, mb, mc, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
+    case 2: return BN == 128 ? launch_grouped_dev_t<__nv_bfloat16, 128>(ma, mb, mc, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
+                             : launch_grouped_dev_t<__nv_bfloat16, 256>(ma, mb, mc, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
     default: return INFEROP_ERR_DTYPE;
   }
 }
@@ -1132,15 +1247,18 @@ int launch_gemm_swiglu(DeviceCtx* ctx, void* q, float* q_scales, const void* a_q
   p.group_m = 32;
   p.no_loads = opt.debug_no_loads;
   p.status = ctx->status;
-  CUtensorMap ma, mb;
+  p.rep = opt.grouped_rep ? 1 : 0;
+  CUtensorMap ma, mb, ma32;
   int rc = make_tensor_map_2d(&ma, a_q, 1, m_total, k, k, BM, BK, true);
+  if (rc != INFEROP_OK) return rc;
+  rc = make_tensor_map_2d(&ma32, a_q, 1, m_total, k, k, 32, BK, true);
   if (rc != INFEROP_OK) return rc;
   rc = make_tensor_map_2d(&mb, b_q, 1, groups * 2 * inter, k, k, 128, BK, true);
   if (rc != INFEROP_OK) return rc;
   int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
   if (ctas > p.num_tiles) ctas = p.num_tiles;
-  return mid_dt == 1 ? launch_swiglu_t<__half>(ma, mb, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
-                     : launch_swiglu_t<__nv_bfloat16>(ma, mb, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
+  return mid_dt == 1 ? launch_swiglu_t<__half>(ma, mb, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
+                     : launch_swiglu_t<__nv_bfloat16>(ma, mb, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
 }
 
 int launch_gemm_scatter(DeviceCtx* ctx, void* const* slot_peers, int32_t n_peers, int32_t rank,

@@ -53,6 +53,8 @@ struct Options {
   int fused_prologue = 0;  // one-call quantise + GEMM, M <= 32: 1 = quantise inside the small-M kernel (one launch; slower than the chained pair except at M = 1)
   int attn_heads_per_cta = 0;  // paged attention: query heads of a KV head per CTA (0 = auto: 4, 2 or 1)
   int attn_splits = 0;     // paged attention: token ranges per sequence (0 = auto)
+  int grouped_rep = 1;     // grouped GEMMs with a device tile list: M-tiles of at most 32 rows in the replicated form
+  int align_ctas = 0;      // moe_align: CTAs of its cluster (0 = auto: one per 4096 pairs, at most 8)
   int quant_pdl = 1;       // quantiser: launch with programmatic stream serialisation
   int gemm_pdl = 1;        // pair kernel: launch with programmatic stream serialisation
   int debug_no_loads = 0;  // test hook: the TMA producers of the GEMM kernels issue no load (every wait runs out)

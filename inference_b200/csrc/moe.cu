@@ -20,7 +20,10 @@
 #include <math_constants.h>
 #include <stdint.h>
 
+#include <algorithm>
+
 #include "internal.h"
+#include "ptx.cuh"
 #include "quant_math.cuh"
 #include "swiglu_math.cuh"
 
@@ -288,7 +291,8 @@ namespace {
 
 // ---------------------------------------------------------------------------------------------
 // moe_align: everything the grouped GEMM and the scatter / combine kernels need to know about a
-// routing, computed by one CTA of 1024 threads without leaving the device.
+// routing, computed without leaving the device by one thread-block cluster of up to 8 CTAs of
+// 1024 threads (one CTA for small routings).
 //   counts[e]        rows routed to expert e
 //   offsets[e]       first row of expert e in the expert-sorted order (offsets[experts] = pairs)
 //   pos[i]           sorted row of pair i = token * topk + k; inside an expert the pairs keep
@@ -296,11 +300,26 @@ namespace {
 //   src_token[r]     token whose copy sits in sorted row r
 //   tile_row0/meta   the experts' rows cut into M-tiles of up to 128 rows (first row, and
 //                    (expert << 8) | (rows - 1)); num_mtiles[0] = how many
-// The 32 warps take contiguous chunks of the pairs.  A per-warp histogram, an exclusive scan over
-// the experts and a scan over the warps give every (warp, expert) its first row; each warp then
-// walks its chunk in order, 32 pairs at a time, ranking equal experts by lane.
+// The warps of the cluster, numbered CTA by CTA, take contiguous chunks of the pairs.  Every warp
+// counts its chunk into its own histogram; a CTA's per-expert totals are read by the other CTAs
+// through distributed shared memory, so every CTA knows how many rows of an expert lie in the
+// CTAs before it and in all of them.  An exclusive scan over the experts (repeated by each CTA,
+// it is 1024 values) and the scan over the warps give every (warp, expert) its first row; each
+// warp then walks its chunk in order, 32 pairs at a time, ranking equal experts by lane.
 constexpr int kAlignThreads = 1024;
 constexpr int kAlignWarps = kAlignThreads / 32;
+constexpr int kAlignMaxCtas = 8;          // the portable cluster size
+
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ int32_t ld_cluster_s32(uint32_t cluster_addr) {
+  int32_t v;
+  asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
 
 __global__ void __launch_bounds__(kAlignThreads, 1)
 moe_align_kernel(const int32_t* __restrict__ ids, int pairs, int topk, int experts,
@@ -309,13 +328,18 @@ moe_align_kernel(const int32_t* __restrict__ ids, int pairs, int topk, int exper
                  int32_t* __restrict__ tile_meta, int32_t* __restrict__ num_mtiles) {
   extern __shared__ int32_t align_smem[];
   int32_t* hist = align_smem;                                   // [kAlignWarps][experts]
-  unsigned long long* scan = reinterpret_cast<unsigned long long*>(hist + kAlignWarps * experts);  // [1024]
+  int32_t* cta_total = hist + kAlignWarps * experts;            // [1024], read by the other CTAs
+  unsigned long long* scan = reinterpret_cast<unsigned long long*>(cta_total + kAlignThreads);  // [1024]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rank = static_cast<int>(cluster_ctarank()), nranks = static_cast<int>(cluster_nctarank());
   for (int i = tid; i < kAlignWarps * experts; i += kAlignThreads) hist[i] = 0;
   __syncthreads();
 
-  const int chunk = ((pairs + kAlignWarps - 1) / kAlignWarps + 31) & ~31;
-  const int begin = min(pairs, warp * chunk), end = min(pairs, begin + chunk);
+  const int all_warps = nranks * kAlignWarps;
+  const int chunk = ((pairs + all_warps - 1) / all_warps + 31) & ~31;
+  const long long first = static_cast<long long>(rank * kAlignWarps + warp) * chunk;
+  const int begin = static_cast<int>(min(static_cast<long long>(pairs), first));
+  const int end = static_cast<int>(min(static_cast<long long>(pairs), first + chunk));
   int32_t* my_hist = hist + warp * experts;
   for (int i0 = begin; i0 < end; i0 += 256) {   // eight loads in flight per lane
     int ev[8];
@@ -331,39 +355,67 @@ moe_align_kernel(const int32_t* __restrict__ ids, int pairs, int topk, int exper
   }
   __syncthreads();
 
-  // per expert: rows of the warps before this one, and the expert's total
-  int count = 0;
+  // per expert: rows of this CTA's warps before each warp, and the CTA's total
+  int mine = 0;
   if (tid < experts) {
     for (int w = 0; w < kAlignWarps; ++w) {
       const int c = hist[w * experts + tid];
-      hist[w * experts + tid] = count;
+      hist[w * experts + tid] = mine;
+      mine += c;
+    }
+  }
+  cta_total[tid] = mine;
+  cluster_sync_all();
+  // rows of the expert in the CTAs before this one, and in the whole cluster
+  int count = 0, before = 0;
+  if (tid < experts) {
+    const uint32_t local = smem_u32(cta_total + tid);
+    for (int r = 0; r < nranks; ++r) {
+      const int c = r == rank ? mine : ld_cluster_s32(mapa_shared(local, static_cast<uint32_t>(r)));
+      before += r < rank ? c : 0;
       count += c;
     }
   }
+  // nobody reads another CTA's shared memory after this point; the matching wait stands at the
+  // end of the kernel, so that no CTA leaves while a neighbour may still read its totals
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+
   const int tiles = (count + 127) >> 7;
-  // inclusive scan over the experts of (tiles, rows) packed into one 64-bit word
+  // inclusive scan over the experts of (tiles, rows) packed into one 64-bit word: by shuffles
+  // inside a warp, then over the 32 warp sums
   unsigned long long v = (static_cast<unsigned long long>(tiles) << 32) | static_cast<unsigned>(count);
-  scan[tid] = v;
-  __syncthreads();
-  for (int o = 1; o < kAlignThreads; o <<= 1) {
-    const unsigned long long add = tid >= o ? scan[tid - o] : 0ull;
-    __syncthreads();
-    v += add;
-    scan[tid] = v;
-    __syncthreads();
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long up = __shfl_up_sync(0xFFFFFFFFu, v, o);
+    if (lane >= o) v += up;
   }
+  if (lane == 31) scan[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    unsigned long long s = scan[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long up = __shfl_up_sync(0xFFFFFFFFu, s, o);
+      if (lane >= o) s += up;
+    }
+    scan[lane] = s;
+  }
+  __syncthreads();
+  if (warp > 0) v += scan[warp - 1];
   const int row_first = static_cast<int>(v & 0xFFFFFFFFull) - count;   // exclusive
   const int tile_first = static_cast<int>(v >> 32) - tiles;
   if (tid < experts) {
-    counts[tid] = count;
-    offsets[tid] = row_first;
-    for (int w = 0; w < kAlignWarps; ++w) hist[w * experts + tid] += row_first;
-    for (int j = 0; j < tiles; ++j) {
-      tile_row0[tile_first + j] = row_first + j * 128;
-      tile_meta[tile_first + j] = (tid << 8) | (min(128, count - j * 128) - 1);
+    for (int w = 0; w < kAlignWarps; ++w) hist[w * experts + tid] += row_first + before;
+    if (rank == 0) {
+      counts[tid] = count;
+      offsets[tid] = row_first;
+      for (int j = 0; j < tiles; ++j) {
+        tile_row0[tile_first + j] = row_first + j * 128;
+        tile_meta[tile_first + j] = (tid << 8) | (min(128, count - j * 128) - 1);
+      }
     }
   }
-  if (tid == kAlignThreads - 1) {
+  if (rank == 0 && tid == kAlignThreads - 1) {
     offsets[experts] = static_cast<int>(v & 0xFFFFFFFFull);
     num_mtiles[0] = static_cast<int>(v >> 32);
   }
@@ -402,6 +454,7 @@ moe_align_kernel(const int32_t* __restrict__ ids, int pairs, int topk, int exper
       }
     }
   }
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -496,19 +549,36 @@ int64_t moe_max_mtiles(int64_t pairs, int64_t experts) {
 int launch_moe_align(const int32_t* ids, int64_t tokens, int32_t topk, int32_t experts, int32_t* counts,
                      int32_t* offsets, int32_t* pos, int32_t* src_token, int32_t* tile_row0,
                      int32_t* tile_meta, int32_t* num_mtiles, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(kAlignWarps) * experts * 4 + kAlignThreads * 8;
+  const size_t smem = static_cast<size_t>(kAlignWarps) * experts * 4 + kAlignThreads * 4 + kAlignThreads * 8;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(moe_align_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kAlignWarps * 1024 * 4 + kAlignThreads * 8);
+                                         kAlignWarps * 1024 * 4 + kAlignThreads * 12);
     if (e != cudaSuccess) return note_cuda_error(e);
     attr_done[dev] = true;
   }
-  moe_align_kernel<<<1, kAlignThreads, smem, stream>>>(ids, static_cast<int>(tokens * topk), topk, experts,
-                                                       counts, offsets, pos, src_token, tile_row0,
-                                                       tile_meta, num_mtiles);
+  // one CTA per 4096 pairs (four steps of 32 per warp), up to the portable cluster size
+  const int64_t pairs = tokens * topk;
+  int ctas = static_cast<int>(std::min<int64_t>(kAlignMaxCtas, (pairs + 4095) / 4096));
+  if (options().align_ctas > 0) ctas = std::min(options().align_ctas, kAlignMaxCtas);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctas);
+  cfg.blockDim = dim3(kAlignThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = ctas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, moe_align_kernel, ids, static_cast<int>(pairs), static_cast<int>(topk),
+                                     static_cast<int>(experts), counts, offsets, pos, src_token, tile_row0,
+                                     tile_meta, num_mtiles);
+  if (e != cudaSuccess) return note_cuda_error(e);
   return check_launch();
 }
 

@@ -137,6 +137,42 @@ def test_moe_align_matches_the_stable_sort(ops, tokens, experts, topk):
     assert np.array_equal(lay.tile_meta.cpu().numpy()[:n], meta)
 
 
+@pytest.mark.parametrize("tokens,experts,topk", [(4096, 256, 8), (700, 1024, 6), (9, 5, 2), (40000, 16, 2)])
+def test_moe_align_layout_does_not_depend_on_the_cluster_size(ops, tokens, experts, topk):
+    """The pairs are dealt to the warps of 1 to 8 CTAs; the stable order and the tile table must
+    come out the same, also when some CTAs of the cluster get no pair at all."""
+    rng = np.random.default_rng(tokens * 7 + experts)
+    ids = rng.integers(0, experts, size=(tokens, topk)).astype(np.int32)
+    ids[rng.random(ids.shape) < 0.02] = experts + 3          # ids another rank owns
+    flat = ids.reshape(-1)
+    own = np.nonzero(flat < experts)[0]
+    order = own[np.argsort(flat[own], kind="stable")]
+    rows = len(order)
+    pos = np.full(flat.size, -1, np.int32)
+    pos[order] = np.arange(rows, dtype=np.int32)
+    src = (order // topk).astype(np.int32)
+    counts = np.bincount(flat[own], minlength=experts).astype(np.int32)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    row0 = np.array([offsets[e] + r for e in range(experts) for r in range(0, counts[e], 128)], np.int32)
+    meta = np.array([(e << 8) | (min(128, counts[e] - r) - 1) for e in range(experts)
+                     for r in range(0, counts[e], 128)], np.int32)
+    try:
+        for ctas in (1, 2, 3, 8, 0):
+            ops.set_option("align_ctas", ctas)
+            lay = ops.moe_align(cuda(ids), experts)
+            torch.cuda.synchronize()
+            n = int(lay.num_mtiles.item())
+            assert np.array_equal(lay.counts.cpu().numpy(), counts), ctas
+            assert np.array_equal(lay.offsets.cpu().numpy(), offsets), ctas
+            assert np.array_equal(lay.pos.cpu().numpy(), pos), ctas
+            assert np.array_equal(lay.src_token.cpu().numpy()[:rows], src), ctas
+            assert n == len(row0), ctas
+            assert np.array_equal(lay.tile_row0.cpu().numpy()[:n], row0), ctas
+            assert np.array_equal(lay.tile_meta.cpu().numpy()[:n], meta), ctas
+    finally:
+        ops.set_option("align_ctas", 0)
+
+
 def test_moe_align_marks_ids_outside_the_expert_range(ops):
     ids = np.array([[0, 1], [9, 1], [-3, 0]], np.int32)
     lay = ops.moe_align(cuda(ids), 4)
@@ -220,6 +256,75 @@ def test_swiglu_epilogue_equals_gemm_then_silu_and_mul_quant(ops, dt, tokens, ex
     assert bool((canary[pairs * inter:] == 0xA5).all())
     valid = int(lay.offsets.cpu()[-1].item())          # rows that belong to some expert
     assert torch.equal(q1[:valid], q2[:valid]) and torch.equal(s1[:valid], s2[:valid])
+
+
+_SMALL_TILE_COUNTS = [1, 32, 33, 129, 160, 0, 5, 159, 31, 128, 290, 17]
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+def test_grouped_gemm_small_tiles_in_the_replicated_form_are_bit_equal(ops, dt):
+    """M-tiles of at most 32 rows load their rows four times over and spread the columns over the
+    four lane quarters; the arithmetic per element is that of the plain form, so toggling the form
+    must not change a bit, and rows next to a small tile must stay untouched."""
+    from inference_b200 import synth
+    experts, n, k = len(_SMALL_TILE_COUNTS), 640, 512            # 640 = two 256-wide tiles + half a tile
+    ids = np.repeat(np.arange(experts, dtype=np.int32), _SMALL_TILE_COUNTS)
+    ids = np.random.default_rng(21).permutation(ids).reshape(-1, 1)
+    lay = ops.moe_align(cuda(ids), experts)
+    x = synth.activations(ids.shape[0], k, seed=2)
+    aq, a_s = ops.moe_scatter_quant(x, lay)
+    bq, bs = synth.quantised_weights(experts * n, k, seed=3)
+    bq, bs = bq.view(experts, n, k), bs.view(experts, n // 128, k // 128)
+    outs = []
+    try:
+        for form in (1, 0):
+            ops.set_option("grouped_rep", form)
+            out = torch.full((ids.shape[0] + 8, n), 7.0, dtype=dt, device="cuda")
+            ops.w8a8_block_fp8_gemm_grouped_tiles(aq, a_s, bq, bs, lay, out=out[:ids.shape[0]])
+            assert ops.device_status()[0] == 0
+            assert bool((out[ids.shape[0]:] == 7.0).all())
+            outs.append(out)
+    finally:
+        ops.set_option("grouped_rep", 1)
+    assert torch.equal(outs[0], outs[1])
+    want = ops.w8a8_block_fp8_gemm_grouped(aq, a_s, bq, bs, _SMALL_TILE_COUNTS, dt)
+    assert torch.equal(outs[0][:ids.shape[0]], want)
+    # the one-row expert against the oracle
+    r = int(lay.offsets.cpu()[0].item())
+    gold = oracle.w8a8_block_fp8_gemm(aq[r:r + 1].cpu().numpy(), a_s[r:r + 1].cpu().numpy(),
+                                      bq[0].cpu().numpy(), bs[0].cpu().numpy())
+    got = outs[0][r:r + 1].float().cpu().numpy()
+    assert np.linalg.norm(got - gold) <= 1e-2 * np.linalg.norm(gold)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_swiglu_epilogue_small_tiles_in_the_replicated_form_are_bit_equal(ops, dt):
+    from inference_b200 import synth
+    experts, inter, k = len(_SMALL_TILE_COUNTS), 256, 384
+    ids = np.repeat(np.arange(experts, dtype=np.int32), _SMALL_TILE_COUNTS)
+    ids = np.random.default_rng(22).permutation(ids).reshape(-1, 1)
+    rows = ids.shape[0]
+    lay = ops.moe_align(cuda(ids), experts)
+    x = synth.activations(rows, k, seed=4).to(dt)
+    aq, a_s = ops.moe_scatter_quant(x, lay)
+    bq, bs = synth.quantised_weights(experts * 2 * inter, k, seed=5)
+    bq, bs = bq.view(experts, 2 * inter, k), bs.view(experts, 2 * inter // 128, k // 128)
+    res = []
+    try:
+        for form in (1, 0):
+            ops.set_option("grouped_rep", form)
+            canary = torch.full((rows * inter + 4096,), 0xA5, dtype=torch.uint8, device="cuda")
+            q = canary[:rows * inter].view(rows, inter)
+            s = torch.full((rows, inter // 128), -1.0, dtype=torch.float32, device="cuda")
+            ops.w8a8_block_fp8_gemm_grouped_tiles_swiglu(aq, a_s, bq, bs, lay, dt, q, s)
+            assert ops.device_status()[0] == 0
+            assert bool((canary[rows * inter:] == 0xA5).all())
+            res.append((q, s))
+    finally:
+        ops.set_option("grouped_rep", 1)
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    q2, s2 = ops.silu_and_mul_quant(ops.w8a8_block_fp8_gemm_grouped_tiles(aq, a_s, bq, bs, lay, dt))
+    assert torch.equal(res[0][0], q2) and torch.equal(res[0][1], s2)
 
 
 def test_swiglu_epilogue_rejects_bad_arguments(ops):
