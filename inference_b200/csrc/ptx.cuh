@@ -172,6 +172,14 @@ __device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) 
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
+// Read-only global load that stays where it is written among the other volatile statements
+// (barrier waits, tensor-memory loads): a value requested one loop iteration before its use must
+// not be moved next to the use by the compiler when registers are short.
+__device__ __forceinline__ float ld_nc_f32_pinned(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
 // 2-D tiled load global -> shared, completion counted on an mbarrier.  x is the
 // innermost coordinate (elements); x * element size must be a multiple of 16.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
