@@ -392,7 +392,9 @@ INFEROP_API int inferop_selftest_quant_div(int32_t dt, uint64_t* out3);
  *      1 always the large-tile kernel, 2 the small-M kernel whenever M <= 128), "gemm_block_n"
  *      (0 auto, 128 or 256: tile width of the large-tile kernel; results do not depend on it),
  *      "gemm_group_m", "decode_splits", "decode_pdl", "align_ctas" (CTAs of the moe_align cluster:
- *      0 auto, 1..8; the layout does not depend on it).  Returns INFEROP_ERR_SHAPE for an unknown
+ *      0 auto, 1..8; the layout does not depend on it), "grouped_rep" (1 or 0: M-tiles of at most
+ *      32 rows in the replicated form) and "grouped_dynamic" (1 or 0: the grouped GEMMs with a
+ *      device tile list claim their tiles from a device counter); results do not depend on them.  Returns INFEROP_ERR_SHAPE for an unknown
  *      key/value. */
 INFEROP_API int inferop_set_option(const char* key, int64_t value);
 

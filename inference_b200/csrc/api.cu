@@ -96,13 +96,17 @@ DeviceCtx* current_ctx(int* err) {
     std::lock_guard<std::mutex> lock(t.ctx_mutex);
     if (c->ordinal < 0) {
       DeviceStatus* st = nullptr;
-      e = cudaMalloc(&st, sizeof(DeviceStatus));
-      if (e == cudaSuccess) e = cudaMemset(st, 0, sizeof(DeviceStatus));
+      // the status record and, 256 bytes behind it, the tile counters
+      constexpr size_t kCtxBytes = 256 + DeviceCtx::kTileCounters * sizeof(int);
+      static_assert(sizeof(DeviceStatus) <= 256, "the tile counters start 256 bytes behind the status record");
+      e = cudaMalloc(&st, kCtxBytes);
+      if (e == cudaSuccess) e = cudaMemset(st, 0, kCtxBytes);
       if (e != cudaSuccess) {
         *err = note_cuda_error(e);
         return nullptr;
       }
       c->status = st;
+      c->tile_counters = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(st) + 256);
       c->sm_version = t.sm[dev];
       c->sm_count = t.sms[dev];
       c->ordinal = dev;
@@ -818,6 +822,8 @@ int inferop_set_option(const char* key, int64_t value) {
     o.attn_splits = static_cast<int>(value);
   } else if (!strcmp(key, "grouped_rep")) {
     o.grouped_rep = value != 0;
+  } else if (!strcmp(key, "grouped_dynamic")) {
+    o.grouped_dynamic = value != 0;
   } else if (!strcmp(key, "align_ctas")) {
     if (value < 0 || value > 8) return INFEROP_ERR_SHAPE;
     o.align_ctas = static_cast<int>(value);

@@ -47,6 +47,8 @@
 
 #include <type_traits>
 
+#include <atomic>
+
 #include "internal.h"
 #include "quant_math.cuh"
 #include "swiglu_math.cuh"
@@ -95,6 +97,9 @@ struct GemmParams {
   int group_m;   // M-tiles per rasterisation band: a band's A panel stays in L2 while W streams past once
   int tma_store; // 1: epilogue goes through shared memory + TMA store
   int no_loads;  // test hook: the producer issues no load
+  // Grouped launches with a device tile list: tiles are claimed from this counter (zeroed before the
+  // launch) instead of being dealt round-robin, nullptr = static dealing.  See gemm_body.
+  int* sched = nullptr;
   int rep = 0;   // grouped launches: M-tiles of at most 32 rows run in the replicated form (gemm_body)
   // SwiGLU launches only: c receives E4M3 bytes [rows, n / 2], c_scales one fp32 per 128 of them
   float* c_scales;
@@ -108,7 +113,10 @@ enum : uint32_t {
   kSiteMmaTmemEmpty = 0x201,
   kSiteMmaFull = 0x202,
   kSitePromoTmemFull = 0x301,
+  kSiteSchedEmpty = 0x401,
+  kSiteSchedFull = 0x402,
 };
+constexpr int kSchedSlots = 4;   // claimed tiles the producer may be ahead of the slowest consumer warp
 
 // Grouped (MoE) launches: the rows of A and C are the concatenation of the groups' rows, the
 // weights are [groups][N][K].  The host cuts every group into 128-row M-tiles and passes the
@@ -292,6 +300,18 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
   // waiting for whenever two TMA loads complete out of order (seen as a launch failure at full
   // size on 4 GPUs in a three-stage experiment); such a variant needs one barrier per stage AND warp.
   static_assert(kStages % 2 == 0 && kSlices % 2 == 0, "a ring stage must always belong to the same issuer warp");
+  // Registers per thread after the role split (setmaxnreg; ptxas allocates each branch against its
+  // own figure).  The CTA owns what it was launched with, 384 threads x 168 registers, and
+  // setmaxnreg.inc waits until that pool can serve it: the 128 threads of warps 0-3 must give back
+  // at least what the 256 promotion threads take, or the kernel never gets past the role split.
+  // The 256-column tile needs every register it can get for its 128 accumulators and two
+  // 32-column loads in flight; with the 128-column tile the producer and MMA warps keep 80, which
+  // is what their branch needs to stay free of spills.
+  constexpr int kLaunchRegs = 168;
+  constexpr int kLowRegs = TBN == 256 ? 56 : 80;
+  constexpr int kHighRegs = TBN == 256 ? 224 : 208;
+  static_assert(128 * (kLaunchRegs - kLowRegs) >= 256 * (kHighRegs - kLaunchRegs),
+                "warps 0-3 must release at least the registers the promotion warps request");
   // a device-built tile list comes with its length in device memory (at most p.tiles_m entries)
   const int num_tiles =
       (kGrouped && num_mtiles_dev != nullptr) ? min(__ldg(num_mtiles_dev), p.tiles_m) * p.tiles_n
@@ -305,8 +325,21 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
   uint64_t* empty = bars + kStages;                 // [kStages]  MMA (both issuers) -> TMA
   uint64_t* tmem_full = bars + 2 * kStages;         // [kSlices]  MMA -> promotion
   uint64_t* tmem_empty = tmem_full + kSlices;       // [kSlices]  promotion -> MMA
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + kSlices);
+  uint64_t* sched_full = tmem_empty + kSlices;      // [kSchedSlots]  producer -> MMA and promotion warps
+  uint64_t* sched_empty = sched_full + kSchedSlots; // [kSchedSlots]  the ten consumer warps -> producer
+  volatile int* sched_tile = reinterpret_cast<volatile int*>(sched_empty + kSchedSlots);   // [kSchedSlots]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(const_cast<int*>(sched_tile) + kSchedSlots);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  static_assert((2 * kStages + 2 * kSlices + 2 * kSchedSlots) * 8 + kSchedSlots * 4 + 8 <= kBarrierBytes,
+                "barriers, tile slots and flags must fit their corner of shared memory");
+  // Tiles claimed from a device counter.  Dealt round-robin, the CTAs drift apart by tens of
+  // microseconds over a launch, and the two M-tiles of one expert, which stream the same weights,
+  // end up so far apart that the second reader misses L2 (1.45 times the weight bytes came from
+  // HBM on a 256-expert layer).  With a counter, tiles next to each other in the list start within
+  // microseconds of each other whatever happened before.  The producer claims a tile when it has
+  // issued the last load of the previous one and publishes it to the other warps through a small
+  // ring of slots; -1 ends the list.  The results do not depend on who computes which tile.
+  const bool dyn = kGrouped && p.sched != nullptr;
 
   // the shuffle tells the compiler that the warp index is uniform across the warp
   const int warp = __shfl_sync(0xFFFFFFFFu, static_cast<int>(threadIdx.x >> 5), 0);
@@ -320,6 +353,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
     for (int b = 0; b < kSlices; ++b) {
       mbar_init(&tmem_full[b], 1);
       mbar_init(&tmem_empty[b], kPromoWarps);
+    }
+    for (int q = 0; q < kSchedSlots; ++q) {
+      mbar_init(&sched_full[q], 1);
+      mbar_init(&sched_empty[q], 2 + kPromoWarps);
     }
     *abort_flag = 0u;
     mbar_init_fence();
@@ -339,18 +376,50 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_slot, 0);
-  const uint32_t my_tiles =
-      static_cast<int>(blockIdx.x) < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+
+  // the next tile of this CTA as an MMA or promotion warp sees it: -1 at the end of the list, -2
+  // when the wait for the producer's slot ran out
+  uint32_t sched_i = 0;
+  auto next_tile = [&](int prev) -> int {
+    if (!dyn) {
+      const int t = prev < 0 ? static_cast<int>(blockIdx.x) : prev + static_cast<int>(gridDim.x);
+      return t < num_tiles ? t : -1;
+    }
+    const uint32_t q = sched_i % kSchedSlots;
+    if (!mbar_wait(&sched_full[q], (sched_i / kSchedSlots) & 1u, abort_flag, p.status, kSiteSchedFull)) return -2;
+    const int t = sched_tile[q];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sched_empty[q]);
+    ++sched_i;
+    return t;
+  };
 
   if (warp < 4) {
-    reg_dealloc<56>();
+    reg_dealloc<kLowRegs>();
     if (warp == 0 && lane == 0) {
       // ------------------------------ TMA producer ------------------------
       int stage = 0;
       uint32_t phase = 0;
       uint32_t armed = 0, armed_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && !p.no_loads && t < num_tiles; t += gridDim.x) {
+      uint32_t claim_i = 0;
+      for (int t = blockIdx.x; ok && !p.no_loads; t += gridDim.x) {
+        if (dyn) {
+          const uint32_t q = claim_i % kSchedSlots;
+          if (!mbar_wait(&sched_empty[q], ((claim_i / kSchedSlots) & 1u) ^ 1u, abort_flag, p.status,
+                         kSiteSchedEmpty)) {
+            ok = false;
+            break;
+          }
+          t = atomicAdd(p.sched, 1);
+          if (t >= num_tiles) t = -1;
+          sched_tile[q] = t;
+          mbar_arrive(&sched_full[q]);
+          ++claim_i;
+          if (t < 0) break;
+        } else if (t >= num_tiles) {
+          break;
+        }
         const TileInfo ti = tile_info<kGrouped, BN, kSwiglu>(t, p, tab);
         for (int kb = 0; kb < p.kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty)) {
@@ -405,12 +474,23 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       // and 92 per commit, against more than 120 per MMA from divergent single-lane code);
       // one elected lane issues the tcgen05 instructions.
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN);
-      const uint32_t total = my_tiles * static_cast<uint32_t>(p.kb);
       const uint32_t smem_base = smem_u32(smem);
+      // K blocks of the tiles seen so far (the warps learn of a tile from next_tile)
+      uint32_t total = 0;
+      int mma_t = -1;
       // K block `it` uses ring stage it % kStages and accumulator buffer it % kSlices; this warp
       // steps by two, so it keeps running counters instead of dividing (kStages and kSlices are even)
       uint32_t stage = warp - 1, phase = 0, buf = warp - 1, use = 0;
-      for (uint32_t it = warp - 1; it < total; it += 2, stage += 2, buf += 2) {
+      for (uint32_t it = warp - 1;; it += 2, stage += 2, buf += 2) {
+        while (it >= total && mma_t != -2) {
+          mma_t = next_tile(mma_t);
+          if (mma_t < 0) {
+            mma_t = -2;
+            break;
+          }
+          total += static_cast<uint32_t>(p.kb);
+        }
+        if (it >= total) break;
         if (stage >= static_cast<uint32_t>(kStages)) {
           stage -= kStages;
           phase ^= 1u;
@@ -444,7 +524,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       }
     }
   } else {
-    reg_alloc<224>();
+    reg_alloc<kHighRegs>();
     // ------------------------------ promotion + epilogue ------------------
     const int pw = warp - 4;
     const int quarter = pw & 3;  // == warp % 4: the TMEM lane quarter this warp may read
@@ -455,7 +535,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
     const bool issuer = (quarter == 0 && lane == 0);
     uint32_t kiter = 0;
     bool gave_up = false;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    for (int t = next_tile(-1);; t = next_tile(t)) {
+      if (t < 0) {
+        gave_up = t == -2;
+        break;
+      }
       bool ok = true;
       const TileInfo ti = tile_info<kGrouped, BN, kSwiglu>(t, p, tab);
       // Replicated form of a tile with at most 32 rows (grouped launches, 256-column tiles): the
@@ -465,109 +549,64 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
       // half: a quarter of the work per warp, with the same arithmetic per element.  Without it a
       // small tile costs the promotion warps as much as a full one (two of the eight do it all).
       const bool rep = kGrouped && CT == 128 && ti.rep;
-      const int gm = ti.a_row + (rep ? lane : row);
-      const int nbi = ti.sb_row + half * ti.sb_step;
-      const bool have = gm < ti.row_end && nbi < ti.sb_rows;
-      // a TMA store writes whole 128-row boxes (clipped only at the end of C): a grouped tile
-      // with fewer rows must not spill into the next group's rows
-      const bool tma_store = p.tma_store && (!kGrouped || ti.row_end - ti.a_row == BM);
-      const float* sa_ptr = p.a_scales + static_cast<int64_t>(have ? gm : 0) * p.kb;
-      const float* sb_ptr = p.b_scales + static_cast<int64_t>(have ? nbi : 0) * p.kb;
-
-      float2 acc[CT / 2];
+      if constexpr (kGrouped && CT == 128) {
+        if (rep) {
+          // the whole replicated path is kept apart from the full one: 32 accumulators instead of
+          // 128, and nothing of it inside the full path's loop
+          const int gm = ti.a_row + lane;
+          const int nbi = ti.sb_row + half * ti.sb_step;
+          const bool have = gm < ti.row_end && nbi < ti.sb_rows;
+          const float* sa_ptr = p.a_scales + static_cast<int64_t>(have ? gm : 0) * p.kb;
+          const float* sb_ptr = p.b_scales + static_cast<int64_t>(have ? nbi : 0) * p.kb;
+          float2 acc[16];
 #pragma unroll
-      for (int j = 0; j < CT / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
-
-      // The scales of a K block are requested three blocks before the product that uses them, so
-      // an L2 round trip (and most of an HBM one: expert rows' scales are used by one wave of
-      // N-tiles only) never stalls this warp; a warp that waits holds up the accumulator buffer
-      // for all eight.  The loads are pinned where they are written: builds in which the compiler
-      // had them one block ahead, or next to their use, ran expert tiles 1.5-1.7 times slower.
-      float sa_q0 = 0.0f, sa_q1 = 0.0f, sa_q2 = 0.0f, sb_q0 = 0.0f, sb_q1 = 0.0f, sb_q2 = 0.0f;
-      if (have) {
-        sa_q0 = ld_nc_f32_pinned(sa_ptr);
-        sb_q0 = ld_nc_f32_pinned(sb_ptr);
-        if (p.kb > 1) {
-          sa_q1 = ld_nc_f32_pinned(sa_ptr + 1);
-          sb_q1 = ld_nc_f32_pinned(sb_ptr + 1);
-        }
-        if (p.kb > 2) {
-          sa_q2 = ld_nc_f32_pinned(sa_ptr + 2);
-          sb_q2 = ld_nc_f32_pinned(sb_ptr + 2);
-        }
-      }
-      for (int kb = 0; kb < p.kb; ++kb, ++kiter) {
-        const float s = sa_q0 * sb_q0;
-        sa_q0 = sa_q1;
-        sb_q0 = sb_q1;
-        sa_q1 = sa_q2;
-        sb_q1 = sb_q2;
-        if (kb + 3 < p.kb && have) {
-          sa_q2 = ld_nc_f32_pinned(sa_ptr + kb + 3);
-          sb_q2 = ld_nc_f32_pinned(sb_ptr + kb + 3);
-        }
-        const uint32_t buf = kiter % kSlices;
-        if (!mbar_wait(&tmem_full[buf], (kiter / kSlices) & 1u, abort_flag, p.status,
-                       kSitePromoTmemFull)) {
-          ok = false;
-          break;
-        }
-        TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 0);
-        __syncwarp();
-        tc_fence_after_sync();
-        const uint32_t taddr = lane_base + buf * BN;
-        uint32_t v0[32], v1[32];
-        if (rep) {
-          tmem_ld_32x32(taddr + quarter * 32, v0);
-          tmem_ld_wait_pin(v0);
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-          promote32(acc, v0, s);
-          continue;
-        }
-        tmem_ld_32x32(taddr, v0);
-        tmem_ld_32x32(taddr + 32, v1);
-        tmem_ld_wait_pin(v0);
-        tmem_ld_wait_pin(v1);
-        if constexpr (CT == 128) {
-          TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 1);
-          promote32(acc, v0, s);
-          tmem_ld_32x32(taddr + 64, v0);
-          promote32(acc + 16, v1, s);
-          tmem_ld_32x32(taddr + 96, v1);
-          tmem_ld_wait_pin(v0);
-          tmem_ld_wait_pin(v1);
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-          TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 2);
-          promote32(acc + 32, v0, s);
-          promote32(acc + 48, v1, s);
-          TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 3);
-        } else {
-          // 64 columns per thread: one round of loads, the buffer is free before the FMAs
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-          promote32(acc, v0, s);
-          promote32(acc + 16, v1, s);
-        }
-      }
-      if (!ok) {
-        gave_up = true;
-        break;
-      }
-
-      // ---- epilogue: this thread holds C[gm, col .. col + 128) in fp32
-      if constexpr (kSwiglu) {
-        // The right column half (up) parks its 128 values per row, rounded to the 16-bit type, in
-        // the staging memory: row r = 256 bytes, 16-byte chunk j at position j ^ (r & 15), which
-        // keeps both the row-per-thread writes and reads free of bank conflicts.  The left half
-        // (gate) then owns one whole 128-wide output group per thread.
-        named_bar_sync(3, 256);   // the previous tile's readers are done with the staging memory
-        const float* accf = reinterpret_cast<const float*>(acc);
-        if (rep) {
+          for (int j = 0; j < 16; ++j) acc[j] = make_float2(0.0f, 0.0f);
+          float sa_q0 = 0.0f, sa_q1 = 0.0f, sa_q2 = 0.0f, sb_q0 = 0.0f, sb_q1 = 0.0f, sb_q2 = 0.0f;
+          if (have) {
+            sa_q0 = ld_nc_f32_pinned(sa_ptr);
+            sb_q0 = ld_nc_f32_pinned(sb_ptr);
+            if (p.kb > 1) {
+              sa_q1 = ld_nc_f32_pinned(sa_ptr + 1);
+              sb_q1 = ld_nc_f32_pinned(sb_ptr + 1);
+            }
+            if (p.kb > 2) {
+              sa_q2 = ld_nc_f32_pinned(sa_ptr + 2);
+              sb_q2 = ld_nc_f32_pinned(sb_ptr + 2);
+            }
+          }
+          for (int kb = 0; kb < p.kb; ++kb, ++kiter) {
+            const float s = sa_q0 * sb_q0;
+            sa_q0 = sa_q1;
+            sb_q0 = sb_q1;
+            sa_q1 = sa_q2;
+            sb_q1 = sb_q2;
+            if (kb + 3 < p.kb && have) {
+              sa_q2 = ld_nc_f32_pinned(sa_ptr + kb + 3);
+              sb_q2 = ld_nc_f32_pinned(sb_ptr + kb + 3);
+            }
+            const uint32_t buf = kiter % kSlices;
+            if (!mbar_wait(&tmem_full[buf], (kiter / kSlices) & 1u, abort_flag, p.status,
+                           kSitePromoTmemFull)) {
+              ok = false;
+              break;
+            }
+            __syncwarp();
+            tc_fence_after_sync();
+            uint32_t v0[32];
+            tmem_ld_32x32(lane_base + buf * BN + quarter * 32, v0);
+            tmem_ld_wait_pin(v0);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            promote32(acc, v0, s);
+          }
+          if (!ok) {
+            gave_up = true;
+            break;
+          }
+          const float* accf = reinterpret_cast<const float*>(acc);
+          if constexpr (kSwiglu) {
+            named_bar_sync(3, 256);   // the previous tile's readers are done with the staging memory
           // replicated form: this thread holds 32 columns (four 16-byte chunks) of tile row `lane`;
           // the 128-wide output group of a row is spread over the four quarters' warps, which
           // exchange their partial maxima through shared memory
@@ -623,7 +662,126 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
             if (quarter == 0) p.c_scales[static_cast<int64_t>(gm) * (p.n >> 8) + (ti.col >> 7)] = scale;
           }
           continue;
+          } else {
+          // replicated form: 32 columns of tile row `lane`, stored straight from the registers
+          if (gm < ti.row_end) {
+            const float* accf = reinterpret_cast<const float*>(acc);
+            const int col0 = ti.col + half * CT + quarter * 32;
+            OutT* crow = static_cast<OutT*>(p.c) + static_cast<int64_t>(gm) * p.n;
+            constexpr int kVec = 16 / sizeof(OutT);
+#pragma unroll
+            for (int j = 0; j < 32; j += kVec) {
+              const int col = col0 + j;
+              alignas(16) OutT tmp[kVec];
+#pragma unroll
+              for (int e = 0; e < kVec; ++e) tmp[e] = to_out<OutT>(accf[j + e]);
+              if (col + kVec <= p.n && (reinterpret_cast<uintptr_t>(crow + col) & 15u) == 0) {
+                *reinterpret_cast<uint4*>(crow + col) = *reinterpret_cast<const uint4*>(tmp);
+              } else {
+#pragma unroll
+                for (int e = 0; e < kVec; ++e)
+                  if (col + e < p.n) crow[col + e] = tmp[e];
+              }
+            }
+          }
+          continue;
+          }
+          continue;
         }
+      }
+      const int gm = ti.a_row + row;
+      const int nbi = ti.sb_row + half * ti.sb_step;
+      const bool have = gm < ti.row_end && nbi < ti.sb_rows;
+      // a TMA store writes whole 128-row boxes (clipped only at the end of C): a grouped tile
+      // with fewer rows must not spill into the next group's rows
+      const bool tma_store = p.tma_store && (!kGrouped || ti.row_end - ti.a_row == BM);
+      const float* sa_ptr = p.a_scales + static_cast<int64_t>(have ? gm : 0) * p.kb;
+      const float* sb_ptr = p.b_scales + static_cast<int64_t>(have ? nbi : 0) * p.kb;
+
+      float2 acc[CT / 2];
+#pragma unroll
+      for (int j = 0; j < CT / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
+
+      // The scales of a K block are requested three blocks before the product that uses them, so
+      // an L2 round trip (and most of an HBM one: expert rows' scales are used by one wave of
+      // N-tiles only) never stalls this warp; a warp that waits holds up the accumulator buffer
+      // for all eight.  The loads are pinned where they are written: builds in which the compiler
+      // had them one block ahead, or next to their use, ran expert tiles 1.5-1.7 times slower.
+      float sa_q0 = 0.0f, sa_q1 = 0.0f, sa_q2 = 0.0f, sb_q0 = 0.0f, sb_q1 = 0.0f, sb_q2 = 0.0f;
+      if (have) {
+        sa_q0 = ld_nc_f32_pinned(sa_ptr);
+        sb_q0 = ld_nc_f32_pinned(sb_ptr);
+        if (p.kb > 1) {
+          sa_q1 = ld_nc_f32_pinned(sa_ptr + 1);
+          sb_q1 = ld_nc_f32_pinned(sb_ptr + 1);
+        }
+        if (p.kb > 2) {
+          sa_q2 = ld_nc_f32_pinned(sa_ptr + 2);
+          sb_q2 = ld_nc_f32_pinned(sb_ptr + 2);
+        }
+      }
+      for (int kb = 0; kb < p.kb; ++kb, ++kiter) {
+        const float s = sa_q0 * sb_q0;
+        sa_q0 = sa_q1;
+        sb_q0 = sb_q1;
+        sa_q1 = sa_q2;
+        sb_q1 = sb_q2;
+        if (kb + 3 < p.kb && have) {
+          sa_q2 = ld_nc_f32_pinned(sa_ptr + kb + 3);
+          sb_q2 = ld_nc_f32_pinned(sb_ptr + kb + 3);
+        }
+        const uint32_t buf = kiter % kSlices;
+        if (!mbar_wait(&tmem_full[buf], (kiter / kSlices) & 1u, abort_flag, p.status,
+                       kSitePromoTmemFull)) {
+          ok = false;
+          break;
+        }
+        TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 0);
+        __syncwarp();
+        tc_fence_after_sync();
+        const uint32_t taddr = lane_base + buf * BN;
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32(taddr, v0);
+        tmem_ld_32x32(taddr + 32, v1);
+        tmem_ld_wait_pin(v0);
+        tmem_ld_wait_pin(v1);
+        if constexpr (CT == 128) {
+          TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 1);
+          promote32(acc, v0, s);
+          tmem_ld_32x32(taddr + 64, v0);
+          promote32(acc + 16, v1, s);
+          tmem_ld_32x32(taddr + 96, v1);
+          tmem_ld_wait_pin(v0);
+          tmem_ld_wait_pin(v1);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 2);
+          promote32(acc + 32, v0, s);
+          promote32(acc + 48, v1, s);
+          TRACE(0, blockIdx.x == 0 && lane == 0 && quarter == 0, 2 + half, kiter, 3);
+        } else {
+          // 64 columns per thread: one round of loads, the buffer is free before the FMAs
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          promote32(acc, v0, s);
+          promote32(acc + 16, v1, s);
+        }
+      }
+      if (!ok) {
+        gave_up = true;
+        break;
+      }
+
+      // ---- epilogue: this thread holds C[gm, col .. col + 128) in fp32
+      if constexpr (kSwiglu) {
+        // The right column half (up) parks its 128 values per row, rounded to the 16-bit type, in
+        // the staging memory: row r = 256 bytes, 16-byte chunk j at position j ^ (r & 15), which
+        // keeps both the row-per-thread writes and reads free of bank conflicts.  The left half
+        // (gate) then owns one whole 128-wide output group per thread.
+        named_bar_sync(3, 256);   // the previous tile's readers are done with the staging memory
+        const float* accf = reinterpret_cast<const float*>(acc);
         uint8_t* ex = store_buf + row * 256;
         if (half == 1) {
 #pragma unroll
@@ -697,32 +855,6 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* map_a, const CUtens
           }
         }
         continue;
-      }
-      if constexpr (kGrouped) {
-        if (rep) {
-          // replicated form: 32 columns of tile row `lane`, stored straight from the registers
-          if (gm < ti.row_end) {
-            const float* accf = reinterpret_cast<const float*>(acc);
-            const int col0 = ti.col + half * CT + quarter * 32;
-            OutT* crow = static_cast<OutT*>(p.c) + static_cast<int64_t>(gm) * p.n;
-            constexpr int kVec = 16 / sizeof(OutT);
-#pragma unroll
-            for (int j = 0; j < 32; j += kVec) {
-              const int col = col0 + j;
-              alignas(16) OutT tmp[kVec];
-#pragma unroll
-              for (int e = 0; e < kVec; ++e) tmp[e] = to_out<OutT>(accf[j + e]);
-              if (col + kVec <= p.n && (reinterpret_cast<uintptr_t>(crow + col) & 15u) == 0) {
-                *reinterpret_cast<uint4*>(crow + col) = *reinterpret_cast<const uint4*>(tmp);
-              } else {
-#pragma unroll
-                for (int e = 0; e < kVec; ++e)
-                  if (col + e < p.n) crow[col + e] = tmp[e];
-              }
-            }
-          }
-          continue;
-        }
       }
 #pragma unroll
       for (int ch = 0; ch < CT / 64; ++ch) {
@@ -1182,6 +1314,20 @@ int launch_gemm_into(DeviceCtx* ctx, void* c_base, int64_t ldc, int64_t col0, co
   return launch_gemm_to_wide(ctx, dsts, 1, ldc, col0, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, stream);
 }
 
+namespace {
+// A zeroed tile counter for one launch (see gemm_body): the context's counters in rotation, so
+// that launches in flight on different streams do not share one.  A launch captured in a graph
+// keeps its counter: such a graph must not run concurrently with itself.
+int claim_tile_counter(DeviceCtx* ctx, cudaStream_t stream, int** out) {
+  static std::atomic<unsigned> next{0};
+  int* c = ctx->tile_counters + (next.fetch_add(1) % DeviceCtx::kTileCounters);
+  cudaError_t e = cudaMemsetAsync(c, 0, sizeof(int), stream);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  *out = c;
+  return INFEROP_OK;
+}
+}  // namespace
+
 int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales,
                             const void* b_q, const void* b_scales, const int32_t* tile_row0,
                             const int32_t* tile_meta, const int32_t* num_mtiles, int64_t max_mtiles,
@@ -1229,6 +1375,10 @@ int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void
   }
   int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
   if (ctas > p.num_tiles) ctas = p.num_tiles;
+  if (opt.grouped_dynamic) {
+    rc = claim_tile_counter(ctx, stream, &p.sched);
+    if (rc != INFEROP_OK) return rc;
+  }
   switch (out_dt) {
     case 0: return BN == 128 ? launch_grouped_dev_t<float, 128>(ma, mb, mc, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
                              : launch_grouped_dev_t<float, 256>(ma, mb, mc, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
@@ -1275,6 +1425,10 @@ int launch_gemm_swiglu(DeviceCtx* ctx, void* q, float* q_scales, const void* a_q
   if (rc != INFEROP_OK) return rc;
   int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
   if (ctas > p.num_tiles) ctas = p.num_tiles;
+  if (opt.grouped_dynamic) {
+    rc = claim_tile_counter(ctx, stream, &p.sched);
+    if (rc != INFEROP_OK) return rc;
+  }
   return mid_dt == 1 ? launch_swiglu_t<__half>(ma, mb, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream)
                      : launch_swiglu_t<__nv_bfloat16>(ma, mb, ma32, p, tile_row0, tile_meta, num_mtiles, ctas, stream);
 }

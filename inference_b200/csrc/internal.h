@@ -20,6 +20,10 @@ struct DeviceCtx {
   int sm_version = 0;
   int sm_count = 0;
   DeviceStatus* status = nullptr;  // device memory, zero-initialised
+  // Tile counters of the grouped GEMM launches that claim their tiles on the device: kTileCounters
+  // ints behind the status record, one per launch in rotation (zeroed on the stream before the launch).
+  static constexpr int kTileCounters = 64;
+  int* tile_counters = nullptr;
   // Scratch of the small-M GEMM path, one set per stream that has used it (launches on one
   // stream run in order and may share a set; launches on different streams may overlap).
   static constexpr int kMaxStreams = 64;
@@ -54,6 +58,7 @@ struct Options {
   int attn_heads_per_cta = 0;  // paged attention: query heads of a KV head per CTA (0 = auto: 4, 2 or 1)
   int attn_splits = 0;     // paged attention: token ranges per sequence (0 = auto)
   int grouped_rep = 1;     // grouped GEMMs with a device tile list: M-tiles of at most 32 rows in the replicated form
+  int grouped_dynamic = 1; // grouped GEMMs with a device tile list: tiles claimed from a device counter (0: dealt round-robin)
   int align_ctas = 0;      // moe_align: CTAs of its cluster (0 = auto: one per 4096 pairs, at most 8)
   int quant_pdl = 1;       // quantiser: launch with programmatic stream serialisation
   int gemm_pdl = 1;        // pair kernel: launch with programmatic stream serialisation

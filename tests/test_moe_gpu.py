@@ -259,13 +259,15 @@ def test_swiglu_epilogue_equals_gemm_then_silu_and_mul_quant(ops, dt, tokens, ex
 
 
 _SMALL_TILE_COUNTS = [1, 32, 33, 129, 160, 0, 5, 159, 31, 128, 290, 17]
+_FORMS = [(1, 1), (0, 1), (1, 0), (0, 0)]    # (small tiles replicated, tiles claimed from a device counter)
 
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
 def test_grouped_gemm_small_tiles_in_the_replicated_form_are_bit_equal(ops, dt):
     """M-tiles of at most 32 rows load their rows four times over and spread the columns over the
     four lane quarters; the arithmetic per element is that of the plain form, so toggling the form
-    must not change a bit, and rows next to a small tile must stay untouched."""
+    must not change a bit, and rows next to a small tile must stay untouched.  Nor may it matter
+    whether the CTAs claim their tiles from the device counter or are dealt them round-robin."""
     from inference_b200 import synth
     experts, n, k = len(_SMALL_TILE_COUNTS), 640, 512            # 640 = two 256-wide tiles + half a tile
     ids = np.repeat(np.arange(experts, dtype=np.int32), _SMALL_TILE_COUNTS)
@@ -277,8 +279,9 @@ def test_grouped_gemm_small_tiles_in_the_replicated_form_are_bit_equal(ops, dt):
     bq, bs = bq.view(experts, n, k), bs.view(experts, n // 128, k // 128)
     outs = []
     try:
-        for form in (1, 0):
+        for form, claimed in _FORMS:
             ops.set_option("grouped_rep", form)
+            ops.set_option("grouped_dynamic", claimed)
             out = torch.full((ids.shape[0] + 8, n), 7.0, dtype=dt, device="cuda")
             ops.w8a8_block_fp8_gemm_grouped_tiles(aq, a_s, bq, bs, lay, out=out[:ids.shape[0]])
             assert ops.device_status()[0] == 0
@@ -286,7 +289,9 @@ def test_grouped_gemm_small_tiles_in_the_replicated_form_are_bit_equal(ops, dt):
             outs.append(out)
     finally:
         ops.set_option("grouped_rep", 1)
-    assert torch.equal(outs[0], outs[1])
+        ops.set_option("grouped_dynamic", 1)
+    for o in outs[1:]:
+        assert torch.equal(outs[0], o)
     want = ops.w8a8_block_fp8_gemm_grouped(aq, a_s, bq, bs, _SMALL_TILE_COUNTS, dt)
     assert torch.equal(outs[0][:ids.shape[0]], want)
     # the one-row expert against the oracle
@@ -311,8 +316,9 @@ def test_swiglu_epilogue_small_tiles_in_the_replicated_form_are_bit_equal(ops, d
     bq, bs = bq.view(experts, 2 * inter, k), bs.view(experts, 2 * inter // 128, k // 128)
     res = []
     try:
-        for form in (1, 0):
+        for form, claimed in _FORMS:
             ops.set_option("grouped_rep", form)
+            ops.set_option("grouped_dynamic", claimed)
             canary = torch.full((rows * inter + 4096,), 0xA5, dtype=torch.uint8, device="cuda")
             q = canary[:rows * inter].view(rows, inter)
             s = torch.full((rows, inter // 128), -1.0, dtype=torch.float32, device="cuda")
@@ -322,9 +328,43 @@ def test_swiglu_epilogue_small_tiles_in_the_replicated_form_are_bit_equal(ops, d
             res.append((q, s))
     finally:
         ops.set_option("grouped_rep", 1)
-    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+        ops.set_option("grouped_dynamic", 1)
+    for q, sc in res[1:]:
+        assert torch.equal(res[0][0], q) and torch.equal(res[0][1], sc)
     q2, s2 = ops.silu_and_mul_quant(ops.w8a8_block_fp8_gemm_grouped_tiles(aq, a_s, bq, bs, lay, dt))
     assert torch.equal(res[0][0], q2) and torch.equal(res[0][1], s2)
+
+
+def test_grouped_gemm_claimed_tiles_wait_runs_out_cleanly(ops):
+    """With the producers issuing nothing (a host-set test hook) no role of the grouped kernel can
+    make progress from the start: the warps that wait for a claimed tile give up after the wait
+    budget, the call reports where, and the next call is right."""
+    from inference_b200 import _capi, synth
+    import ctypes as C
+    experts, n, k = 4, 256, 256
+    ids = np.repeat(np.arange(experts, dtype=np.int32), [40, 130, 7, 128]).reshape(-1, 1)
+    lay = ops.moe_align(cuda(ids), experts)
+    x = synth.activations(ids.shape[0], k, seed=2)
+    aq, a_s = ops.moe_scatter_quant(x, lay)
+    bq, bs = synth.quantised_weights(experts * n, k, seed=3)
+    bq, bs = bq.view(experts, n, k), bs.view(experts, n // 128, k // 128)
+    want = ops.w8a8_block_fp8_gemm_grouped_tiles(aq, a_s, bq, bs, lay)
+    assert ops.device_status()[0] == 0
+    rec = (C.c_uint32 * 4)()
+    try:
+        ops.set_option("wait_budget_us", 1000)
+        ops.set_option("debug_no_loads", 1)
+        ops.w8a8_block_fp8_gemm_grouped_tiles(aq, a_s, bq, bs, lay)
+        rc = _capi.lib.inferop_device_status(rec, 1)                 # synchronises
+        assert rc == _capi.ERR_DEVICE_WAIT, f"status {rc}, record {[hex(v) for v in rec]}"
+        assert rec[0] in {0x402, 0x201, 0x202, 0x301}, hex(rec[0])
+        assert _capi.lib.inferop_device_status(rec, 0) == _capi.OK   # the record was reset
+    finally:
+        ops.set_option("debug_no_loads", 0)
+        ops.set_option("wait_budget_us", 0)
+    got = ops.w8a8_block_fp8_gemm_grouped_tiles(aq, a_s, bq, bs, lay)
+    assert ops.device_status()[0] == 0
+    assert torch.equal(got, want)
 
 
 def test_swiglu_epilogue_rejects_bad_arguments(ops):
