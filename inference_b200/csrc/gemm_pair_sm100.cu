@@ -281,14 +281,32 @@ w8a8_pair_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
       for (int j = 0; j < CT / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
 
-      float sa_n = have ? __ldg(sa_ptr) : 0.0f;
-      float sb_n = have ? __ldg(sb_ptr) : 0.0f;
+      // the scales of a K block are requested three blocks before the product that uses them, by
+      // loads the compiler cannot move next to their use (see gemm_sm100.cu): a warp that waits
+      // for its scale holds up the accumulator buffer for all sixteen of the pair
+      float sa_q0 = 0.0f, sa_q1 = 0.0f, sa_q2 = 0.0f, sb_q0 = 0.0f, sb_q1 = 0.0f, sb_q2 = 0.0f;
+      if (have) {
+        sa_q0 = ld_nc_f32_pinned(sa_ptr);
+        sb_q0 = ld_nc_f32_pinned(sb_ptr);
+        if (p.kb > 1) {
+          sa_q1 = ld_nc_f32_pinned(sa_ptr + 1);
+          sb_q1 = ld_nc_f32_pinned(sb_ptr + 1);
+        }
+        if (p.kb > 2) {
+          sa_q2 = ld_nc_f32_pinned(sa_ptr + 2);
+          sb_q2 = ld_nc_f32_pinned(sb_ptr + 2);
+        }
+      }
       bool ok = true;
       for (int kb = 0; kb < p.kb; ++kb, ++kiter) {
-        const float s = sa_n * sb_n;
-        if (kb + 1 < p.kb && have) {
-          sa_n = __ldg(sa_ptr + kb + 1);
-          sb_n = __ldg(sb_ptr + kb + 1);
+        const float s = sa_q0 * sb_q0;
+        sa_q0 = sa_q1;
+        sb_q0 = sb_q1;
+        sa_q1 = sa_q2;
+        sb_q1 = sb_q2;
+        if (kb + 3 < p.kb && have) {
+          sa_q2 = ld_nc_f32_pinned(sa_ptr + kb + 3);
+          sb_q2 = ld_nc_f32_pinned(sb_ptr + kb + 3);
         }
         const uint32_t buf = kiter % kSlices;
         if (!mbar_wait(&tmem_full[buf], (kiter / kSlices) & 1u, abort_flag, p.status, kSitePPromoTmemFull)) {
