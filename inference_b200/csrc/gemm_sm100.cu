@@ -1159,6 +1159,20 @@ int launch_gemm(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales, 
   }
 }
 
+namespace {
+// A zeroed tile counter for one launch (see gemm_body): the context's counters in rotation, so
+// that launches in flight on different streams do not share one.  A launch captured in a graph
+// keeps its counter: such a graph must not run concurrently with itself.
+int claim_tile_counter(DeviceCtx* ctx, cudaStream_t stream, int** out) {
+  static std::atomic<unsigned> next{0};
+  int* c = ctx->tile_counters + (next.fetch_add(1) % DeviceCtx::kTileCounters);
+  cudaError_t e = cudaMemsetAsync(c, 0, sizeof(int), stream);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  *out = c;
+  return INFEROP_OK;
+}
+}  // namespace
+
 int launch_gemm_grouped(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales,
                         const void* b_q, const void* b_scales, const int64_t* m_per_group,
                         int64_t groups, int64_t n, int64_t k, int32_t out_dt, cudaStream_t stream) {
@@ -1207,6 +1221,11 @@ int launch_gemm_grouped(DeviceCtx* ctx, void* c, const void* a_q, const void* a_
     p.num_tiles = n_mtiles * p.tiles_n;
     int ctas = opt.gemm_ctas > 0 ? opt.gemm_ctas : ctx->sm_count;
     if (ctas > p.num_tiles) ctas = p.num_tiles;
+    p.sched = nullptr;
+    if (opt.grouped_dynamic) {
+      const int crc = claim_tile_counter(ctx, stream, &p.sched);
+      if (crc != INFEROP_OK) return crc;
+    }
     switch (out_dt) {
       case 0: return BN == 128 ? launch_grouped_t<float, 128>(ma, mb, mc, p, tab, ctas, stream)
                                : launch_grouped_t<float, 256>(ma, mb, mc, p, tab, ctas, stream);
@@ -1313,20 +1332,6 @@ int launch_gemm_into(DeviceCtx* ctx, void* c_base, int64_t ldc, int64_t col0, co
   void* dsts[1] = {c_base};
   return launch_gemm_to_wide(ctx, dsts, 1, ldc, col0, a_q, a_scales, b_q, b_scales, m, n, k, out_dt, stream);
 }
-
-namespace {
-// A zeroed tile counter for one launch (see gemm_body): the context's counters in rotation, so
-// that launches in flight on different streams do not share one.  A launch captured in a graph
-// keeps its counter: such a graph must not run concurrently with itself.
-int claim_tile_counter(DeviceCtx* ctx, cudaStream_t stream, int** out) {
-  static std::atomic<unsigned> next{0};
-  int* c = ctx->tile_counters + (next.fetch_add(1) % DeviceCtx::kTileCounters);
-  cudaError_t e = cudaMemsetAsync(c, 0, sizeof(int), stream);
-  if (e != cudaSuccess) return note_cuda_error(e);
-  *out = c;
-  return INFEROP_OK;
-}
-}  // namespace
 
 int launch_gemm_grouped_dev(DeviceCtx* ctx, void* c, const void* a_q, const void* a_scales,
                             const void* b_q, const void* b_scales, const int32_t* tile_row0,
