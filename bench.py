@@ -870,7 +870,7 @@ def moe_ep_bench(args, world, rank, dev, max_over_ranks, sync_all, experts=256, 
     g = torch.Generator(device="cpu").manual_seed(60 + rank)
     logits = torch.randn((tokens, experts), generator=g).to(dev)
     out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
-    for _ in range(2):
+    for _ in range(5):     # the first calls also set up NCCL's all-to-all connections
         layer.forward(x, logits, out)
     sync_all()
     stream = torch.cuda.current_stream()
