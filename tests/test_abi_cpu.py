@@ -57,6 +57,12 @@ def test_argument_validation_needs_no_gpu():
     assert lib.inferop_w8a8_block_fp8_gemm(1, 1, 1, 1, 1, 0, 4, 128, 128, 128, 2, None) == _capi.ERR_SHAPE
     assert lib.inferop_w8a8_block_fp8_gemm(1, 1, 1, 1, 1, 4, 4, 128, 128, 128, 3, None) == _capi.ERR_DTYPE
     assert lib.inferop_set_option(b"no_such_key", 1) == _capi.ERR_SHAPE
+    # the knobs of the grouped launches: accepted in range, refused out of range, defaults restored
+    assert lib.inferop_set_option(b"align_ctas", 9) == _capi.ERR_SHAPE
+    for key, values, default in ((b"align_ctas", (1, 8), 0), (b"grouped_rep", (0,), 1), (b"grouped_dynamic", (0,), 1)):
+        for v in values:
+            assert lib.inferop_set_option(key, v) == _capi.OK
+        assert lib.inferop_set_option(key, default) == _capi.OK
     assert _capi.status_string(_capi.ERR_ARCH)
 
 
